@@ -1,0 +1,178 @@
+// Memory-bound row kernels: embedding gather, RMSNorm (optionally on gathered rows),
+// SwiGLU, and rotary position encoding fused with the append of keys and values
+// into cache pages.  All arithmetic is 32-bit; inputs and outputs are float32 or
+// bfloat16 as the type codes say.  Any width is accepted (no power-of-two rule).
+#include "common.cuh"
+
+using bf16 = __nv_bfloat16;
+
+namespace {
+
+// ---------------------------------------------------------------- embedding
+template <typename WT>
+__global__ void embed_gather_kernel(const WT* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int H, int V) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= V) id = 0;  // the host rejects such ids before the launch
+    const WT* row = table + (size_t)id * H;
+    float* o = out + (size_t)t * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = bw::to_f32(row[c]);
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// y = x * rsqrt(mean(x^2) + eps) * w.  One block per output row; input row is
+// rows[i] when `rows` is given (final norm on the rows whose logits are wanted).
+template <typename WT, typename OT>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict__ w,
+                               const int* __restrict__ rows, OT* __restrict__ out,
+                               int H, float eps) {
+    __shared__ float scratch[32];
+    const int i = blockIdx.x;
+    const int src = rows ? rows[i] : i;
+    const float* xr = x + (size_t)src * H;
+    OT* o = out + (size_t)i * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) { float v = xr[c]; ss = fmaf(v, v, ss); }
+    ss = bw::block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        o[c] = bw::from_f32<OT>(xr[c] * r * bw::to_f32(w[c]));
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// in: [T, 2I] with gate in columns [0, I) and up in [I, 2I); out: [T, I].
+template <typename IT, typename OT>
+__global__ void swiglu_kernel(const IT* __restrict__ gu, OT* __restrict__ out, int I, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I; const int c = (int)(idx - t * I);
+        const float g = bw::to_f32(gu[t * 2 * (size_t)I + c]);
+        const float u = bw::to_f32(gu[t * 2 * (size_t)I + I + c]);
+        const float s = g / (1.f + expf(-g));
+        out[idx] = bw::from_f32<OT>(s * u);
+    }
+}
+
+// ---------------------------------------------------------------- RoPE + append
+// qkv: [T, (nh + 2 nkv) * hd] (q heads, then k heads, then v heads).
+// q_out: [T, nh * hd] rotated queries.  Rotated keys and raw values go to the
+// page of the token's position: pages are [num_pages, nkv, page_size, hd].
+// rotary_dim = 0 rotates nothing (a mixer without rotary encoding).
+template <typename IT, typename OT>
+__global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __restrict__ positions,
+                                   const int* __restrict__ req_of_token,
+                                   const int* __restrict__ block_table, int max_blocks,
+                                   const float* __restrict__ inv_freq, int rotary_dim,
+                                   OT* __restrict__ q_out, OT* __restrict__ k_pages,
+                                   OT* __restrict__ v_pages, int nh, int nkv, int hd,
+                                   int page_size, int num_pages) {
+    extern __shared__ float cs[];  // cos[rd/2], sin[rd/2]
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = rotary_dim >> 1;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float a = (float)pos * inv_freq[j];
+        float s, c;
+        sincosf(a, &s, &c);
+        cs[j] = c; cs[half + j] = s;
+    }
+    __syncthreads();
+    const int r = req_of_token[t];
+    const int page = block_table[(size_t)r * max_blocks + pos / page_size];
+    const int slot = pos % page_size;
+    const bool page_ok = page >= 0 && page < num_pages;
+    const int row_w = (nh + 2 * nkv) * hd;
+    const IT* row = qkv + (size_t)t * row_w;
+    const int n_rot = (nh + nkv) * hd;
+    for (int e = threadIdx.x; e < row_w; e += blockDim.x) {
+        const int h = e / hd, c = e - h * hd;
+        float v = bw::to_f32(row[e]);
+        if (e < n_rot && c < rotary_dim) {
+            if (c < half) {
+                const float b = bw::to_f32(row[e + half]);
+                v = v * cs[c] - b * cs[half + c];
+            } else {
+                const float a = bw::to_f32(row[e - half]);
+                v = a * cs[half + (c - half)] + v * cs[c - half];
+            }
+        }
+        if (h < nh) {
+            q_out[(size_t)t * nh * hd + e] = bw::from_f32<OT>(v);
+        } else if (page_ok) {
+            const bool is_k = h < nh + nkv;
+            const int kvh = is_k ? h - nh : h - nh - nkv;
+            OT* dst = (is_k ? k_pages : v_pages) +
+                      (((size_t)page * nkv + kvh) * page_size + slot) * hd + c;
+            *dst = bw::from_f32<OT>(v);
+        }
+    }
+}
+
+template <typename T> const T* cp(const void* p) { return reinterpret_cast<const T*>(p); }
+template <typename T> T* mp(void* p) { return reinterpret_cast<T*>(p); }
+
+}  // namespace
+
+BW_EXPORT int bw_embed_gather(const void* table, int table_type, const int* ids, float* out,
+                              int T, int H, int V, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_type == BW_F32) embed_gather_kernel<float><<<T, threads, 0, s>>>(cp<float>(table), ids, out, H, V);
+    else if (table_type == BW_BF16) embed_gather_kernel<bf16><<<T, threads, 0, s>>>(cp<bf16>(table), ids, out, H, V);
+    else return BW_ERR_BAD_ARG;
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+BW_EXPORT int bw_rmsnorm(const float* x, const void* w, int w_type, const int* rows, void* out,
+                         int out_type, int n_rows, int H, float eps, void* stream) {
+    if (n_rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define BW_RMS(WT, OT) rmsnorm_kernel<WT, OT><<<n_rows, threads, 0, s>>>(x, cp<WT>(w), rows, mp<OT>(out), H, eps)
+    if (w_type == BW_F32 && out_type == BW_F32) BW_RMS(float, float);
+    else if (w_type == BW_F32 && out_type == BW_BF16) BW_RMS(float, bf16);
+    else if (w_type == BW_BF16 && out_type == BW_F32) BW_RMS(bf16, float);
+    else if (w_type == BW_BF16 && out_type == BW_BF16) BW_RMS(bf16, bf16);
+    else return BW_ERR_BAD_ARG;
+#undef BW_RMS
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+BW_EXPORT int bw_swiglu(const void* gu, int in_type, void* out, int out_type, int T, int I, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)T * I;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (in_type == BW_F32 && out_type == BW_F32) swiglu_kernel<float, float><<<blocks, threads, 0, s>>>(cp<float>(gu), mp<float>(out), I, total);
+    else if (in_type == BW_BF16 && out_type == BW_BF16) swiglu_kernel<bf16, bf16><<<blocks, threads, 0, s>>>(cp<bf16>(gu), mp<bf16>(out), I, total);
+    else if (in_type == BW_F32 && out_type == BW_BF16) swiglu_kernel<float, bf16><<<blocks, threads, 0, s>>>(cp<float>(gu), mp<bf16>(out), I, total);
+    else return BW_ERR_BAD_ARG;
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+BW_EXPORT int bw_rope_append(const void* qkv, int in_type, const int* positions, const int* req_of_token,
+                             const int* block_table, int max_blocks, const float* inv_freq,
+                             int rotary_dim, void* q_out, void* k_pages, void* v_pages, int out_type,
+                             int T, int nh, int nkv, int hd, int page_size, int num_pages, void* stream) {
+    if (T <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return BW_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    const size_t smem = (size_t)rotary_dim * sizeof(float);
+#define BW_RA(IT, OT) rope_append_kernel<IT, OT><<<T, threads, smem, s>>>(cp<IT>(qkv), positions, req_of_token, \
+        block_table, max_blocks, inv_freq, rotary_dim, mp<OT>(q_out), mp<OT>(k_pages), mp<OT>(v_pages), \
+        nh, nkv, hd, page_size, num_pages)
+    if (in_type == BW_F32 && out_type == BW_F32) BW_RA(float, float);
+    else if (in_type == BW_F32 && out_type == BW_BF16) BW_RA(float, bf16);
+    else if (in_type == BW_BF16 && out_type == BW_BF16) BW_RA(bf16, bf16);
+    else return BW_ERR_BAD_ARG;
+#undef BW_RA
+    BW_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,141 @@
+"""The step's batch as the kernels see it: flat token arrays plus per-request rows,
+packed into one int32 buffer that goes to the device in one copy.
+
+A batch is a list of request segments.  A segment of one token at the end of a
+request is a decode token, a longer one is a portion of a prompt; the kernels do
+not distinguish them: every token carries its position and the index of its
+request, every request its block-table row.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places among them
+    (0-based, within ``tokens``) whose logits are wanted."""
+    rid: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepBatch:
+    T: int
+    R: int
+    token_ids: torch.Tensor       # [T] int32
+    positions: torch.Tensor       # [T] int32
+    req_of_token: torch.Tensor    # [T] int32, index into the per-request rows
+    cu_q: torch.Tensor            # [R+1] int32, token offsets of the segments
+    q_start: torch.Tensor         # [R] int32, position of each segment's first token
+    kv_len: torch.Tensor          # [R] int32, request length after this step
+    state_slot: torch.Tensor      # [R] int32
+    logit_rows: torch.Tensor      # [n_want] int32, token indices
+    block_tables: Dict[int, torch.Tensor]  # group -> [R, max_blocks] int32
+    # host mirrors
+    h_q_start: List[int] = field(default_factory=list)
+    h_q_len: List[int] = field(default_factory=list)
+    h_kv_len: List[int] = field(default_factory=list)
+    h_slots: List[int] = field(default_factory=list)
+    rids: List[object] = field(default_factory=list)
+    extras: Dict[str, object] = field(default_factory=dict)  # per-step data kernels derive lazily
+
+    @property
+    def max_q_len(self) -> int:
+        return max(self.h_q_len) if self.h_q_len else 0
+
+    @property
+    def max_kv_len(self) -> int:
+        return max(self.h_kv_len) if self.h_kv_len else 0
+
+
+class BatchBuilder:
+    """Packs step data into pinned host memory and uploads it with one copy.
+
+    A small ring of pinned buffers, each guarded by an event, lets the host prepare
+    the next step while the previous copy may still be in flight."""
+
+    def __init__(self, device: torch.device, ring: int = 4):
+        self.device = device
+        self._ring = ring
+        self._bufs: List[Optional[torch.Tensor]] = [None] * ring
+        self._events: List[Optional[torch.cuda.Event]] = [None] * ring
+        self._next = 0
+
+    def _pinned(self, n: int) -> torch.Tensor:
+        i = self._next
+        self._next = (i + 1) % self._ring
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        buf = self._bufs[i]
+        if buf is None or buf.numel() < n:
+            cap = max(1024, 1 << (n - 1).bit_length())
+            buf = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            self._bufs[i] = buf
+        self._slot = i
+        return buf
+
+    def build(self, segments, logit_rows: Sequence[int], block_rows: Dict[int, List[List[int]]],
+              min_blocks: int = 0) -> StepBatch:
+        """``segments``: list of (rid, tokens, q_start, kv_len, slot).  ``block_rows``:
+        group -> one block-table row (list of page ids) per segment."""
+        R = len(segments)
+        T = sum(len(s[1]) for s in segments)
+        widths = {g: max([min_blocks, 1] + [len(r) for r in rows]) for g, rows in block_rows.items()}
+        n_want = len(logit_rows)
+        total = 3 * T + (R + 1) + 3 * R + n_want + sum(R * w for w in widths.values())
+        host = self._pinned(total)
+        h = host[:total].numpy()
+        off = 0
+
+        def take(n):
+            nonlocal off
+            a = (off, off + n)
+            off += n
+            return a
+
+        a_tok, a_pos, a_req = take(T), take(T), take(T)
+        a_cu, a_qs, a_kv, a_sl = take(R + 1), take(R), take(R), take(R)
+        a_lr = take(n_want)
+        a_bt = {g: take(R * w) for g, w in widths.items()}
+        t = 0
+        h[a_cu[0]] = 0
+        for r, (rid, toks, q_start, kv_len, slot) in enumerate(segments):
+            n = len(toks)
+            h[a_tok[0] + t: a_tok[0] + t + n] = toks
+            h[a_pos[0] + t: a_pos[0] + t + n] = range(q_start, q_start + n)
+            h[a_req[0] + t: a_req[0] + t + n] = r
+            t += n
+            h[a_cu[0] + r + 1] = t
+            h[a_qs[0] + r] = q_start
+            h[a_kv[0] + r] = kv_len
+            h[a_sl[0] + r] = slot
+        if n_want:
+            h[a_lr[0]:a_lr[1]] = logit_rows
+        for g, rows in block_rows.items():
+            w = widths[g]
+            view = h[a_bt[g][0]:a_bt[g][1]].reshape(R, w)
+            view[:] = -1
+            for r, row in enumerate(rows):
+                view[r, :len(row)] = row
+        dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        dev.copy_(host[:total], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = self._events[self._slot] or torch.cuda.Event()
+            ev.record()
+            self._events[self._slot] = ev
+
+        def d(a):
+            return dev[a[0]:a[1]]
+
+        return StepBatch(
+            T=T, R=R, token_ids=d(a_tok), positions=d(a_pos), req_of_token=d(a_req), cu_q=d(a_cu),
+            q_start=d(a_qs), kv_len=d(a_kv), state_slot=d(a_sl), logit_rows=d(a_lr),
+            block_tables={g: d(a_bt[g]).view(R, widths[g]) for g in widths},
+            h_q_start=[s[2] for s in segments], h_q_len=[len(s[1]) for s in segments],
+            h_kv_len=[s[3] for s in segments], h_slots=[s[4] for s in segments],
+            rids=[s[0] for s in segments])

@@ -1,0 +1,214 @@
+"""The engine: a model, its cache, and ONE step function.
+
+``Engine.step(entries)`` takes a batch of (request, its next tokens): portions of
+prompts beside single decoded tokens, cut anywhere.  It runs only those tokens,
+reading everything earlier from the cache, and returns the float32 logits at the
+places asked for.  The reference has three disjoint widths instead (one token,
+one chunk of one sequence, one token each of B sequences:
+src/core/engine.cpp:822, 895, 1304); here they are one call.
+
+Pages for every token of the step are reserved before anything runs, so a step
+either runs whole or raises :class:`OutOfPages` with nothing changed (the
+reference budgets pages before compute likewise:
+src/core/engine_prefill_coordinator.cpp:160-169).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Mapping, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages
+from ..config.registry import load_config, parse_config
+from ..config.specs import ModelConfig
+from ..models.decoder import DecoderModel
+from ..parts.base import BuildContext, PagedKVRequest
+from ..weights.loader import bind_tensors, load_weights
+from ..weights.random_init import random_tensors
+from .batch import BatchBuilder, StepBatch, StepEntry
+
+_DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16,
+           "bf16": torch.bfloat16, torch.float32: torch.float32, torch.bfloat16: torch.bfloat16}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+@dataclass
+class EngineOptions:
+    dtype: object = "bfloat16"      # "bfloat16" | "float32"
+    page_size: int = 16
+    num_pages: Optional[int] = None  # pages per cache group; None: from max_tokens or kv_fraction
+    max_tokens: Optional[int] = None  # tokens the cache holds (each request rounded up to a page)
+    kv_fraction: float = 0.6         # of the memory free after the weights, if neither is given
+    max_requests: int = 64
+    max_batch_tokens: int = 8192
+    device: str = "cuda:0"
+
+
+def require_cuda(device: torch.device) -> None:
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise EngineError("blackwellllm_b200 runs on a CUDA device (B200, sm_100a) only; "
+                          "there is no CPU path")
+
+
+class Engine:
+    def __init__(self, config: ModelConfig, model: DecoderModel, options: EngineOptions):
+        self.config = config
+        self.model = model
+        self.options = options
+        self.device = torch.device(options.device)
+        self.dtype = _DTYPES[options.dtype]
+        requests = model.cache_requests()
+        paged = [r for r in requests if isinstance(r, PagedKVRequest)]
+        num_pages = self._decide_num_pages(options, requests)
+        self.cache = CacheManager(requests, options.page_size, num_pages, options.max_requests,
+                                  dtype=self.dtype, device=self.device)
+        self._builder = BatchBuilder(self.device)
+        self.steps_run = 0
+        self.tokens_run = 0
+        del paged
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def _options(opts: Mapping[str, object]) -> EngineOptions:
+        o = opts.get("options")
+        if o is not None:
+            return o
+        return EngineOptions(**{k: v for k, v in opts.items() if k != "options"})
+
+    @classmethod
+    def _build(cls, config: ModelConfig, options: EngineOptions):
+        if options.dtype not in _DTYPES:
+            raise EngineError(f"dtype must be 'bfloat16' or 'float32', got {options.dtype!r}")
+        device = torch.device(options.device)
+        require_cuda(device)
+        torch.cuda.set_device(device)
+        ctx = BuildContext(device, _DTYPES[options.dtype])
+        return DecoderModel(config, ctx), ctx
+
+    @classmethod
+    def from_folder(cls, model_dir: str, **opts) -> "Engine":
+        """A folder with config.json and model.safetensors (or an index and shards)."""
+        options = cls._options(opts)
+        config = load_config(model_dir)
+        model, ctx = cls._build(config, options)
+        model.bind(load_weights(model_dir, model.param_specs(), ctx.dtype, ctx.device))
+        return cls(config, model, options)
+
+    @classmethod
+    def from_tensors(cls, raw_config: Mapping[str, object], tensors: Mapping[str, torch.Tensor],
+                     **opts) -> "Engine":
+        options = cls._options(opts)
+        config = parse_config(raw_config)
+        model, ctx = cls._build(config, options)
+        model.bind(bind_tensors(tensors, model.param_specs(), ctx.dtype, ctx.device))
+        return cls(config, model, options)
+
+    @classmethod
+    def from_config(cls, raw_config: Mapping[str, object], seed: int = 0, std: float = 0.02,
+                    bias_std: Optional[float] = None, **opts) -> "Engine":
+        """Random weights made on the device (no folder is written)."""
+        options = cls._options(opts)
+        config = parse_config(raw_config)
+        model, ctx = cls._build(config, options)
+        specs = model.param_specs()
+        tensors = random_tensors(specs, seed, std, bias_std, dtype=ctx.dtype, device=ctx.device)
+        model.bind(bind_tensors(tensors, specs, ctx.dtype, ctx.device))
+        return cls(config, model, options)
+
+    def _decide_num_pages(self, o: EngineOptions, requests) -> int:
+        if o.num_pages is not None:
+            return int(o.num_pages)
+        if o.max_tokens is not None:
+            return max(1, -(-int(o.max_tokens) // o.page_size))
+        groups: Dict[PagedKVRequest, int] = {}
+        for r in requests:
+            if isinstance(r, PagedKVRequest):
+                groups[r] = groups.get(r, 0) + 1
+        if not groups:
+            return 1
+        esize = 4 if self.dtype == torch.float32 else 2
+        per_page = sum(n * 2 * r.num_kv_heads * o.page_size * r.head_dim * esize for r, n in groups.items())
+        free, _ = torch.cuda.mem_get_info(self.device)
+        return max(1, int(free * o.kv_fraction) // per_page)
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, rid) -> None:
+        self.cache.add_request(rid)
+
+    def end_request(self, rid) -> None:
+        """The request is finished: its pages and its state slot are given back."""
+        self.cache.free_request(rid)
+
+    def has_request(self, rid) -> bool:
+        return self.cache.has(rid)
+
+    # ------------------------------------------------------------------ the step
+    def prepare(self, entries: Sequence[StepEntry]) -> StepBatch:
+        """Checks the entries, reserves pages for all their tokens (all or nothing)
+        and uploads the batch."""
+        V = self.config.vocab_size
+        seen = set()
+        T = 0
+        for e in entries:
+            if e.rid in seen:
+                raise EngineError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+            n = len(e.tokens)
+            if n == 0:
+                raise EngineError(f"request {e.rid!r}: a step entry needs at least one token")
+            for t in e.tokens:
+                if not 0 <= int(t) < V:
+                    raise EngineError(f"request {e.rid!r}: token id {t} is outside [0, {V})")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise EngineError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
+            T += n
+        if T > self.options.max_batch_tokens:
+            raise EngineError(f"step of {T} tokens exceeds max_batch_tokens={self.options.max_batch_tokens}")
+        new = [e.rid for e in entries if not self.cache.has(e.rid)]
+        if len(new) > self.cache.slots.num_free:
+            raise OutOfPages(f"{len(new)} new requests but {self.cache.slots.num_free} request slots are free")
+        n_groups = len(self.cache.groups)
+        need = [0] * n_groups
+        ps = self.cache.page_size
+        for e in entries:
+            if self.cache.has(e.rid):
+                pn = self.cache.pages_needed(e.rid, len(e.tokens))
+            else:
+                pn = [-(-len(e.tokens) // ps)] * n_groups
+            need = [a + b for a, b in zip(need, pn)]
+        free = self.cache.free_pages()
+        if any(n > f for n, f in zip(need, free)):
+            raise OutOfPages(f"step needs {need} pages per group, {free} are free")
+        for rid in new:
+            self.cache.add_request(rid)
+        segments, rows, t0 = [], [], 0
+        for e in entries:
+            q_start = self.cache.append(e.rid, len(e.tokens))
+            segments.append((e.rid, [int(t) for t in e.tokens], q_start, q_start + len(e.tokens),
+                             self.cache.slot(e.rid)))
+            rows.extend(t0 + int(w) for w in e.want)
+            t0 += len(e.tokens)
+        block_rows = {g: [self.cache.block_table(e.rid, g) for e in entries] for g in range(n_groups)}
+        return self._builder.build(segments, rows, block_rows)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs one batch; returns float32 logits [wanted, vocab] on the device, in the
+        order of the entries and of each entry's ``want``."""
+        if not entries:
+            return torch.empty((0, self.config.vocab_size), dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            batch = self.prepare(entries)
+            logits = self.model.forward(batch, self.cache.views)
+        for e in entries:
+            self.cache.release_passed(e.rid)
+        self.steps_run += 1
+        self.tokens_run += batch.T
+        return logits

@@ -1,0 +1,257 @@
+"""Python face of the CUDA kernels: argument checks, then a ctypes call on the
+current CUDA stream.  Nothing here computes; a tensor on the CPU, of the wrong
+type or not contiguous is an error, never a detour through another
+implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+_TYPE = {torch.float32: F32, torch.bfloat16: BF16}
+
+c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{what}: bad argument")
+    if code == -2:
+        raise KernelError(f"{what}: size or option not supported by this kernel")
+    if code == -3:
+        raise KernelError(f"{what}: CUDA driver call failed")
+    if code <= -10:
+        raise KernelError(f"{what}: refused with code {code}")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dev(t: torch.Tensor, name: str, dtype=None, contiguous=True):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    return t
+
+
+def _code(t: torch.Tensor, name: str) -> int:
+    if t.dtype not in _TYPE:
+        raise KernelError(f"{name}: dtype {t.dtype} is not supported (float32 or bfloat16)")
+    return _TYPE[t.dtype]
+
+
+_sigs_done = set()
+
+
+def _fn(lib_name: str, fn_name: str, argtypes, macros=None, extra_flags=()):
+    lib = load_library(lib_name, macros, extra_flags)
+    fn = getattr(lib, fn_name)
+    key = (id(lib), fn_name)
+    if key not in _sigs_done:
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _sigs_done.add(key)
+    return fn
+
+
+# ------------------------------------------------------------------ elementwise
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _dev(table, "table"); _dev(ids, "ids", torch.int32)
+    V, H = table.shape
+    T = ids.numel()
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _dev(out, "out", torch.float32)
+    fn = _fn("elementwise", "bw_embed_gather",
+             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(table), _code(table, "table"), _ptr(ids), _ptr(out), T, H, V, _stream()), "embed_gather")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _dev(x, "x", torch.float32); _dev(w, "w")
+    H = x.shape[-1]
+    if w.numel() != H:
+        raise KernelError(f"rmsnorm: gain has {w.numel()} elements, rows have {H}")
+    n = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _dev(rows, "rows", torch.int32)
+    if out is None:
+        out = torch.empty((n, H), dtype=out_dtype, device=x.device)
+    _dev(out, "out", out_dtype)
+    fn = _fn("elementwise", "bw_rmsnorm",
+             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(x), _ptr(w), _code(w, "w"), _ptr(rows), _ptr(out), _code(out, "out"), n, H,
+              float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def swiglu(gu: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    _dev(gu, "gate_up")
+    T, I2 = gu.shape
+    if I2 % 2:
+        raise KernelError("swiglu: input width must be even (gate | up)")
+    out = torch.empty((T, I2 // 2), dtype=out_dtype or gu.dtype, device=gu.device)
+    fn = _fn("elementwise", "bw_swiglu", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(gu), _code(gu, "gate_up"), _ptr(out), _code(out, "out"), T, I2 // 2, _stream()), "swiglu")
+    return out
+
+
+def rope_append(qkv: torch.Tensor, positions: torch.Tensor, req_of_token: torch.Tensor,
+                block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                k_pages: torch.Tensor, v_pages: torch.Tensor, nh: int, nkv: int, hd: int,
+                q_out: Optional[torch.Tensor] = None, append: bool = True) -> torch.Tensor:
+    """Rotates q and k heads of ``qkv`` [T, (nh+2nkv)*hd], returns q [T, nh*hd] in the
+    pages' dtype, and writes rotated k and raw v to pages [num_pages, nkv, page, hd]."""
+    _dev(qkv, "qkv"); _dev(positions, "positions", torch.int32)
+    _dev(req_of_token, "req_of_token", torch.int32); _dev(block_table, "block_table", torch.int32)
+    _dev(k_pages, "k_pages"); _dev(v_pages, "v_pages", k_pages.dtype)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * hd:
+        raise KernelError(f"rope_append: qkv width {qkv.shape[1]} != (nh + 2 nkv) * hd = {(nh + 2 * nkv) * hd}")
+    num_pages, pk, page_size, phd = k_pages.shape
+    if pk != nkv or phd != hd or v_pages.shape != k_pages.shape:
+        raise KernelError("rope_append: pages must be [num_pages, nkv, page_size, head_dim]")
+    if rotary_dim:
+        _dev(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("rope_append: inv_freq must have rotary_dim / 2 entries")
+    if q_out is None:
+        q_out = torch.empty((T, nh * hd), dtype=k_pages.dtype, device=qkv.device)
+    _dev(q_out, "q_out", k_pages.dtype)
+    fn = _fn("elementwise", "bw_rope_append",
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(qkv), _code(qkv, "qkv"), _ptr(positions), _ptr(req_of_token), _ptr(block_table),
+              block_table.shape[1], _ptr(inv_freq), rotary_dim, _ptr(q_out), _ptr(k_pages), _ptr(v_pages),
+              _code(k_pages, "pages"), T, nh, nkv, hd, page_size, num_pages if append else 0, _stream()),
+           "rope_append")
+    return q_out
+
+
+# ------------------------------------------------------------------ matrix products
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+              accumulate: bool = False) -> torch.Tensor:
+    """out (=|+=) x @ w.T (+ bias) with float32 FMAs on the CUDA cores."""
+    _dev(x, "x", contiguous=False); _dev(w, "w")
+    if x.dtype != w.dtype:
+        raise KernelError(f"gemm: x is {x.dtype} but w is {w.dtype}")
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: x has {K} columns, w has {K2}")
+    if x.stride(1) != 1:
+        raise KernelError("gemm: x rows must be contiguous")
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm: accumulate needs an output tensor")
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    _dev(out, "out", contiguous=False)
+    if out.shape != (M, N) or out.stride(1) != 1:
+        raise KernelError("gemm: out must be [M, N] with contiguous rows")
+    if bias is not None:
+        _dev(bias, "bias")
+        if bias.numel() != N:
+            raise KernelError("gemm: bias must have N entries")
+    fn = _fn("gemm_simt", "bw_gemm_simt",
+             [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+              c_int, c_void_p])
+    _check(fn(_ptr(x), _ptr(w), _code(x, "x"), _ptr(bias), _code(bias, "bias") if bias is not None else 0,
+              _ptr(out), _code(out, "out"), M, N, K, x.stride(0), out.stride(0), int(accumulate), _stream()),
+           "gemm_simt")
+    return out
+
+
+# ------------------------------------------------------------------ attention
+
+def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, positions: torch.Tensor,
+                   req_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, window: Optional[int],
+                   scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _dev(q, "q"); _dev(k_pages, "k_pages", q.dtype); _dev(v_pages, "v_pages", q.dtype)
+    _dev(positions, "positions", torch.int32); _dev(req_of_token, "req_of_token", torch.int32)
+    _dev(block_table, "block_table", torch.int32)
+    num_pages, nkv, page_size, hd = k_pages.shape
+    T = q.shape[0]
+    if q.shape[1] != nh * hd:
+        raise KernelError("attention: q must be [T, nh * head_dim]")
+    if out is None:
+        out = torch.empty_like(q)
+    fn = _fn("attention_simt", "bw_attention_simt",
+             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _code(q, "q"), _ptr(positions), _ptr(req_of_token),
+              _ptr(block_table), block_table.shape[1], _ptr(out), T, nh, nkv, hd, page_size, num_pages,
+              int(window or 0), float(scale), _stream()), "attention_simt")
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
+           u: Optional[torch.Tensor]) -> torch.Tensor:
+    """One token per row of ``logits`` [R, V]; greedy where temperature is None or <= 0."""
+    _dev(logits, "logits", torch.float32, contiguous=False)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be [R, V] with contiguous rows")
+    R, V = logits.shape
+    for name, t in (("temperature", temperature), ("top_p", top_p), ("u", u)):
+        if t is not None:
+            _dev(t, name, torch.float32)
+            if t.numel() != R:
+                raise KernelError(f"sample: {name} must have one entry per row")
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    fn = _fn("sampling", "bw_sample",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p])
+    _check(fn(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(u), _ptr(out), R, V, logits.stride(0),
+              _stream()), "sample")
+    return out
+
+
+# ------------------------------------------------------------------ dispatch
+
+def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 kernel takes this product (see gemm_tc)."""
+    return False
+
+
+def gemm_tc(x, w, bias=None, out=None, out_dtype=None, accumulate=False):
+    raise KernelError("the tensor-core matrix product is not available for this shape")
+
+
+def check_attention_supported(dtype: torch.dtype, head_dim: int) -> None:
+    if head_dim <= 0 or head_dim > 256:
+        raise KernelError(f"attention: head_dim {head_dim} is not supported (1..256)")
+    if dtype == torch.bfloat16 and head_dim % 16:
+        raise KernelError(f"attention: the bfloat16 kernels take head sizes in steps of 16, got {head_dim}")
+
+
+def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
+                    block_table: torch.Tensor, nh: int, window: Optional[int], scale: float) -> torch.Tensor:
+    """Causal attention of the batch's tokens over the paged cache (which already
+    holds this step's keys and values)."""
+    return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
+                          window, scale)

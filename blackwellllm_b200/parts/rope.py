@@ -1,0 +1,61 @@
+"""Position encodings for attention mixers.
+
+:class:`RotaryEncoding` is rotate_half RoPE (src/kernels/rope.cu:7-35): pair
+(j, j + rd/2) of each query and key head turns by ``pos * inv_freq[j]``,
+``inv_freq[j] = theta ** (-2j/rd)``, optionally rescaled by the llama3
+wavelength bands (src/kernels/rope.cuh:24-38).  The table is computed once on the
+host in float64 and stored as float32; the angle is the float32 product
+``float(pos) * inv_freq[j]`` and sine/cosine are the precise ones.
+
+:class:`NoPosition` rotates nothing.  Both append rotated keys and raw values to
+the cache pages in the same kernel.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..kernels import ops
+from .base import BuildContext, PositionEncoding, register_position
+
+
+def rotary_inv_freq(theta: float, rotary_dim: int, scaling=None) -> torch.Tensor:
+    j = torch.arange(rotary_dim // 2, dtype=torch.float64)
+    inv = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * j / rotary_dim)
+    if scaling is not None:
+        if getattr(scaling, "kind", None) != "llama3":
+            raise ValueError(f"unknown rope scaling {scaling!r}")
+        orig = float(scaling.original_max_position_embeddings)
+        low, high, factor = scaling.low_freq_factor, scaling.high_freq_factor, scaling.factor
+        wavelen = 2.0 * math.pi / inv
+        smooth = (orig / wavelen - low) / (high - low)
+        mid = (1.0 - smooth) * inv / factor + smooth * inv
+        inv = torch.where(wavelen < orig / high, inv,
+                          torch.where(wavelen > orig / low, inv / factor, mid))
+    return inv.to(torch.float32)
+
+
+class RotaryEncoding(PositionEncoding):
+    def __init__(self, spec, head_dim: int, ctx: BuildContext):
+        if spec.rotary_dim % 2 or not 0 < spec.rotary_dim <= head_dim:
+            raise ValueError(f"rotary_dim {spec.rotary_dim} must be even and in (0, head_dim={head_dim}]")
+        self.rotary_dim = int(spec.rotary_dim)
+        self.inv_freq = rotary_inv_freq(spec.theta, self.rotary_dim, spec.scaling).to(ctx.device)
+
+    def rotate_append(self, qkv, batch, cache, nh, nkv, hd, append=True):
+        return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
+                               self.inv_freq, self.rotary_dim, cache.k_pages, cache.v_pages, nh, nkv, hd, append=append)
+
+
+class NoPosition(PositionEncoding):
+    def __init__(self, spec, head_dim: int, ctx: BuildContext):
+        pass
+
+    def rotate_append(self, qkv, batch, cache, nh, nkv, hd, append=True):
+        return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
+                               None, 0, cache.k_pages, cache.v_pages, nh, nkv, hd, append=append)
+
+
+register_position("rope", RotaryEncoding)
+register_position("none", NoPosition)
