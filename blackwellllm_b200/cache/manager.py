@@ -185,6 +185,31 @@ class CacheManager:
                 freed += len(pages)
         return freed
 
+    def truncate(self, rid, new_length: int) -> None:
+        """Rolls the request back to ``new_length`` tokens and gives back the pages
+        behind it (the reference's rewind, src/core/paging/paged_kv_cache.h:196-208).
+        Not possible into a stretch whose pages a window has already released."""
+        rq = self._requests[rid]
+        if not 0 <= new_length <= rq.length:
+            raise ValueError(f"cannot truncate request {rid!r} of {rq.length} tokens to {new_length}")
+        if self._states and 0 < new_length < rq.length:
+            raise ValueError("a request with fixed-size state can only be rolled back to its start")
+        if self._states and new_length == 0:
+            for sv in self._states:
+                if sv.state is not None:
+                    sv.state[rq.slot].zero_()
+        keep = -(-new_length // self.page_size)
+        for gi, g in enumerate(self.groups):
+            if g.request.window is not None and rq.first_live[gi] > self._first_needed_block(g, new_length):
+                raise ValueError(f"request {rid!r}: the pages before position {new_length} were released "
+                                 f"by the window and cannot be restored")
+        for gi, g in enumerate(self.groups):
+            tail = rq.blocks[gi][keep:]
+            g.allocator.free([p for p in tail if p >= 0])
+            del rq.blocks[gi][keep:]
+            rq.first_live[gi] = min(rq.first_live[gi], keep)
+        rq.length = new_length
+
     def free_request(self, rid) -> None:
         rq = self._requests.pop(rid)
         for gi, g in enumerate(self.groups):
