@@ -233,13 +233,67 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Opt
 
 # ------------------------------------------------------------------ dispatch
 
+_GEMM_TC_ARGS = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_int,
+                 c_void_p, c_ll, c_int, c_void_p]
+_WORKSPACE_BYTES = 64 << 20
+_workspaces = {}
+
+
+def _workspace(device: torch.device) -> torch.Tensor:
+    """Scratch for split-K partial sums, one per device, made at first use."""
+    ws = _workspaces.get(device)
+    if ws is None:
+        ws = torch.empty(_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
 def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the tcgen05 kernel takes this product (see gemm_tc)."""
-    return False
+    """Whether the tcgen05 kernel takes this product: bfloat16, inner size and row
+    stride multiples of 8 elements, 16-byte aligned (what a TMA descriptor can express)."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous():
+        return False
+    K = x.shape[1]
+    return (K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc(x, w, bias=None, out=None, out_dtype=None, accumulate=False):
-    raise KernelError("the tensor-core matrix product is not available for this shape")
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+            accumulate: bool = False, force_splits: int = 0) -> torch.Tensor:
+    """out (=|+=) x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, float32 sums)."""
+    _dev(x, "x", torch.bfloat16, contiguous=False); _dev(w, "w", torch.bfloat16)
+    if not gemm_tc_supports(x, w):
+        raise KernelError("gemm_tc: operands must be bfloat16 with K and the row stride multiples of 8 "
+                          "and 16-byte aligned")
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: x has {K} columns, w has {K2}")
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm: accumulate needs an output tensor")
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    _dev(out, "out", contiguous=False)
+    if out.shape != (M, N) or out.stride(1) != 1:
+        raise KernelError("gemm: out must be [M, N] with contiguous rows")
+    if bias is not None:
+        _dev(bias, "bias")
+        if bias.numel() != N:
+            raise KernelError("gemm: bias must have N entries")
+    ws = _workspace(x.device)
+    fn = _fn("gemm_tc", "bw_gemm_tc", _GEMM_TC_ARGS)
+    _check(fn(_ptr(x), _ptr(w), _ptr(bias), _code(bias, "bias") if bias is not None else 0, _ptr(out),
+              _code(out, "out"), M, N, K, x.stride(0), out.stride(0), int(accumulate), _ptr(ws), ws.numel(),
+              int(force_splits), _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_status() -> int:
+    """0 if no bounded wait in the tensor-core kernels ever gave up (synchronises the device)."""
+    lib = load_library("gemm_tc")
+    lib.bw_gemm_tc_status.restype = c_int
+    return int(lib.bw_gemm_tc_status())
 
 
 def check_attention_supported(dtype: torch.dtype, head_dim: int) -> None:
