@@ -1,0 +1,454 @@
+// Paged causal grouped-query flash attention for bfloat16, head size HEAD_DIM (a
+// compile-time multiple of 16, at most 256; the library is built per head size).
+// Tensor-core products with mma.sync m16n8k16 (bf16 in, fp32 out); scores, the
+// running maximum, the running sum and the output accumulator are float32; the
+// probabilities are rounded to bfloat16 for the P.V product.
+//
+// The query heads of one kv head are stacked into the row dimension: row = token *
+// G + head-in-group.  Two kernels share the same inner loop over 64-key tiles that
+// cp.async gathers page by page into padded shared memory (double buffered):
+//   * attn_rows_kernel: a work item is 64 rows of one (request, kv head); each of
+//     the 4 warps owns 16 rows and walks all keys up to the causal diagonal.
+//     For prompt portions (more than 16 rows).
+//   * attn_keys_kernel: a work item is all (at most 16) rows of one (request, kv
+//     head) over one slice of the keys; the 4 warps split each tile's keys and are
+//     merged at the end; slices are merged by attn_merge_kernel.  For decode tokens.
+// Keys beyond the request's length and pages the block table no longer holds are
+// zero-filled in shared memory and masked, so stale cache contents never matter.
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<multiple of 16>"
+#endif
+
+using bf16 = __nv_bfloat16;
+
+namespace {
+
+constexpr int HD = HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 in [16, 256]");
+constexpr int BN = 64;                 // keys per tile
+constexpr int NWARPS = 4;
+constexpr int THREADS = NWARPS * 32;
+constexpr int ROW_BYTES = HD * 2 + 16; // padded row: ldmatrix rows land in distinct 16-byte bank groups
+constexpr int KSTEPS = HD / 16;
+constexpr int CPR = HD / 8;            // 16-byte chunks per row
+constexpr int TILE_BYTES = BN * ROW_BYTES;
+
+struct Params {
+    const bf16* q; const bf16* k_pages; const bf16* v_pages; bf16* out;
+    const int* cu_q; const int* q_start; const int* kv_len; const int* block_table;
+    const int* work;              // int4 per item
+    float* part_o; float* part_ml; // slices' partial results (attn_keys_kernel)
+    int max_blocks, nh, nkv, G, page_size, num_pages, window;
+    float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;  // 0: nothing is read, 16 zero bytes are written
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Gathers keys [key0, key0 + BN) of kv head g into a K and a V tile (padded rows).
+__device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int g, int kv_len, int key0,
+                                             uint8_t* k_tile, uint8_t* v_tile) {
+    for (int idx = threadIdx.x; idx < BN * CPR; idx += THREADS) {
+        const int row = idx / CPR, ch = idx - row * CPR;
+        const int kp = key0 + row;
+        bool valid = kp < kv_len;
+        int page = valid ? bt[kp / p.page_size] : -1;
+        valid = valid && page >= 0 && page < p.num_pages;
+        const size_t off = valid ? ((((size_t)page * p.nkv + g) * p.page_size + (kp % p.page_size)) * HD + ch * 8) : 0;
+        cp_async16(smem_u32(k_tile + row * ROW_BYTES + ch * 16), p.k_pages + off, valid);
+        cp_async16(smem_u32(v_tile + row * ROW_BYTES + ch * 16), p.v_pages + off, valid);
+    }
+}
+
+// Rows [row0, row0 + 16) of the stacked queries of (request, kv head g) into 16 padded smem rows
+// (zeros for rows beyond n_rows).  row = token * G + head-in-group.
+__device__ __forceinline__ void load_q_rows(const Params& p, int tok_base, int g, int row0, int n_rows,
+                                            uint8_t* q_tile, int rows_to_load) {
+    for (int idx = threadIdx.x; idx < rows_to_load * CPR; idx += THREADS) {
+        const int r = idx / CPR, ch = idx - r * CPR;
+        const int row = row0 + r;
+        const bool valid = row < n_rows;
+        const int tok = row / p.G, hg = row - tok * p.G;
+        const size_t off = valid ? (((size_t)(tok_base + tok) * p.nh + g * p.G + hg) * HD + ch * 8) : 0;
+        cp_async16(smem_u32(q_tile + r * ROW_BYTES + ch * 16), p.q + off, valid);
+    }
+}
+
+struct RowState {
+    float m[2], l[2];      // rows lane/4 and lane/4 + 8 of the warp's 16
+    int qpos[2], lo[2];    // the rows' own positions and first visible key (qpos < 0: no such row)
+};
+
+// One slab of NK keys (starting k_off rows into the tiles) for the warp's 16 query rows.
+template <int NK>
+__device__ __forceinline__ void process_keys(const uint32_t (&qf)[KSTEPS][4], const uint8_t* k_tile,
+                                             const uint8_t* v_tile, int k_off, int key_pos0, bool need_mask,
+                                             float scale_log2, RowState& st, float (&o)[HD / 8][4]) {
+    const int lane = threadIdx.x & 31;
+    float s[NK / 8][4];
+#pragma unroll
+    for (int j = 0; j < NK / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+    const uint32_t kb = smem_u32(k_tile) + (k_off + (lane & 7) + 8 * (lane >> 4)) * ROW_BYTES + 16 * ((lane >> 3) & 1);
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+        for (int nb = 0; nb < NK / 16; ++nb) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(kb + nb * 16 * ROW_BYTES + ks * 32, b0, b1, b2, b3);
+            mma_bf16(s[2 * nb], qf[ks], b0, b1);
+            mma_bf16(s[2 * nb + 1], qf[ks], b2, b3);
+        }
+    }
+    // scale, mask, online softmax
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            float v = s[j][e] * scale_log2;
+            if (need_mask) {
+                const int kp = key_pos0 + k_off + j * 8 + 2 * (lane & 3) + (e & 1);
+                if (kp > st.qpos[h] || kp < st.lo[h]) v = -INFINITY;
+            }
+            s[j][e] = v;
+            mx[h] = fmaxf(mx[h], v);
+        }
+    }
+    float corr[2], mu[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(st.m[h], mx[h]);
+        mu[h] = m_new == -INFINITY ? 0.f : m_new;
+        corr[h] = exp2f(st.m[h] - mu[h]);   // m = -inf: 0
+        st.m[h] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float pv = exp2f(s[j][e] - mu[e >> 1]);
+            s[j][e] = pv;
+            sum[e >> 1] += pv;
+        }
+    }
+    st.l[0] = st.l[0] * corr[0] + sum[0];
+    st.l[1] = st.l[1] * corr[1] + sum[1];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) { o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1]; }
+    // O += P . V
+    const uint32_t vb = smem_u32(v_tile) + (k_off + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_BYTES + 16 * (lane >> 4);
+#pragma unroll
+    for (int kk = 0; kk < NK / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int nb = 0; nb < HD / 16; ++nb) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t(vb + kk * 16 * ROW_BYTES + nb * 32, b0, b1, b2, b3);
+            mma_bf16(o[2 * nb], a, b0, b1);
+            mma_bf16(o[2 * nb + 1], a, b2, b3);
+        }
+    }
+}
+
+__device__ __forceinline__ void load_q_frags(const uint8_t* q_rows, uint32_t (&qf)[KSTEPS][4]) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t base = smem_u32(q_rows) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_BYTES + 16 * (lane >> 4);
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) ldsm_x4(base + ks * 32, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+}
+
+__device__ __forceinline__ void init_rows(const Params& p, RowState& st, int row_base, int n_rows, int q_pos0) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = row_base + (lane >> 2) + 8 * h;
+        st.m[h] = -INFINITY; st.l[h] = 0.f;
+        if (row < n_rows) {
+            st.qpos[h] = q_pos0 + row / p.G;
+            st.lo[h] = p.window > 0 ? max(0, st.qpos[h] - p.window + 1) : 0;
+        } else { st.qpos[h] = -1; st.lo[h] = 0; }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// work item: (request, first token of the tile within the request's segment, -, -)
+__global__ void __launch_bounds__(THREADS)
+attn_rows_kernel(Params p, int toks_per_tile) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint8_t* q_tile = smem;                       // 64 rows
+    uint8_t* kv = smem + BN * ROW_BYTES;          // [2 stages][K, V]
+    const int4 w = reinterpret_cast<const int4*>(p.work)[blockIdx.x];
+    const int r = w.x, tok0 = w.y, g = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_len = p.cu_q[r + 1] - p.cu_q[r];
+    const int kv_len = p.kv_len[r];
+    const int ntok = min(toks_per_tile, q_len - tok0);
+    const int n_rows = ntok * p.G;                // <= 64
+    const int q_pos0 = p.q_start[r] + tok0;
+    const int* bt = p.block_table + (size_t)r * p.max_blocks;
+
+    load_q_rows(p, p.cu_q[r] + tok0, g, 0, n_rows, q_tile, 64);
+    cp_async_commit();
+
+    const int last_pos = q_pos0 + ntok - 1;
+    const int first_key = p.window > 0 ? max(0, q_pos0 - p.window + 1) : 0;
+    const int t_lo = first_key / BN, t_hi = last_pos / BN;   // inclusive
+    load_kv_tile(p, bt, g, kv_len, t_lo * BN, kv, kv + TILE_BYTES);
+    cp_async_commit();
+
+    RowState st;
+    init_rows(p, st, warp * 16, n_rows, q_pos0);
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+
+    cp_async_wait<1>();
+    __syncthreads();
+    uint32_t qf[KSTEPS][4];
+    load_q_frags(q_tile + warp * 16 * ROW_BYTES, qf);
+    const bool warp_live = warp * 16 < n_rows;
+    const int warp_last_pos = q_pos0 + min(n_rows - 1, warp * 16 + 15) / p.G;
+
+    for (int t = t_lo; t <= t_hi; ++t) {
+        const int stage = (t - t_lo) & 1;
+        uint8_t* k_tile = kv + stage * 2 * TILE_BYTES;
+        if (t < t_hi) load_kv_tile(p, bt, g, kv_len, (t + 1) * BN, kv + (stage ^ 1) * 2 * TILE_BYTES,
+                                   kv + (stage ^ 1) * 2 * TILE_BYTES + TILE_BYTES);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (warp_live && t * BN <= warp_last_pos) {
+            const int warp_first_pos = q_pos0 + (warp * 16) / p.G;
+            const bool need_mask = (t * BN + BN - 1 > warp_first_pos) ||
+                                   (p.window > 0 && t * BN < warp_last_pos - p.window + 1);
+            process_keys<BN>(qf, k_tile, k_tile + TILE_BYTES, 0, t * BN, need_mask, p.scale_log2, st, o);
+        }
+        __syncthreads();
+    }
+    // normalise and store
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float l = st.l[h];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = warp * 16 + (lane >> 2) + 8 * h;
+        if (row >= n_rows) continue;
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int tok = row / p.G, hg = row - tok * p.G;
+        bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok0 + tok) * p.nh + g * p.G + hg) * HD + 2 * (lane & 3);
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j)
+            *reinterpret_cast<__nv_bfloat162*>(dst + j * 8) =
+                __floats2bfloat162_rn(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// work item: (request, slice, number of slices, item index for the partial buffers)
+__global__ void __launch_bounds__(THREADS)
+attn_keys_kernel(Params p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint8_t* q_tile = smem;                       // 16 rows
+    uint8_t* kv = smem + 16 * ROW_BYTES;          // [2 stages][K, V]
+    const int4 w = reinterpret_cast<const int4*>(p.work)[blockIdx.x];
+    const int r = w.x, slice = w.y, n_slices = w.z, item = w.w, g = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_len = p.cu_q[r + 1] - p.cu_q[r];
+    const int kv_len = p.kv_len[r];
+    const int n_rows = q_len * p.G;               // <= 16
+    const int q_pos0 = p.q_start[r];
+    const int* bt = p.block_table + (size_t)r * p.max_blocks;
+
+    const int last_pos = q_pos0 + q_len - 1;
+    const int first_key = p.window > 0 ? max(0, q_pos0 - p.window + 1) : 0;
+    const int t_first = first_key / BN, t_end = last_pos / BN + 1;
+    const int per = (t_end - t_first + n_slices - 1) / n_slices;
+    const int t_lo = t_first + slice * per, t_hi = min(t_end, t_lo + per) - 1;   // inclusive; may be empty
+
+    RowState st;
+    init_rows(p, st, 0, n_rows, q_pos0);
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+
+    if (t_lo <= t_hi) {
+        load_q_rows(p, p.cu_q[r], g, 0, n_rows, q_tile, 16);
+        cp_async_commit();
+        load_kv_tile(p, bt, g, kv_len, t_lo * BN, kv, kv + TILE_BYTES);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        uint32_t qf[KSTEPS][4];
+        load_q_frags(q_tile, qf);
+        for (int t = t_lo; t <= t_hi; ++t) {
+            const int stage = (t - t_lo) & 1;
+            uint8_t* k_tile = kv + stage * 2 * TILE_BYTES;
+            if (t < t_hi) load_kv_tile(p, bt, g, kv_len, (t + 1) * BN, kv + (stage ^ 1) * 2 * TILE_BYTES,
+                                       kv + (stage ^ 1) * 2 * TILE_BYTES + TILE_BYTES);
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncthreads();
+            const int k_off = warp * 16;
+            if (t * BN + k_off <= last_pos) {
+                const bool need_mask = (t * BN + BN - 1 > q_pos0) || (p.window > 0 && t * BN < last_pos - p.window + 1);
+                process_keys<16>(qf, k_tile, k_tile + TILE_BYTES, k_off, t * BN, need_mask, p.scale_log2, st, o);
+            }
+            __syncthreads();
+        }
+    }
+    // merge the four warps (each saw a quarter of every tile's keys) through shared memory
+    float* ms = reinterpret_cast<float*>(smem);            // [4][16]
+    float* ls = ms + NWARPS * 16;                          // [4][16]
+    float* os = ls + NWARPS * 16;                          // [4][16][HD]
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float l = st.l[h];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = (lane >> 2) + 8 * h;
+        if ((lane & 3) == 0) { ms[warp * 16 + row] = st.m[h]; ls[warp * 16 + row] = l; }
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) {
+            float* d = os + ((size_t)(warp * 16 + row)) * HD + j * 8 + 2 * (lane & 3);
+            d[0] = o[j][2 * h]; d[1] = o[j][2 * h + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_rows * HD; idx += THREADS) {
+        const int row = idx / HD, c = idx - row * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int wv = 0; wv < NWARPS; ++wv) M = fmaxf(M, ms[wv * 16 + row]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < NWARPS; ++wv) {
+            const float mw = ms[wv * 16 + row];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            acc += os[((size_t)(wv * 16 + row)) * HD + c] * f;
+            L += ls[wv * 16 + row] * f;
+        }
+        const int tok = row / p.G, hg = row - tok * p.G;
+        if (n_slices == 1) {
+            p.out[((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + c] =
+                __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            // `item` counts the slices of all earlier items, so every (item, kv head, slice) has its own slot
+            const size_t pr = ((size_t)item * p.nkv + (size_t)g * n_slices + slice) * 16 + row;
+            p.part_o[pr * HD + c] = acc;
+            if (c == 0) { p.part_ml[pr * 2] = M; p.part_ml[pr * 2 + 1] = L; }
+        }
+    }
+}
+
+// sums the slices of every sliced item: grid (sliced items, nkv)
+__global__ void __launch_bounds__(THREADS)
+attn_merge_kernel(Params p, const int* merge_items) {
+    const int4 w = reinterpret_cast<const int4*>(merge_items)[blockIdx.x];
+    const int r = w.x, n_slices = w.z, item = w.w, g = blockIdx.y;
+    const int n_rows = (p.cu_q[r + 1] - p.cu_q[r]) * p.G;
+    for (int idx = threadIdx.x; idx < n_rows * HD; idx += THREADS) {
+        const int row = idx / HD, c = idx - row * HD;
+        const size_t base = ((size_t)item * p.nkv + (size_t)g * n_slices) * 16 + row;
+        float M = -INFINITY;
+        for (int s = 0; s < n_slices; ++s) M = fmaxf(M, p.part_ml[(base + (size_t)s * 16) * 2]);
+        float acc = 0.f, L = 0.f;
+        for (int s = 0; s < n_slices; ++s) {
+            const size_t pr = base + (size_t)s * 16;
+            const float ms = p.part_ml[pr * 2];
+            const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            acc += p.part_o[pr * HD + c] * f;
+            L += p.part_ml[pr * 2 + 1] * f;
+        }
+        const int tok = row / p.G, hg = row - tok * p.G;
+        p.out[((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+}
+
+constexpr int SMEM_ROWS = (BN + 4 * BN) * ROW_BYTES;     // q tile of 64 rows + 2 stages of K and V
+constexpr int SMEM_KEYS_LOOP = (16 + 4 * BN) * ROW_BYTES;
+constexpr int SMEM_KEYS_MERGE = (2 * NWARPS * 16 + NWARPS * 16 * HD) * 4;
+constexpr int SMEM_KEYS = SMEM_KEYS_LOOP > SMEM_KEYS_MERGE ? SMEM_KEYS_LOOP : SMEM_KEYS_MERGE;
+
+}  // namespace
+
+BW_EXPORT int bw_attention_head_dim() { return HD; }
+
+// rows_work: n_rows_items int4 (request, first token, 0, 0) for segments of more than 16 stacked rows.
+// keys_work: n_keys_items int4 (request, slice, slices, item) for the others; merge_work: one int4 per
+// item that has more than one slice.  part_o / part_ml: float32 scratch for
+// [items, nkv, slices, 16, HD] and [.., 2].  window <= 0: all keys.
+BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
+                               const int* q_start, const int* kv_len, const int* block_table, int max_blocks,
+                               const int* rows_work, int n_rows_items, const int* keys_work, int n_keys_items,
+                               const int* merge_work, int n_merge_items, float* part_o, float* part_ml, int nh,
+                               int nkv, int page_size, int num_pages, int window, float scale, void* stream) {
+    if (nkv <= 0 || nh % nkv != 0) return BW_ERR_BAD_ARG;
+    const int G = nh / nkv;
+    if (G > 16) return BW_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ROWS);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_KEYS);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    Params p;
+    p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages; p.out = (bf16*)out;
+    p.cu_q = cu_q; p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
+    p.part_o = part_o; p.part_ml = part_ml;
+    p.max_blocks = max_blocks; p.nh = nh; p.nkv = nkv; p.G = G; p.page_size = page_size; p.num_pages = num_pages;
+    p.window = window > 0 ? window : 0;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    if (n_rows_items > 0) {
+        p.work = rows_work;
+        attn_rows_kernel<<<dim3(n_rows_items, nkv), THREADS, SMEM_ROWS, s>>>(p, 64 / G);
+        BW_LAUNCH_CHECK();
+    }
+    if (n_keys_items > 0) {
+        p.work = keys_work;
+        attn_keys_kernel<<<dim3(n_keys_items, nkv), THREADS, SMEM_KEYS, s>>>(p);
+        BW_LAUNCH_CHECK();
+        if (n_merge_items > 0) {
+            attn_merge_kernel<<<dim3(n_merge_items, nkv), THREADS, 0, s>>>(p, merge_work);
+            BW_LAUNCH_CHECK();
+        }
+    }
+    return 0;
+}

@@ -42,6 +42,7 @@ class StepBatch:
     h_kv_len: List[int] = field(default_factory=list)
     h_slots: List[int] = field(default_factory=list)
     rids: List[object] = field(default_factory=list)
+    static_bound: Optional[int] = None  # set for graph replay: kernels size grids for this many keys
     extras: Dict[str, object] = field(default_factory=dict)  # per-step data kernels derive lazily
 
     @property
@@ -80,9 +81,10 @@ class BatchBuilder:
         return buf
 
     def build(self, segments, logit_rows: Sequence[int], block_rows: Dict[int, List[List[int]]],
-              min_blocks: int = 0) -> StepBatch:
+              min_blocks: int = 0, into: Optional[torch.Tensor] = None) -> StepBatch:
         """``segments``: list of (rid, tokens, q_start, kv_len, slot).  ``block_rows``:
-        group -> one block-table row (list of page ids) per segment."""
+        group -> one block-table row (list of page ids) per segment.  ``into``: a device
+        buffer of exactly this batch's size to overwrite (fixed addresses for a CUDA graph)."""
         R = len(segments)
         T = sum(len(s[1]) for s in segments)
         widths = {g: max([min_blocks, 1] + [len(r) for r in rows]) for g, rows in block_rows.items()}
@@ -122,7 +124,12 @@ class BatchBuilder:
             view[:] = -1
             for r, row in enumerate(rows):
                 view[r, :len(row)] = row
-        dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        if into is not None:
+            if into.numel() != total:
+                raise ValueError(f"static batch buffer holds {into.numel()} words, this batch needs {total}")
+            dev = into
+        else:
+            dev = torch.empty(total, dtype=torch.int32, device=self.device)
         dev.copy_(host[:total], non_blocking=True)
         if self.device.type == "cuda":
             ev = self._events[self._slot] or torch.cuda.Event()

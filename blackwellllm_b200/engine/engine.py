@@ -48,6 +48,9 @@ class EngineOptions:
     kv_fraction: float = 0.6         # of the memory free after the weights, if neither is given
     max_requests: int = 64
     max_batch_tokens: int = 8192
+    max_context: Optional[int] = None  # longest request; None: what the pool holds
+    cuda_graphs: bool = True         # replay decode-only steps from a CUDA graph per batch size
+    max_graph_batch: int = 256
     device: str = "cuda:0"
 
 
@@ -70,6 +73,9 @@ class Engine:
         self.cache = CacheManager(requests, options.page_size, num_pages, options.max_requests,
                                   dtype=self.dtype, device=self.device)
         self._builder = BatchBuilder(self.device)
+        self._graphs: Dict[int, dict] = {}
+        longest = options.max_context or num_pages * options.page_size
+        self._graph_width = -(-longest // options.page_size)
         self.steps_run = 0
         self.tokens_run = 0
         del paged
@@ -150,7 +156,7 @@ class Engine:
         return self.cache.has(rid)
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: Sequence[StepEntry]) -> StepBatch:
+    def prepare(self, entries: Sequence[StepEntry], min_blocks: int = 0, into=None) -> StepBatch:
         """Checks the entries, reserves pages for all their tokens (all or nothing)
         and uploads the batch."""
         V = self.config.vocab_size
@@ -197,18 +203,70 @@ class Engine:
             rows.extend(t0 + int(w) for w in e.want)
             t0 += len(e.tokens)
         block_rows = {g: [self.cache.block_table(e.rid, g) for e in entries] for g in range(n_groups)}
-        return self._builder.build(segments, rows, block_rows)
+        return self._builder.build(segments, rows, block_rows, min_blocks=min_blocks, into=into)
+
+    # A decode-only step (one token and one wanted place per request) has the same
+    # shapes every time: its kernels are captured once per batch size in a CUDA graph
+    # and replayed.  Everything that changes from step to step (tokens, positions,
+    # block tables, lengths) lives in one device buffer at a fixed address that is
+    # overwritten before each replay.
+    def _graph_key(self, entries: Sequence[StepEntry]):
+        if not self.options.cuda_graphs or len(entries) > self.options.max_graph_batch:
+            return None
+        for e in entries:
+            if len(e.tokens) != 1 or list(e.want) != [0]:
+                return None
+        return len(entries)
+
+    def _step_graph(self, entries: Sequence[StepEntry], R: int) -> torch.Tensor:
+        width = self._graph_width
+        slot = self._graphs.get(R)
+        if slot is None:
+            n_groups = len(self.cache.groups)
+            total = 3 * R + (R + 1) + 3 * R + R + n_groups * R * width
+            slot = {"buf": torch.zeros(total, dtype=torch.int32, device=self.device), "graph": None,
+                    "logits": None, "kernels": 0}
+            self._graphs[R] = slot
+        batch = self.prepare(entries, min_blocks=width, into=slot["buf"])
+        if any(t.shape[1] != width for t in batch.block_tables.values()):
+            raise EngineError("a request outgrew max_context: its block table no longer fits the graph")
+        batch.static_bound = width * self.cache.page_size
+        if slot["graph"] is None:
+            from ..kernels import ops
+            self.model.forward(batch, self.cache.views)           # warm-up: builds kernels, scratch
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches
+            with torch.cuda.graph(graph):
+                slot["logits"] = self.model.forward(batch, self.cache.views)
+            slot["kernels"] = ops.launches - before
+            slot["graph"] = graph
+            slot["batch"] = batch   # keeps the per-step tensors that the captured kernels read alive
+        slot["graph"].replay()
+        return slot["logits"]
+
+    def graph_kernel_count(self, batch_size: int) -> int:
+        """Launcher calls captured in the decode graph of this batch size (0: none yet)."""
+        slot = self._graphs.get(batch_size)
+        return slot["kernels"] if slot else 0
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one batch; returns float32 logits [wanted, vocab] on the device, in the
-        order of the entries and of each entry's ``want``."""
+        order of the entries and of each entry's ``want``.  The result of a graph
+        replay is overwritten by the next step of the same batch size."""
         if not entries:
             return torch.empty((0, self.config.vocab_size), dtype=torch.float32, device=self.device)
         with torch.cuda.device(self.device):
-            batch = self.prepare(entries)
-            logits = self.model.forward(batch, self.cache.views)
+            R = self._graph_key(entries)
+            if R is not None:
+                logits = self._step_graph(entries, R)
+                T = R
+            else:
+                batch = self.prepare(entries)
+                logits = self.model.forward(batch, self.cache.views)
+                T = batch.T
         for e in entries:
             self.cache.release_passed(e.rid)
         self.steps_run += 1
-        self.tokens_run += batch.T
+        self.tokens_run += T
         return logits

@@ -57,7 +57,7 @@ class BlackwellEngine:
                  config: Optional[Mapping[str, object]] = None, random_seed: int = 0, random_std: float = 0.02,
                  dtype: str = "bfloat16", page_size: int = 16, num_pages: Optional[int] = None,
                  max_batch_tokens: int = 2048, chunk: Optional[int] = None, kv_fraction: Optional[float] = None,
-                 seed: int = 0, device: str = "cuda:0"):
+                 seed: int = 0, device: str = "cuda:0", cuda_graphs: bool = True):
         """``model``: a folder with config.json and model.safetensors.  Or ``config``
         (the config.json object) for random weights from ``random_seed``.  The cache
         holds ``max_batch_size`` sequences of ``max_context_length`` tokens unless
@@ -70,7 +70,8 @@ class BlackwellEngine:
             num_pages = rq.max_batch_size * -(-rq.max_context_length // page_size)
         opts = EngineOptions(dtype=dtype, page_size=page_size, num_pages=num_pages,
                              kv_fraction=kv_fraction or 0.6, max_requests=max(rq.max_batch_size, 1),
-                             max_batch_tokens=max(max_batch_tokens, rq.max_batch_size), device=device)
+                             max_batch_tokens=max(max_batch_tokens, rq.max_batch_size), device=device,
+                             max_context=rq.max_context_length, cuda_graphs=cuda_graphs)
         if (model is None) == (config is None):
             raise EngineError("give either a model folder or a config for random weights")
         if model is not None:

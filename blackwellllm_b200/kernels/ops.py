@@ -22,8 +22,13 @@ class KernelError(RuntimeError):
     pass
 
 
+launches = 0  # launcher calls that succeeded since import (each is one or two kernels)
+
+
 def _check(code: int, what: str) -> None:
+    global launches
     if code == 0:
+        launches += 1
         return
     if code == -1:
         raise KernelError(f"{what}: bad argument")
@@ -306,6 +311,81 @@ def check_attention_supported(dtype: torch.dtype, head_dim: int) -> None:
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
                     block_table: torch.Tensor, nh: int, window: Optional[int], scale: float) -> torch.Tensor:
     """Causal attention of the batch's tokens over the paged cache (which already
-    holds this step's keys and values)."""
-    return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
-                          window, scale)
+    holds this step's keys and values).  float32: the CUDA-core kernel; bfloat16:
+    the tensor-core kernel built for this head size."""
+    if q.dtype == torch.float32:
+        return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
+                              window, scale)
+    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale)
+
+
+_ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                   c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+_TARGET_CTAS = 148 * 4
+
+
+def attention_work(batch, G: int, nkv: int, window: Optional[int]):
+    """Work lists of the tensor-core attention for this batch and group size, made
+    once per step and shared by all layers: segments of more than 16 stacked rows
+    (tokens x heads of a group) are cut into 64-row tiles; the others (decode tokens)
+    are cut into key slices so that the GPU is filled.  With ``batch.static_bound``
+    (graph replay) the number of slices depends on that bound, not on the lengths."""
+    key = ("attn_work", G, nkv, window)
+    cached = batch.extras.get(key)
+    if cached is not None:
+        return cached
+    tpt = 64 // G
+    rows_items, keys_items, merge_items = [], [], []
+    small = [r for r in range(batch.R) if batch.h_q_len[r] * G <= 16]
+    total_slices = 0
+    for r in range(batch.R):
+        q_len = batch.h_q_len[r]
+        if q_len * G > 16:
+            rows_items += [(r, t0, 0, 0) for t0 in range(0, q_len, tpt)]
+            continue
+        span = batch.static_bound or batch.h_kv_len[r]
+        if window:
+            span = min(span, window + q_len)
+        tiles = -(-span // 64)
+        want = -(-_TARGET_CTAS // max(1, len(small) * nkv))
+        n = max(1, min(want, tiles // 2, 64))
+        keys_items += [(r, s, n, total_slices) for s in range(n)]
+        if n > 1:
+            merge_items.append((r, 0, n, total_slices))
+        total_slices += n
+    dev = batch.token_ids.device
+
+    def up(items):
+        if not items:
+            return None
+        return torch.tensor(items, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+
+    work = (up(rows_items), len(rows_items), up(keys_items), len(keys_items), up(merge_items),
+            len(merge_items), total_slices if merge_items else 0)
+    batch.extras[key] = work
+    return work
+
+
+def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_table: torch.Tensor,
+                  nh: int, window: Optional[int], scale: float) -> torch.Tensor:
+    _dev(q, "q", torch.bfloat16); _dev(k_pages, "k_pages", torch.bfloat16); _dev(v_pages, "v_pages", torch.bfloat16)
+    _dev(block_table, "block_table", torch.int32)
+    num_pages, nkv, page_size, hd = k_pages.shape
+    check_attention_supported(torch.bfloat16, hd)
+    if q.shape[1] != nh * hd or nh % nkv:
+        raise KernelError("attention: q must be [T, nh * head_dim] with nh a multiple of the kv heads")
+    G = nh // nkv
+    if G > 16:
+        raise KernelError(f"attention: {G} query heads per kv head exceed the kernel's limit of 16")
+    rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices = attention_work(batch, G, nkv, window)
+    out = torch.empty_like(q)
+    part_o = part_ml = None
+    if n_merge:
+        part_o = torch.empty((slices * nkv * 16, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((slices * nkv * 16, 2), dtype=torch.float32, device=q.device)
+    fn = _fn("attention_mma", "bw_attention_mma", _ATTN_MMA_ARGS, macros={"HEAD_DIM": hd})
+    _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
+              _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, _ptr(keys_w),
+              n_keys, _ptr(merge_w), n_merge, _ptr(part_o), _ptr(part_ml), nh, nkv, page_size, num_pages,
+              int(window or 0), float(scale), _stream()), "attention_mma")
+    return out

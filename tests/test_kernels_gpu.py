@@ -151,3 +151,153 @@ def test_swiglu(ops, I, dt):
     ref = plain_swiglu(gu[:, :I].double(), gu[:, I:].double())
     tol = 2e-6 if dt == torch.float32 else 2 ** -8
     assert float((out.double() - ref).abs().max()) <= tol * float(ref.abs().max())
+
+
+# ------------------------------------------------------------------ attention over pages
+
+class FakeBatch:
+    """The fields of a step's batch that the attention kernels read."""
+
+    def __init__(self, q_lens, kv_lens, static_bound=None):
+        self.R = len(q_lens)
+        self.h_q_len, self.h_kv_len = list(q_lens), list(kv_lens)
+        self.h_q_start = [k - q for q, k in zip(q_lens, kv_lens)]
+        cu = [0]
+        for q in q_lens:
+            cu.append(cu[-1] + q)
+        self.T = cu[-1]
+        i32 = dict(dtype=torch.int32, device=DEV)
+        self.cu_q = torch.tensor(cu, **i32)
+        self.q_start = torch.tensor(self.h_q_start, **i32)
+        self.kv_len = torch.tensor(kv_lens, **i32)
+        self.positions = torch.tensor([s + i for s, q in zip(self.h_q_start, q_lens) for i in range(q)], **i32)
+        self.req_of_token = torch.tensor([r for r, q in enumerate(q_lens) for _ in range(q)], **i32)
+        self.token_ids = self.positions
+        self.static_bound = static_bound
+        self.extras = {}
+
+
+def paged_case(q_lens, kv_lens, nh, nkv, hd, page, dtype, seed=0, spike=None):
+    """Random q/k/v per request, keys and values scattered over shuffled pages (with
+    unused pages full of NaN).  Returns what the kernels need and the plain result."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(q_lens)
+    blocks = [-(-k // page) for k in kv_lens]
+    num_pages = sum(blocks) + 5
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    k_pages = torch.full((num_pages, nkv, page, hd), float("nan"))
+    v_pages = torch.full((num_pages, nkv, page, hd), float("nan"))
+    width = max(blocks) + 2
+    table = torch.full((R, width), -1, dtype=torch.int32)
+    qs, refs = [], []
+    for r in range(R):
+        L, ql = kv_lens[r], q_lens[r]
+        k = torch.randn(L, nkv, hd, generator=g).to(dtype).float()
+        v = torch.randn(L, nkv, hd, generator=g).to(dtype).float()
+        q = torch.randn(L, nh, hd, generator=g).to(dtype).float()
+        if spike is not None:
+            spike(r, q, k, v)
+            q, k, v = q.to(dtype).float(), k.to(dtype).float(), v.to(dtype).float()
+        ids = [perm.pop() for _ in range(blocks[r])]
+        table[r, :blocks[r]] = torch.tensor(ids, dtype=torch.int32)
+        for b, pid in enumerate(ids):
+            n = min(page, L - b * page)
+            k_pages[pid, :, :n] = k[b * page: b * page + n].transpose(0, 1)
+            v_pages[pid, :, :n] = v[b * page: b * page + n].transpose(0, 1)
+            # the rest of a request's last page keeps NaN: it must never be read into a result
+        qs.append(q[L - ql:])
+        refs.append((q, k, v, L - ql))
+    return (torch.cat(qs).reshape(-1, nh * hd).to(dtype).to(DEV), k_pages.to(dtype).to(DEV),
+            v_pages.to(dtype).to(DEV), table.to(DEV), refs)
+
+
+def plain_rows(refs, window, nh, hd):
+    outs = []
+    for q, k, v, start in refs:
+        o = plain_attention(q.double(), k.double(), v.double(), window=window)
+        outs.append(o[start:].reshape(-1, nh * hd))
+    return torch.cat(outs)
+
+
+def run_attention(ops, dtype, q, kp, vp, table, batch, nh, window, scale):
+    if dtype == torch.float32:
+        return ops.attention_simt(q, kp, vp, batch.positions, batch.req_of_token, table, nh, window, scale)
+    return ops.attention_mma(q, kp, vp, batch, table, nh, window, scale)
+
+
+ATT_TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 16), (3, 1, 32, 8), (8, 8, 64, 16), (32, 8, 128, 16),
+                                            (14, 2, 48, 4), (6, 2, 256, 32), (5, 5, 80, 24)])
+def test_attention_mixed_batch(ops, dtype, nh, nkv, hd, page):
+    # prompt portions (one from position 0, one continuing), decode tokens, a two-token portion
+    q_lens = [70, 1, 33, 2, 1, 130]
+    kv_lens = [70, 200, 97, 64, 1, 400]
+    q, kp, vp, table, refs = paged_case(q_lens, kv_lens, nh, nkv, hd, page, dtype, seed=hd)
+    batch = FakeBatch(q_lens, kv_lens)
+    out = run_attention(ops, dtype, q, kp, vp, table, batch, nh, None, hd ** -0.5)
+    ref = plain_rows(refs, None, nh, hd)
+    assert not torch.isnan(out).any()
+    err = float((out.double().cpu() - ref).abs().max())
+    assert err <= ATT_TOL[dtype] * float(ref.abs().max()), err
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [1, 7, 64, 100])
+def test_attention_window(ops, dtype, window):
+    nh, nkv, hd, page = 6, 2, 32, 8
+    q_lens, kv_lens = [90, 1, 1, 3], [90, 300, 64, 131]
+    q, kp, vp, table, refs = paged_case(q_lens, kv_lens, nh, nkv, hd, page, dtype, seed=window)
+    # pages that every query's window has passed are gone from the block table
+    for r, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        gone = max(0, (kl - ql) - window + 1) // page
+        table[r, :gone] = -1
+    batch = FakeBatch(q_lens, kv_lens)
+    out = run_attention(ops, dtype, q, kp, vp, table, batch, nh, window, hd ** -0.5)
+    ref = plain_rows(refs, window, nh, hd)
+    assert not torch.isnan(out).any()
+    assert float((out.double().cpu() - ref).abs().max()) <= ATT_TOL[dtype] * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_far_key_and_window_edge(ops, dtype):
+    """One key far back gets a score that dwarfs all others: the output must be its
+    value.  With a window that ends one key after it, it must not be seen at all."""
+    nh, nkv, hd, page = 4, 2, 64, 16
+    L, far = 700, 3
+
+    def spike(r, q, k, v):
+        k[far] = 0
+        k[far, :, 0] = 8.0
+        q[-1] = 0
+        q[-1, :, 0] = 8.0 * hd ** 0.5
+        v[far] = 5.0
+
+    for q_len in (1, 40):
+        q, kp, vp, table, refs = paged_case([q_len], [L], nh, nkv, hd, page, dtype, seed=1, spike=spike)
+        batch = FakeBatch([q_len], [L])
+        out = run_attention(ops, dtype, q, kp, vp, table, batch, nh, None, hd ** -0.5)
+        assert float((out[-1].float() - 5.0).abs().max()) < 0.05          # the far key wins
+        w_in, w_out = L - far, L - far - 1                                 # window edge: in, then just out
+        o_in = run_attention(ops, dtype, q, kp, vp, table, FakeBatch([q_len], [L]), nh, w_in, hd ** -0.5)
+        o_out = run_attention(ops, dtype, q, kp, vp, table, FakeBatch([q_len], [L]), nh, w_out, hd ** -0.5)
+        assert float((o_in[-1].float() - 5.0).abs().max()) < 0.05
+        assert float(o_out[-1].float().abs().max()) < 4.0
+        ref = plain_rows(refs, w_out, nh, hd)
+        assert float((o_out.double().cpu() - ref).abs().max()) <= ATT_TOL[dtype] * float(ref.abs().max())
+
+
+def test_attention_decode_slices_and_static_bound(ops):
+    """Long decode rows are cut into key slices; a graph-style static bound changes
+    the number of slices but not the result beyond rounding."""
+    nh, nkv, hd, page = 8, 2, 128, 16
+    q_lens, kv_lens = [1, 1, 2], [3000, 17, 1025]
+    q, kp, vp, table, refs = paged_case(q_lens, kv_lens, nh, nkv, hd, page, torch.bfloat16, seed=5)
+    ref = plain_rows(refs, None, nh, hd)
+    a = ops.attention_mma(q, kp, vp, FakeBatch(q_lens, kv_lens), table, nh, None, hd ** -0.5)
+    b = ops.attention_mma(q, kp, vp, FakeBatch(q_lens, kv_lens, static_bound=8192), table, nh, None, hd ** -0.5)
+    for out in (a, b):
+        assert float((out.double().cpu() - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+    assert float((a.float() - b.float()).abs().max()) <= 2e-2 * float(ref.abs().max())
