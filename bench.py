@@ -105,6 +105,8 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--points", default="1,64", help="other decode batch sizes to report")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run one part only (for profiling); the JSON line then lacks the other part")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -145,7 +147,7 @@ def main():
     T = args.prefill_tokens
     prompt = torch.randint(0, V, (T,), generator=gen).tolist()
     pre_ms = []
-    for it in range(3):
+    for it in range(3 if args.only != "decode" else 0):
         s, e = ev(), ev()
         torch.cuda.synchronize()
         s.record()
@@ -154,7 +156,7 @@ def main():
         torch.cuda.synchronize()
         pre_ms.append(s.elapsed_time(e))
         eng.end_request("prefill")
-    prefill_ms = min(pre_ms[1:])
+    prefill_ms = min(pre_ms[1:]) if pre_ms else float("nan")
     nh, hd = cfg["num_attention_heads"], cfg["head_dim"]
     prefill_flops = 2.0 * T * args.layers * per_layer + 2.0 * V * cfg["hidden_size"] \
         + args.layers * 4.0 * nh * hd * T * (T + 1) / 2
@@ -205,6 +207,9 @@ def main():
         return (time.perf_counter() - t0) * 1e3 / steps
 
     points = {}
+    if args.only == "prefill":
+        print(json.dumps({"prefill": prefill}))
+        return 0
     for B in sizes:
         if B == args.batch:
             continue

@@ -66,6 +66,18 @@ def _code(t: torch.Tensor, name: str) -> int:
 
 
 _sigs_done = set()
+_timings = None  # name -> [calls, milliseconds] while kernel timing is on
+
+
+def enable_timing(on: bool = True) -> None:
+    """Per-launcher CUDA-event timers (each call is synchronised: for profiling only)."""
+    global _timings
+    _timings = {} if on else None
+
+
+def timing_report() -> dict:
+    """{launcher: (calls, total ms)} since enable_timing(True)."""
+    return {k: tuple(v) for k, v in (_timings or {}).items()}
 
 
 def _fn(lib_name: str, fn_name: str, argtypes, macros=None, extra_flags=()):
@@ -76,7 +88,20 @@ def _fn(lib_name: str, fn_name: str, argtypes, macros=None, extra_flags=()):
         fn.argtypes = argtypes
         fn.restype = c_int
         _sigs_done.add(key)
-    return fn
+    if _timings is None:
+        return fn
+
+    def timed(*args):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        rc = fn(*args)
+        e.record()
+        e.synchronize()
+        rec = _timings.setdefault(fn_name, [0, 0.0])
+        rec[0] += 1
+        rec[1] += s.elapsed_time(e)
+        return rc
+    return timed
 
 
 # ------------------------------------------------------------------ elementwise
