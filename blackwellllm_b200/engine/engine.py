@@ -213,6 +213,8 @@ class Engine:
     def _graph_key(self, entries: Sequence[StepEntry]):
         if not self.options.cuda_graphs or len(entries) > self.options.max_graph_batch:
             return None
+        if not all(getattr(b.mixer, "graph_safe", True) for b in self.model.blocks):
+            return None  # a mixer that works on the host between kernels cannot be captured
         for e in entries:
             if len(e.tokens) != 1 or list(e.want) != [0]:
                 return None

@@ -90,6 +90,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    graph_safe = True  # False: forward() does host work between kernels; decode steps then run uncaptured
+
     def cache_request(self):
         return None
 

@@ -1,0 +1,34 @@
+"""Plain CPU twin of the sampler: the same rule as the kernel, written the slow way.
+
+The reference's rule (src/kernels/sampling.cu:128-210): temperature below 1e-5 is
+argmax; else softmax(logits / T), the tokens sorted by probability, the shortest
+prefix whose mass reaches top_p kept, and a uniform draw over the kept mass.  Here
+the draw walks the kept tokens in index order (the reference walks them in sorted
+order with an unseeded generator, so only the distribution is comparable), and
+tokens tied with the last kept one are kept too.
+"""
+import torch
+
+
+def plain_sample(logits: torch.Tensor, temperature: float, top_p: float, u: float):
+    """Returns (token, margin): margin is the distance of the draw from the nearest
+    edge of the chosen token's CDF interval, as a fraction of the kept mass."""
+    lg = logits.double()
+    if temperature < 1e-5:
+        m = lg.max()
+        return int((lg == m).nonzero()[0]), 1.0
+    e = torch.exp((lg - lg.max()) / temperature)
+    keep = torch.ones_like(e, dtype=torch.bool)
+    if top_p < 1.0:
+        srt, _ = torch.sort(e, descending=True)
+        cum = torch.cumsum(srt, 0)
+        k = int((cum >= top_p * e.sum()).nonzero()[0])
+        keep = e >= srt[k]
+    kept = torch.where(keep, e, torch.zeros_like(e))
+    cdf = torch.cumsum(kept, 0)
+    mass = float(cdf[-1])
+    goal = u * mass
+    idx = int((cdf > goal).nonzero()[0]) if bool((cdf > goal).any()) else int(keep.nonzero()[-1])
+    lo = float(cdf[idx] - kept[idx])
+    margin = min(goal - lo, float(cdf[idx]) - goal) / mass
+    return idx, margin

@@ -1,0 +1,210 @@
+"""The engine through its Python entry point, against the plain implementation:
+greedy generation, long decoding, the first tokens of a sequence, sampling with
+temperature and nucleus against the CPU twin, the position-addressed calls, and
+what happens when pages run out."""
+import pytest
+import torch
+
+import tiny
+from plain_model import load_plain_weights, plain_greedy, plain_logits
+from plain_sampling import plain_sample
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = str(tmp_path_factory.mktemp("models"))
+    return {(n, d): tiny.make_folder(n, d, root) for n in tiny.CONFIGS for d in ("float32", "bfloat16")}
+
+
+def make(folder, dtype, ctx=512, batch=4, **kw):
+    from blackwellllm_b200 import BlackwellEngine, InferenceConfig
+    return BlackwellEngine(folder, InferenceConfig(max_context_length=ctx, max_batch_size=batch), dtype=dtype, **kw)
+
+
+def check_greedy_path(raw, W, prompt, tokens, dtype):
+    """float32: the plain greedy continuation, token for token.  bfloat16: every token
+    is the plain implementation's best or within the rounding bound of it."""
+    if dtype == "float32":
+        assert tokens == plain_greedy(raw, W, prompt, len(tokens))
+        return
+    seq = list(prompt)
+    for t in tokens:
+        lg = plain_logits(raw, W, seq)[-1]
+        assert float(lg.max() - lg[t]) <= tiny.TOL["bfloat16"] * float(lg.abs().max())
+        seq.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["llama", "qwen"])
+def test_greedy_generation_through_the_entry_point(folders, name, dtype):
+    from blackwellllm_b200 import SamplingParams
+    raw, _, page = tiny.CONFIGS[name]
+    folder = folders[(name, dtype)]
+    W = load_plain_weights(folder)
+    llm = make(folder, dtype, page_size=page)
+    prompts = [tiny.prompt(n, raw["vocab_size"], 40 + n) for n in (5, 17, 33)]
+    res = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=8))
+    for p, r in zip(prompts, res):
+        assert r.finish_reason == "limit" and len(r.token_ids) == 8 and r.prompt_token_ids == p
+        check_greedy_path(raw, W, p, r.token_ids, dtype)
+    assert llm.engine.cache.free_pages() == [g.num_pages for g in llm.engine.cache.groups]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(folders, dtype):
+    """A one-token prompt, then 150 tokens decoded one by one (graph replay), checked
+    against the plain implementation at every position."""
+    from blackwellllm_b200 import StepEntry
+    raw, _, page = tiny.CONFIGS["llama3"]
+    folder = folders[("llama3", dtype)]
+    W = load_plain_weights(folder)
+    llm = make(folder, dtype, page_size=page, ctx=256, batch=1)
+    ids = tiny.prompt(151, raw["vocab_size"], 9)
+    ref = plain_logits(raw, W, ids)
+    eng = llm.engine
+    worst = 0.0
+    for i, t in enumerate(ids):
+        lg = eng.step([StepEntry("a", [t], [0])])[0].double().cpu()
+        worst = max(worst, float((lg - ref[i]).abs().max()) / float(ref.abs().max()))
+    assert worst <= tiny.TOL[dtype], worst
+    assert eng.graph_kernel_count(1) > 0      # the decode steps ran from the captured graph
+
+
+def test_sampling_kernel_matches_the_cpu_twin():
+    from blackwellllm_b200.kernels import ops
+    from blackwellllm_b200.sampling.params import uniform
+    g = torch.Generator().manual_seed(0)
+    V = 1000
+    logits = (torch.randn(64, V, generator=g) * 3).to(DEV)
+    temps = [0.0, 0.3, 0.6, 1.0, 1.7] * 13
+    tops = [1.0, 0.9, 0.5, 0.99, 0.2, 1.0, 0.7] * 10
+    R = 64
+    t = torch.tensor(temps[:R], device=DEV)
+    p = torch.tensor(tops[:R], device=DEV)
+    us = [uniform(5, i) for i in range(R)]
+    u = torch.tensor(us, device=DEV)
+    got = ops.sample(logits, t, p, u).tolist()
+    checked = 0
+    for r in range(R):
+        want, margin = plain_sample(logits[r].cpu(), temps[r], tops[r], us[r])
+        if margin > 1e-4:   # a draw that close to a CDF edge may fall either way in float32
+            assert got[r] == want, (r, temps[r], tops[r])
+            checked += 1
+    assert checked >= 60
+    # greedy: lowest index wins a tie
+    tie = torch.zeros(2, 50, device=DEV)
+    tie[0, 7] = tie[0, 30] = 2.0
+    tie[1, 49] = 1.0
+    assert ops.sample(tie, None, None, None).tolist() == [7, 49]
+
+
+def test_sampling_distribution_and_nucleus():
+    from blackwellllm_b200.kernels import ops
+    probs = torch.tensor([0.5, 0.25, 0.15, 0.07, 0.03])
+    logits = probs.log().repeat(4000, 1).to(DEV)
+    u = torch.rand(4000, generator=torch.Generator().manual_seed(1)).to(DEV)
+    ones = torch.ones(4000, device=DEV)
+    full = ops.sample(logits, ones, ones, u)
+    freq = torch.bincount(full.long().cpu(), minlength=5).double() / 4000
+    assert float((freq - probs.double()).abs().max()) < 0.03
+    nucleus = ops.sample(logits, ones, ones * 0.8, u)   # 0.5 + 0.25 + 0.15 reach 0.8: three tokens stay
+    assert set(nucleus.tolist()) == {0, 1, 2}
+
+
+def test_temperature_generation_is_seeded_and_independent_of_the_batch(folders):
+    """Chunked prefill (chunk 12) mixed with decoding, temperature 1.0: the tokens
+    follow the CPU twin on the plain logits, and a request's tokens do not depend on
+    which other requests share its batches."""
+    from blackwellllm_b200 import SamplingParams
+    from blackwellllm_b200.sampling.params import uniform
+    raw, _, page = tiny.CONFIGS["qwen"]
+    folder = folders[("qwen", "float32")]
+    W = load_plain_weights(folder)
+    prompts = [tiny.prompt(n, raw["vocab_size"], 70 + n) for n in (1, 9, 40, 70)]
+    sp = SamplingParams(temperature=1.0, top_p=1.0, max_new_tokens=6)
+    llm = make(folder, "float32", page_size=page, chunk=12, max_batch_tokens=32, seed=2)
+    res = llm.generate(prompts, sp)
+    for rid, (p, r) in enumerate(zip(prompts, res)):
+        seq = list(p)
+        for i, t in enumerate(r.token_ids):
+            want, margin = plain_sample(plain_logits(raw, W, seq)[-1], 1.0, 1.0, uniform(2 * 1_000_003 + rid, i))
+            if margin > 1e-4:
+                assert t == want
+            seq.append(t)
+    alone = make(folder, "float32", page_size=page, seed=2)
+    solo = alone.generate([prompts[0]], sp)[0]          # request number 0 again, with no company
+    assert solo.token_ids == res[0].token_ids
+
+
+def test_position_addressed_calls(folders):
+    from blackwellllm_b200 import DecodeRequest, EngineError
+    raw, _, page = tiny.CONFIGS["llama"]
+    folder = folders[("llama", "float32")]
+    W = load_plain_weights(folder)
+    llm = make(folder, "float32", page_size=page)
+    p = tiny.prompt(20, raw["vocab_size"], 3)
+    want = plain_greedy(raw, W, p, 3)
+    nxt = llm.prefill(p, 0, 0.0, 1.0, seq_id=0)
+    got = [nxt]
+    for i in range(2):
+        nxt = llm.forward(nxt, len(p) + i, 0.0, 1.0, seq_id=0)
+        got.append(nxt)
+    assert got == want
+    # the per-token loop gives the same continuation as the chunked prefill
+    for i, t in enumerate(p):
+        last = llm.forward(t, i, 0.0, 1.0, seq_id=1)
+    assert last == want[0]
+    # re-decoding an earlier position rewinds; a gap is an error, not a fault
+    assert llm.forward(p[10], 10, 0.0, 1.0, seq_id=1) == plain_greedy(raw, W, p[:11], 1)[0]
+    with pytest.raises(EngineError, match="gap"):
+        llm.forward(1, 50, 0.0, 1.0, seq_id=1)
+    with pytest.raises(EngineError, match="twice"):
+        llm.forward_batch([DecodeRequest(0, 1, 22), DecodeRequest(0, 2, 22)])
+    # batched decode of distinct sequences equals the sequential calls
+    llm.rewind(0, len(p))
+    llm.prefill(p[:11], 0, 0.0, 1.0, seq_id=2)
+    both = llm.forward_batch([DecodeRequest(0, want[0], len(p)), DecodeRequest(2, 7, 11)])
+    assert both[0] == want[1] and both[1] == plain_greedy(raw, W, p[:11] + [7], 1)[0]
+    llm.release_sequence(0); llm.release_sequence(1); llm.release_sequence(2)
+    assert llm.engine.cache.free_pages() == [g.num_pages for g in llm.engine.cache.groups]
+
+
+def test_pages_run_out_preemption_reproduces_the_tokens(folders):
+    from blackwellllm_b200 import SamplingParams
+    raw, _, page = tiny.CONFIGS["llama"]
+    folder = folders[("llama", "float32")]
+    W = load_plain_weights(folder)
+    prompts = [tiny.prompt(30, raw["vocab_size"], 200 + i) for i in range(3)]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=40)
+    # 3 requests x 69 cached tokens need 15 pages of 16; the pool has 9
+    llm = make(folder, "float32", page_size=16, num_pages=9, ctx=512, batch=3)
+    res = llm.generate(prompts, sp)
+    assert llm.scheduler.stats.preemptions >= 1
+    for p, r in zip(prompts, res):
+        assert r.token_ids == plain_greedy(raw, W, p, 40)
+    assert llm.engine.cache.free_pages() == [9]
+    from blackwellllm_b200.engine.scheduler import RequestRefused
+    with pytest.raises(RequestRefused):
+        llm.add_request(tiny.prompt(120, raw["vocab_size"], 1), SamplingParams(max_new_tokens=100))
+
+
+def test_no_cpu_path_and_bad_tokens(folders):
+    from blackwellllm_b200 import Engine, EngineError, StepEntry
+    from blackwellllm_b200.kernels import ops
+    folder = folders[("llama", "float32")]
+    with pytest.raises(EngineError, match="CUDA"):
+        Engine.from_folder(folder, dtype="float32", device="cpu")
+    with pytest.raises(ops.KernelError, match="CUDA tensor"):
+        ops.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-5, torch.float32)
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=64)
+    with pytest.raises(EngineError, match="outside"):
+        eng.step([StepEntry("a", [256], [0])])
+    with pytest.raises(EngineError, match="wanted place"):
+        eng.step([StepEntry("a", [1, 2], [2])])
+    from blackwellllm_b200.cache.pages import OutOfPages
+    with pytest.raises(OutOfPages):
+        eng.step([StepEntry("a", [1] * 65, [])])
+    assert not eng.has_request("a") and eng.cache.free_pages() == [4]   # nothing was changed
