@@ -75,15 +75,36 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Gathers keys [key0, key0 + BN) of kv head g into a K and a V tile (padded rows).
 __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int g, int kv_len, int key0,
                                              uint8_t* k_tile, uint8_t* v_tile) {
-    for (int idx = threadIdx.x; idx < BN * CPR; idx += THREADS) {
-        const int row = idx / CPR, ch = idx - row * CPR;
-        const int kp = key0 + row;
-        bool valid = kp < kv_len;
-        int page = valid ? bt[kp / p.page_size] : -1;
-        valid = valid && page >= 0 && page < p.num_pages;
-        const size_t off = valid ? ((((size_t)page * p.nkv + g) * p.page_size + (kp % p.page_size)) * HD + ch * 8) : 0;
-        cp_async16(smem_u32(k_tile + row * ROW_BYTES + ch * 16), p.k_pages + off, valid);
-        cp_async16(smem_u32(v_tile + row * ROW_BYTES + ch * 16), p.v_pages + off, valid);
+    if constexpr (THREADS % CPR == 0) {
+        // each thread owns one 16-byte column and every (THREADS / CPR)-th row: the block index and
+        // the slot in the page advance by additions, the page id is looked up once per page
+        constexpr int RPP = THREADS / CPR;
+        const int ch = threadIdx.x % CPR;
+        int row = threadIdx.x / CPR;
+        int kp = key0 + row;
+        int blk = kp / p.page_size, slot = kp - blk * p.page_size;
+        int cur_blk = -1, page = -1;
+#pragma unroll 4
+        for (; row < BN; row += RPP, kp += RPP, slot += RPP) {
+            while (slot >= p.page_size) { slot -= p.page_size; ++blk; }
+            bool valid = kp < kv_len;
+            if (valid && blk != cur_blk) { page = bt[blk]; cur_blk = blk; }
+            valid = valid && page >= 0 && page < p.num_pages;
+            const size_t off = valid ? ((((size_t)page * p.nkv + g) * p.page_size + slot) * HD + ch * 8) : 0;
+            cp_async16(smem_u32(k_tile + row * ROW_BYTES + ch * 16), p.k_pages + off, valid);
+            cp_async16(smem_u32(v_tile + row * ROW_BYTES + ch * 16), p.v_pages + off, valid);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < BN * CPR; idx += THREADS) {
+            const int row = idx / CPR, ch = idx - row * CPR;
+            const int kp = key0 + row;
+            bool valid = kp < kv_len;
+            int page = valid ? bt[kp / p.page_size] : -1;
+            valid = valid && page >= 0 && page < p.num_pages;
+            const size_t off = valid ? ((((size_t)page * p.nkv + g) * p.page_size + (kp % p.page_size)) * HD + ch * 8) : 0;
+            cp_async16(smem_u32(k_tile + row * ROW_BYTES + ch * 16), p.k_pages + off, valid);
+            cp_async16(smem_u32(v_tile + row * ROW_BYTES + ch * 16), p.v_pages + off, valid);
+        }
     }
 }
 

@@ -40,6 +40,44 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict
         o[c] = bw::from_f32<OT>(xr[c] * r * bw::to_f32(w[c]));
 }
 
+// The same with 4 elements per access, for widths that are multiples of 4 (the sum runs over
+// the same per-thread strided order scaled by 4; rows stay independent of one another).
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<uint32_t*>(&a); r.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+template <typename WT, typename OT>
+__global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, const WT* __restrict__ w,
+                                    const int* __restrict__ rows, OT* __restrict__ out, int H, float eps) {
+    __shared__ float scratch[32];
+    const int i = blockIdx.x;
+    const int src = rows ? rows[i] : i;
+    const float* xr = x + (size_t)src * H;
+    OT* o = out + (size_t)i * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+        const float4 v = load4(xr + c);
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    ss = bw::block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+        const float4 v = load4(xr + c), g = load4(w + c);
+        store4(o + c, make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w));
+    }
+}
+
 // ---------------------------------------------------------------- SwiGLU
 // in: [T, 2I] with gate in columns [0, I) and up in [I, 2I); out: [T, I].
 template <typename IT, typename OT>
@@ -59,12 +97,26 @@ __global__ void swiglu_kernel(const IT* __restrict__ gu, OT* __restrict__ out, i
 // q_out: [T, nh * hd] rotated queries.  Rotated keys and raw values go to the
 // page of the token's position: pages are [num_pages, nkv, page_size, hd].
 // rotary_dim = 0 rotates nothing (a mixer without rotary encoding).
+// cos and sin of pos * inv_freq[j] for every token of the step: [T, rotary_dim] (cos, then sin).
+// All layers with the same rotary parameters share one table per step.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float* __restrict__ table, int rotary_dim, int T) {
+    const int half = rotary_dim >> 1;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * half) return;
+    const int t = idx / half, j = idx - t * half;
+    float s, c;
+    sincosf((float)positions[t] * inv_freq[j], &s, &c);
+    table[(size_t)t * rotary_dim + j] = c;
+    table[(size_t)t * rotary_dim + half + j] = s;
+}
+
 template <typename IT, typename OT>
 __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __restrict__ positions,
                                    const int* __restrict__ req_of_token,
                                    const int* __restrict__ block_table, int max_blocks,
-                                   const float* __restrict__ inv_freq, int rotary_dim,
-                                   OT* __restrict__ q_out, OT* __restrict__ k_pages,
+                                   const float* __restrict__ inv_freq, const float* __restrict__ table,
+                                   int rotary_dim, OT* __restrict__ q_out, OT* __restrict__ k_pages,
                                    OT* __restrict__ v_pages, int nh, int nkv, int hd,
                                    int page_size, int num_pages) {
     extern __shared__ float cs[];  // cos[rd/2], sin[rd/2]
@@ -72,10 +124,14 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
     const int pos = positions[t];
     const int half = rotary_dim >> 1;
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
-        const float a = (float)pos * inv_freq[j];
-        float s, c;
-        sincosf(a, &s, &c);
-        cs[j] = c; cs[half + j] = s;
+        if (table) {
+            cs[j] = table[(size_t)t * rotary_dim + j];
+            cs[half + j] = table[(size_t)t * rotary_dim + half + j];
+        } else {
+            float s, c;
+            sincosf((float)pos * inv_freq[j], &s, &c);
+            cs[j] = c; cs[half + j] = s;
+        }
     }
     __syncthreads();
     const int r = req_of_token[t];
@@ -130,8 +186,10 @@ BW_EXPORT int bw_rmsnorm(const float* x, const void* w, int w_type, const int* r
                          int out_type, int n_rows, int H, float eps, void* stream) {
     if (n_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-#define BW_RMS(WT, OT) rmsnorm_kernel<WT, OT><<<n_rows, threads, 0, s>>>(x, cp<WT>(w), rows, mp<OT>(out), H, eps)
+    const bool vec = H % 4 == 0 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    const int threads = vec ? (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
+#define BW_RMS(WT, OT) do { if (vec) rmsnorm_vec4_kernel<WT, OT><<<n_rows, threads, 0, s>>>(x, cp<WT>(w), rows, mp<OT>(out), H, eps); \
+        else rmsnorm_kernel<WT, OT><<<n_rows, threads, 0, s>>>(x, cp<WT>(w), rows, mp<OT>(out), H, eps); } while (0)
     if (w_type == BW_F32 && out_type == BW_F32) BW_RMS(float, float);
     else if (w_type == BW_F32 && out_type == BW_BF16) BW_RMS(float, bf16);
     else if (w_type == BW_BF16 && out_type == BW_F32) BW_RMS(bf16, float);
@@ -156,8 +214,19 @@ BW_EXPORT int bw_swiglu(const void* gu, int in_type, void* out, int out_type, in
     return 0;
 }
 
+BW_EXPORT int bw_rope_table(const int* positions, const float* inv_freq, float* table, int rotary_dim, int T,
+                            void* stream) {
+    if (T <= 0 || rotary_dim <= 0) return 0;
+    if (rotary_dim & 1) return BW_ERR_BAD_ARG;
+    const int total = T * (rotary_dim / 2);
+    rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, table, rotary_dim, T);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+// table: [T, rotary_dim] from bw_rope_table, or null to compute the angles here.
 BW_EXPORT int bw_rope_append(const void* qkv, int in_type, const int* positions, const int* req_of_token,
-                             const int* block_table, int max_blocks, const float* inv_freq,
+                             const int* block_table, int max_blocks, const float* inv_freq, const float* table,
                              int rotary_dim, void* q_out, void* k_pages, void* v_pages, int out_type,
                              int T, int nh, int nkv, int hd, int page_size, int num_pages, void* stream) {
     if (T <= 0) return 0;
@@ -166,7 +235,7 @@ BW_EXPORT int bw_rope_append(const void* qkv, int in_type, const int* positions,
     const int threads = 256;
     const size_t smem = (size_t)rotary_dim * sizeof(float);
 #define BW_RA(IT, OT) rope_append_kernel<IT, OT><<<T, threads, smem, s>>>(cp<IT>(qkv), positions, req_of_token, \
-        block_table, max_blocks, inv_freq, rotary_dim, mp<OT>(q_out), mp<OT>(k_pages), mp<OT>(v_pages), \
+        block_table, max_blocks, inv_freq, table, rotary_dim, mp<OT>(q_out), mp<OT>(k_pages), mp<OT>(v_pages), \
         nh, nkv, hd, page_size, num_pages)
     if (in_type == BW_F32 && out_type == BW_F32) BW_RA(float, float);
     else if (in_type == BW_F32 && out_type == BW_BF16) BW_RA(float, bf16);

@@ -40,11 +40,14 @@ struct Epilogue {
     int tokens, features;
 };
 
+// Wide tiles take the whole SM; narrow ones (few tokens: a weight stream bound by HBM) use 4
+// stages so that 2-3 CTAs share an SM and one CTA's start-up and epilogue overlap the others' loads.
 template <int BN> __host__ __device__ constexpr int stages_for() {
     constexpr int per = A_BYTES + BN * BK * 2;
     constexpr int s = SMEM_BUDGET / per;
-    return s > 8 ? 8 : s;
+    return BN <= 64 ? 4 : (s > 8 ? 8 : s);
 }
+constexpr int ctas_per_sm(int bn) { return bn <= 16 ? 3 : (bn <= 64 ? 2 : 1); }
 
 __device__ __forceinline__ void store_val(const Epilogue& ep, int token, int feature, float v) {
     if (ep.bias) v += ep.bias_type == BW_F32 ? ((const float*)ep.bias)[feature]
@@ -276,8 +279,8 @@ BW_EXPORT int bw_gemm_tc_plan(int M, int N, int K, long long workspace_elems, in
     int best = 1; double best_score = 0;
     for (int s = 1; s <= 8; ++s) {
         if (s > 1 && (kb_total / s < 8 || (long long)s * M * N > workspace_elems)) break;
-        const long long ctas = tiles * s;
-        const double wave = (double)ctas / ((double)ceil_div(ctas, 148) * 148);
+        const long long ctas = tiles * s, slots = 148LL * ctas_per_sm(b);
+        const double wave = (double)ctas / ((double)ceil_div(ctas, slots) * slots);
         const double extra = s > 1 ? 4.0 * s * M / (double)K : 0.0;   // partial traffic relative to the weights
         const double score = wave / (1.0 + extra);
         if (score > best_score * 1.02) { best_score = score; best = s; }

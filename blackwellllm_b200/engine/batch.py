@@ -43,7 +43,11 @@ class StepBatch:
     h_slots: List[int] = field(default_factory=list)
     rids: List[object] = field(default_factory=list)
     static_bound: Optional[int] = None  # set for graph replay: kernels size grids for this many keys
-    extras: Dict[str, object] = field(default_factory=dict)  # per-step data kernels derive lazily
+    # Data that kernels derive once per step and share between layers.  `extras`: made on the
+    # device from this step's values (recomputed inside a captured graph at every replay);
+    # `static_extras`: made on the host from the batch's shape alone (kept across replays).
+    extras: Dict[object, object] = field(default_factory=dict)
+    static_extras: Dict[object, object] = field(default_factory=dict)
 
     @property
     def max_q_len(self) -> int:

@@ -237,6 +237,7 @@ class Engine:
             from ..kernels import ops
             self.model.forward(batch, self.cache.views)           # warm-up: builds kernels, scratch
             torch.cuda.synchronize(self.device)
+            batch.extras.clear()   # what depends on this step's values is recomputed inside the graph
             graph = torch.cuda.CUDAGraph()
             before = ops.launches
             with torch.cuda.graph(graph):

@@ -80,7 +80,7 @@ def timing_report() -> dict:
     return {k: tuple(v) for k, v in (_timings or {}).items()}
 
 
-def _fn(lib_name: str, fn_name: str, argtypes, macros=None, extra_flags=()):
+def _fn(lib_name: str, fn_name: str, argtypes, macros=None, extra_flags=(), tag=None):
     lib = load_library(lib_name, macros, extra_flags)
     fn = getattr(lib, fn_name)
     key = (id(lib), fn_name)
@@ -97,7 +97,7 @@ def _fn(lib_name: str, fn_name: str, argtypes, macros=None, extra_flags=()):
         rc = fn(*args)
         e.record()
         e.synchronize()
-        rec = _timings.setdefault(fn_name, [0, 0.0])
+        rec = _timings.setdefault(fn_name if tag is None else f"{fn_name} {tag}", [0, 0.0])
         rec[0] += 1
         rec[1] += s.elapsed_time(e)
         return rc
@@ -149,12 +149,24 @@ def swiglu(gu: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.T
     return out
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int) -> torch.Tensor:
+    """cos and sin of ``pos * inv_freq`` per token: float32 [T, rotary_dim] (cos, then sin)."""
+    _dev(positions, "positions", torch.int32); _dev(inv_freq, "inv_freq", torch.float32)
+    T = positions.numel()
+    table = torch.empty((T, rotary_dim), dtype=torch.float32, device=positions.device)
+    fn = _fn("elementwise", "bw_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(positions), _ptr(inv_freq), _ptr(table), rotary_dim, T, _stream()), "rope_table")
+    return table
+
+
 def rope_append(qkv: torch.Tensor, positions: torch.Tensor, req_of_token: torch.Tensor,
                 block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int,
                 k_pages: torch.Tensor, v_pages: torch.Tensor, nh: int, nkv: int, hd: int,
-                q_out: Optional[torch.Tensor] = None, append: bool = True) -> torch.Tensor:
+                q_out: Optional[torch.Tensor] = None, append: bool = True,
+                table: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rotates q and k heads of ``qkv`` [T, (nh+2nkv)*hd], returns q [T, nh*hd] in the
-    pages' dtype, and writes rotated k and raw v to pages [num_pages, nkv, page, hd]."""
+    pages' dtype, and writes rotated k and raw v to pages [num_pages, nkv, page, hd].
+    ``table``: the step's cos/sin table from :func:`rope_table` (else computed here)."""
     _dev(qkv, "qkv"); _dev(positions, "positions", torch.int32)
     _dev(req_of_token, "req_of_token", torch.int32); _dev(block_table, "block_table", torch.int32)
     _dev(k_pages, "k_pages"); _dev(v_pages, "v_pages", k_pages.dtype)
@@ -171,11 +183,15 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, req_of_token: torch.
     if q_out is None:
         q_out = torch.empty((T, nh * hd), dtype=k_pages.dtype, device=qkv.device)
     _dev(q_out, "q_out", k_pages.dtype)
+    if table is not None:
+        _dev(table, "table", torch.float32)
+        if tuple(table.shape) != (T, rotary_dim):
+            raise KernelError("rope_append: the cos/sin table must be [T, rotary_dim]")
     fn = _fn("elementwise", "bw_rope_append",
-             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(qkv), _code(qkv, "qkv"), _ptr(positions), _ptr(req_of_token), _ptr(block_table),
-              block_table.shape[1], _ptr(inv_freq), rotary_dim, _ptr(q_out), _ptr(k_pages), _ptr(v_pages),
+              block_table.shape[1], _ptr(inv_freq), _ptr(table), rotary_dim, _ptr(q_out), _ptr(k_pages), _ptr(v_pages),
               _code(k_pages, "pages"), T, nh, nkv, hd, page_size, num_pages if append else 0, _stream()),
            "rope_append")
     return q_out
@@ -312,7 +328,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         if bias.numel() != N:
             raise KernelError("gemm: bias must have N entries")
     ws = _workspace(x.device)
-    fn = _fn("gemm_tc", "bw_gemm_tc", _GEMM_TC_ARGS)
+    fn = _fn("gemm_tc", "bw_gemm_tc", _GEMM_TC_ARGS, tag=f"{M}x{N}x{K}" if _timings is not None else None)
     _check(fn(_ptr(x), _ptr(w), _ptr(bias), _code(bias, "bias") if bias is not None else 0, _ptr(out),
               _code(out, "out"), M, N, K, x.stride(0), out.stride(0), int(accumulate), _ptr(ws), ws.numel(),
               int(force_splits), _stream()), "gemm_tc")
@@ -349,19 +365,26 @@ _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_vo
 _TARGET_CTAS = 148 * 4
 
 
-def attention_work(batch, G: int, nkv: int, window: Optional[int]):
+def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128):
     """Work lists of the tensor-core attention for this batch and group size, made
     once per step and shared by all layers: segments of more than 16 stacked rows
     (tokens x heads of a group) are cut into 64-row tiles; the others (decode tokens)
     are cut into key slices so that the GPU is filled.  With ``batch.static_bound``
     (graph replay) the number of slices depends on that bound, not on the lengths."""
-    key = ("attn_work", G, nkv, window)
-    cached = batch.extras.get(key)
+    key = ("attn_work", G, nkv, window, hd)
+    cached = batch.static_extras.get(key)
     if cached is not None:
         return cached
     tpt = 64 // G
     rows_items, keys_items, merge_items = [], [], []
     small = [r for r in range(batch.R) if batch.h_q_len[r] * G <= 16]
+    # CTAs of the key-slice kernel that fit on the GPU at once (shared memory bound)
+    slots = 148 * max(1, min(8, (227 * 1024) // ((16 + 4 * 64) * (hd * 2 + 16) + 1024)))
+    heads = max(1, len(small) * nkv)
+    if heads <= slots:
+        want = slots // heads            # one full wave: all slices run side by side, no tail
+    else:
+        want = -(-4 * slots // heads)    # many short CTAs: at least four waves smooth the tail
     total_slices = 0
     for r in range(batch.R):
         q_len = batch.h_q_len[r]
@@ -372,7 +395,6 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int]):
         if window:
             span = min(span, window + q_len)
         tiles = -(-span // 64)
-        want = -(-_TARGET_CTAS // max(1, len(small) * nkv))
         n = max(1, min(want, tiles // 2, 64))
         keys_items += [(r, s, n, total_slices) for s in range(n)]
         if n > 1:
@@ -387,7 +409,7 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int]):
 
     work = (up(rows_items), len(rows_items), up(keys_items), len(keys_items), up(merge_items),
             len(merge_items), total_slices if merge_items else 0)
-    batch.extras[key] = work
+    batch.static_extras[key] = work
     return work
 
 
@@ -402,7 +424,7 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     G = nh // nkv
     if G > 16:
         raise KernelError(f"attention: {G} query heads per kv head exceed the kernel's limit of 16")
-    rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices = attention_work(batch, G, nkv, window)
+    rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices = attention_work(batch, G, nkv, window, hd)
     out = torch.empty_like(q)
     part_o = part_ml = None
     if n_merge:

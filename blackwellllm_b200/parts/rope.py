@@ -42,10 +42,18 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError(f"rotary_dim {spec.rotary_dim} must be even and in (0, head_dim={head_dim}]")
         self.rotary_dim = int(spec.rotary_dim)
         self.inv_freq = rotary_inv_freq(spec.theta, self.rotary_dim, spec.scaling).to(ctx.device)
+        self._key = ("rope_table", float(spec.theta), self.rotary_dim, spec.scaling)
 
     def rotate_append(self, qkv, batch, cache, nh, nkv, hd, append=True):
+        # the cosines and sines of the step's positions are the same in every layer with these
+        # rotary parameters: computed by the first one, kept on the batch for the others
+        table = batch.extras.get(self._key)
+        if table is None:
+            table = ops.rope_table(batch.positions, self.inv_freq, self.rotary_dim)
+            batch.extras[self._key] = table
         return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
-                               self.inv_freq, self.rotary_dim, cache.k_pages, cache.v_pages, nh, nkv, hd, append=append)
+                               self.inv_freq, self.rotary_dim, cache.k_pages, cache.v_pages, nh, nkv, hd,
+                               append=append, table=table)
 
 
 class NoPosition(PositionEncoding):

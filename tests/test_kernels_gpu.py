@@ -175,6 +175,7 @@ class FakeBatch:
         self.token_ids = self.positions
         self.static_bound = static_bound
         self.extras = {}
+        self.static_extras = {}
 
 
 def paged_case(q_lens, kv_lens, nh, nkv, hd, page, dtype, seed=0, spike=None):
