@@ -1,21 +1,24 @@
 // bfloat16 matrix product on the 5th-generation tensor cores:
 //     acc[i, j] = sum_k A[i, k] * B[j, k]      (A: [Ra, K], B: [Rb, K], both row-major)
-// TMA brings 128 x 64 tiles of A and BN x 64 tiles of B into shared memory (128-byte
-// swizzle), one elected thread issues tcgen05.mma into a TMEM accumulator, and four
-// epilogue warps read it back with tcgen05.ld.  Each CTA loads its own tiles (no
-// multicast).  One output tile per CTA; split-K over gridDim.z writes float32
-// partials that a second kernel sums in split order (deterministic).
+// A persistent kernel: one CTA per SM walks a list of work items (output tile, K split).
+// TMA brings 128 x 64 tiles of A and BN x 64 tiles of B into a shared-memory ring (128-byte
+// swizzle), one elected thread issues tcgen05.mma into one of TWO TMEM accumulators, and
+// four epilogue warps drain the other one with tcgen05.ld, so the epilogue of an item
+// overlaps the main loop of the next.  Each CTA loads its own tiles (no multicast).
 //
 // The same kernel serves both orientations of  out[tokens, features] = x . w^T:
 //   normal     A = x (tokens),   B = w (features): prefill, many tokens;
 //   transposed A = w (features), B = x (tokens):   few tokens (decode): the weight
 //              rows fill the 128-row MMA dimension and the tokens are the narrow N.
-// Epilogue: + bias[feature], then store (float32 | bfloat16) or add into float32 out.
+// Split-K: every item writes its float32 partial tile to scratch; per (tile, 32-row
+// quarter) a counter tells the warp that finishes last to add the partials IN SPLIT
+// ORDER (deterministic) and run the epilogue.  Counters return to zero by themselves.
+// Epilogue: + bias[feature], then store float32 | bfloat16, or add into float32 out
+// (the residual stream), or SwiGLU over interleaved gate/up features -> bfloat16.
 //
-// Roles (192 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issuer,
-// warps 2..5 epilogue (TMEM lane quarter = warp % 4).  Every wait is bounded; a
-// timeout sets the status word, and all roles fall through to the common exit
-// where TMEM is freed.
+// Roles (192 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps
+// 2..5 epilogue (TMEM lane quarter = warp % 4).  Every wait is bounded; a timeout sets
+// the status word and all roles fall through to the common exit where TMEM is freed.
 #include "tcgen05.cuh"
 
 using bf16 = __nv_bfloat16;
@@ -27,128 +30,184 @@ constexpr int BK = 64;        // k-block: 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int THREADS = 192;
-constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int NUM_SMS = 148;
+constexpr int STAGING_BYTES = 4 * 32 * 33 * 4;          // one 32 x 33 float block per epilogue warp
+constexpr int SMEM_BUDGET = 226 * 1024 - STAGING_BYTES - 2048;
+constexpr int SWIGLU_BLOCK = 16;   // gate/up features are interleaved in blocks of 16 rows of the weight
 
 __device__ int g_status = 0;  // 0 ok; else the code of the first wait that gave up
 
 struct Epilogue {
-    void* out;            // [tokens, features], row stride ldo (elements)
+    void* out;            // [tokens, features] (SwiGLU: [tokens, features / 2]), row stride ldo (elements)
     float* partial;       // split-K: [splits, tokens, features] dense float32; else null
+    int* counters;        // split-K: one per (tile, quarter), zero before and after the launch
     const void* bias;     // [features] or null
     long long ldo;
-    int out_type, bias_type, accumulate, transposed;
-    int tokens, features;
+    int out_type, bias_type, accumulate, transposed, swiglu;
+    int tokens, features, splits;
 };
 
-// Wide tiles take the whole SM; narrow ones (few tokens: a weight stream bound by HBM) use 4
-// stages so that 2-3 CTAs share an SM and one CTA's start-up and epilogue overlap the others' loads.
 template <int BN> __host__ __device__ constexpr int stages_for() {
     constexpr int per = A_BYTES + BN * BK * 2;
     constexpr int s = SMEM_BUDGET / per;
-    return BN <= 64 ? 4 : (s > 8 ? 8 : s);
+    return s > 8 ? 8 : s;
 }
-constexpr int ctas_per_sm(int bn) { return bn <= 16 ? 3 : (bn <= 64 ? 2 : 1); }
 
-__device__ __forceinline__ void store_val(const Epilogue& ep, int token, int feature, float v) {
-    if (ep.bias) v += ep.bias_type == BW_F32 ? ((const float*)ep.bias)[feature]
-                                              : __bfloat162float(((const bf16*)ep.bias)[feature]);
-    const size_t off = (size_t)token * ep.ldo + feature;
+// The lane holds the finished sums vals[0..N) of ONE feature for N consecutive tokens (token0 + c);
+// the 32 lanes of the warp hold 32 consecutive features.  nvalid (the same in all lanes) of the
+// tokens exist.  When the result is added to `out`, all old values are fetched before the first
+// store, so the loads are in flight together instead of one round trip per token.
+template <int N>
+__device__ __forceinline__ void emit(const Epilogue& ep, float* part, const float (&vals)[N], int token0,
+                                     int nvalid, int feature, bool fvalid) {
+    if (part) {
+#pragma unroll
+        for (int c = 0; c < N; ++c)
+            if (c < nvalid && fvalid) part[(size_t)(token0 + c) * ep.features + feature] = vals[c];
+        return;
+    }
+    if (ep.swiglu) {
+        // lanes 0..15 hold gate, lanes 16..31 up of the same 16 output features
+        const int lane = threadIdx.x & 31;
+        const int j = (feature / (2 * SWIGLU_BLOCK)) * SWIGLU_BLOCK + lane;
+#pragma unroll
+        for (int c = 0; c < N; ++c) {
+            const float other = __shfl_xor_sync(0xffffffffu, vals[c], 16);
+            if (c < nvalid && fvalid && lane < SWIGLU_BLOCK)
+                ((bf16*)ep.out)[(size_t)(token0 + c) * ep.ldo + j] =
+                    __float2bfloat16_rn(__fdividef(vals[c], 1.f + __expf(-vals[c])) * other);
+        }
+        return;
+    }
+    if (!fvalid) return;
+    float b = 0.f;
+    if (ep.bias) b = ep.bias_type == BW_F32 ? ((const float*)ep.bias)[feature]
+                                             : __bfloat162float(((const bf16*)ep.bias)[feature]);
+    const size_t off = (size_t)token0 * ep.ldo + feature;
     if (ep.out_type == BW_F32) {
         float* o = (float*)ep.out + off;
-        *o = ep.accumulate ? *o + v : v;
+        float old[N];
+        if (ep.accumulate) {
+#pragma unroll
+            for (int c = 0; c < N; ++c) old[c] = c < nvalid ? o[(size_t)c * ep.ldo] : 0.f;
+        }
+#pragma unroll
+        for (int c = 0; c < N; ++c)
+            if (c < nvalid) o[(size_t)c * ep.ldo] = vals[c] + b + (ep.accumulate ? old[c] : 0.f);
     } else {
-        ((bf16*)ep.out)[off] = __float2bfloat16_rn(v);
+        bf16* o = (bf16*)ep.out + off;
+#pragma unroll
+        for (int c = 0; c < N; ++c)
+            if (c < nvalid) o[(size_t)c * ep.ldo] = __float2bfloat16_rn(vals[c] + b);
     }
 }
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               Epilogue ep, int kb_total, int kb_per_split) {
+               Epilogue ep, int kb_total, int kb_per_split, int tiles_a, int tiles_b, int num_work) {
     constexpr int STAGES = stages_for<BN>();
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators
     constexpr uint32_t IDESC = bw::umma_idesc_bf16(BM, BN);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // full[STAGES], empty[STAGES], tmem_full
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    float* staging = (float*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES + STAGING_BYTES);
+    // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
-    const int kb0 = split * kb_per_split;
-    const int nkb = min(kb_total, kb0 + kb_per_split) - kb0;
-
     const uint32_t full0 = bw::smem_u32(bars), empty0 = bw::smem_u32(bars + STAGES);
-    const uint32_t tmem_full = bw::smem_u32(bars + 2 * STAGES);
+    const uint32_t tfull0 = bw::smem_u32(bars + 2 * STAGES), tempty0 = bw::smem_u32(bars + 2 * STAGES + 2);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { bw::mbar_init(full0 + 8 * s, 1); bw::mbar_init(empty0 + 8 * s, 1); }
-        bw::mbar_init(tmem_full, 1);
+        for (int a = 0; a < 2; ++a) { bw::mbar_init(tfull0 + 8 * a, 1); bw::mbar_init(tempty0 + 8 * a, 4); }
         bw::fence_barrier_init();
         bw::tma_prefetch_desc(&tmA);
         bw::tma_prefetch_desc(&tmB);
-        tmem_slot[1] = (uint32_t)g_status;   // an earlier timeout: later CTAs do no work
+        tmem_slot[1] = (uint32_t)g_status;   // an earlier timeout: later launches do no work
     }
     if (warp == 1) bw::tmem_alloc(bw::smem_u32(tmem_slot), TMEM_COLS);
     bw::tc_fence_before();
     __syncthreads();
     bw::tc_fence_after();
-    const uint32_t tmem_acc = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot;
     const bool dead = tmem_slot[1] != 0;
+    const int tiles = tiles_a * tiles_b;
 
     if (dead) {
         // fall through to the exit
     } else if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
-                if (!bw::mbar_wait(empty0 + 8 * s, ph ^ 1, &g_status, 1)) break;
-                bw::mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                const uint32_t a_dst = bw::smem_u32(smem + s * STAGE_BYTES);
-                bw::tma_load_2d(a_dst, &tmA, full0 + 8 * s, (kb0 + i) * BK, tile_a * BM);
-                bw::tma_load_2d(a_dst + A_BYTES, &tmB, full0 + 8 * s, (kb0 + i) * BK, tile_b * BN);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+                const int tile = w % tiles, split = w / tiles;
+                const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;
+                const int kb0 = split * kb_per_split;
+                const int nkb = min(kb_total, kb0 + kb_per_split) - kb0;
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!bw::mbar_wait(empty0 + 8 * s, ph ^ 1, &g_status, 1)) { ok = false; break; }
+                    bw::mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                    const uint32_t a_dst = bw::smem_u32(smem + s * STAGE_BYTES);
+                    bw::tma_load_2d(a_dst, &tmA, full0 + 8 * s, (kb0 + i) * BK, tile_a * BM);
+                    bw::tma_load_2d(a_dst + A_BYTES, &tmB, full0 + 8 * s, (kb0 + i) * BK, tile_b * BN);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            uint32_t it = 0, n = 0;
             bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
-                const int s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
-                ok = bw::mbar_wait(full0 + 8 * s, ph, &g_status, 2);
-                if (!ok) break;
+            for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++n) {
+                const int split = w / tiles;
+                const int kb0 = split * kb_per_split;
+                const int nkb = min(kb_total, kb0 + kb_per_split) - kb0;
+                const uint32_t acc = n & 1, accph = (n >> 1) & 1;
+                if (!bw::mbar_wait(tempty0 + 8 * acc, accph ^ 1, &g_status, 4)) break;   // epilogue drained it
                 bw::tc_fence_after();
-                const uint32_t a_addr = bw::smem_u32(smem + s * STAGE_BYTES);
-                const uint64_t da = bw::umma_smem_desc_sw128(a_addr);
-                const uint64_t db = bw::umma_smem_desc_sw128(a_addr + A_BYTES);
+                const uint32_t tmem_acc = tmem_base + acc * BN;
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!bw::mbar_wait(full0 + 8 * s, ph, &g_status, 2)) { ok = false; break; }
+                    bw::tc_fence_after();
+                    const uint32_t a_addr = bw::smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t da = bw::umma_smem_desc_sw128(a_addr);
+                    const uint64_t db = bw::umma_smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // advance 32 bytes (2 units of 16 B) along K inside the swizzle row
-                    bw::umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, IDESC, (i | k) != 0);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // advance 32 bytes (2 units of 16 B) along K inside the swizzle row
+                        bw::umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, IDESC, (i | k) != 0);
+                    }
+                    bw::umma_commit(empty0 + 8 * s);   // the stage is free once these MMAs are done
                 }
-                bw::umma_commit(empty0 + 8 * s);   // the stage is free once these MMAs are done
+                bw::umma_commit(tfull0 + 8 * acc);     // this accumulator is complete
             }
-            bw::umma_commit(tmem_full);            // the accumulator is complete
         }
     } else {
         const int quarter = warp & 3;              // TMEM lanes 32 * quarter .. + 31
-        const int row = quarter * 32 + lane;       // row of the A tile
-        const int ga = tile_a * BM + row;          // global A row
-        if (bw::mbar_wait(tmem_full, 0, &g_status, 3)) {
+        float* stage = staging + (warp - 2) * (32 * 33);
+        const int a_rows = ep.transposed ? ep.features : ep.tokens;
+        const int b_rows = ep.transposed ? ep.tokens : ep.features;
+        const size_t plane = (size_t)ep.tokens * ep.features;
+        constexpr int CH = BN < 32 ? 16 : 32;
+        uint32_t n = 0;
+        for (int w = blockIdx.x; w < num_work; w += gridDim.x, ++n) {
+            const int tile = w % tiles, split = w / tiles;
+            const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;
+            const uint32_t acc = n & 1, accph = (n >> 1) & 1;
+            if (!bw::mbar_wait(tfull0 + 8 * acc, accph, &g_status, 3)) break;
             bw::tc_fence_after();
-            const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
-            const int a_rows = ep.transposed ? ep.features : ep.tokens;
-            const int b_rows = ep.transposed ? ep.tokens : ep.features;
-            float* part = ep.partial ? ep.partial + (size_t)split * ep.tokens * ep.features : nullptr;
-            constexpr int CH = BN < 32 ? 16 : 32;
-            // All MMAs are complete, so the pipeline's shared memory is free: each epilogue
-            // warp takes 32 x 33 floats of it to turn its 32 x 32 block, so that in the
-            // normal orientation a warp stores whole rows (32 consecutive features).
-            float* stage = (float*)smem + (warp - 2) * (32 * 33);
+            const uint32_t lane_addr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+            const int ga = tile_a * BM + quarter * 32 + lane;   // this lane's row of A
+            float* part = ep.partial ? ep.partial + (size_t)split * plane : nullptr;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += CH) {
                 uint32_t v[CH];
@@ -156,54 +215,88 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 else bw::tmem_ld_32x16(lane_addr + c0, v);
                 bw::tmem_ld_wait();
                 if (ep.transposed) {
-                    // lanes hold consecutive features of one token per column: already coalesced
-                    if (ga < a_rows) {
+                    // lanes hold 32 consecutive features, the columns are consecutive tokens: coalesced as it is
+                    float vals[CH];
 #pragma unroll
-                        for (int c = 0; c < CH; ++c) {
-                            const int token = tile_b * BN + c0 + c;
-                            if (token < b_rows) {
-                                const float acc = __uint_as_float(v[c]);
-                                if (part) part[(size_t)token * ep.features + ga] = acc;
-                                else store_val(ep, token, ga, acc);
-                            }
-                        }
-                    }
+                    for (int c = 0; c < CH; ++c) vals[c] = __uint_as_float(v[c]);
+                    const int token0 = tile_b * BN + c0;
+                    emit<CH>(ep, part, vals, token0, min(CH, b_rows - token0), ga, ga < a_rows);
                 } else {
                     if constexpr (CH == 32) {
+                        // turn the 32 x 32 block through shared memory so that a warp stores whole rows
 #pragma unroll
                         for (int c = 0; c < 32; ++c) stage[lane * 33 + c] = __uint_as_float(v[c]);
                         __syncwarp();
                         const int feature = tile_b * BN + c0 + lane;
-                        if (feature < b_rows) {
-#pragma unroll 4
-                            for (int r = 0; r < 32; ++r) {
-                                const int token = tile_a * BM + quarter * 32 + r;
-                                if (token >= a_rows) break;
-                                const float acc = stage[r * 33 + lane];
-                                if (part) part[(size_t)token * ep.features + feature] = acc;
-                                else store_val(ep, token, feature, acc);
+                        const int token0 = tile_a * BM + quarter * 32;
+                        float vals[32];
+#pragma unroll
+                        for (int r = 0; r < 32; ++r) vals[r] = stage[r * 33 + lane];
+                        __syncwarp();
+                        if (tile_b * BN + c0 < b_rows)
+                            emit<32>(ep, part, vals, token0, min(32, a_rows - token0), feature, feature < b_rows);
+                    }
+                }
+            }
+            // the accumulator may be overwritten now
+            bw::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) bw::mbar_arrive(tempty0 + 8 * acc);
+
+            if (part) {
+                // split-K: the warp that completes this (tile, quarter) last sums all partials
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) last = atomicAdd(&ep.counters[tile * 4 + quarter], 1) == ep.splits - 1;
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    // eight tokens at a time, so that their loads are in flight together
+                    if (ep.transposed) {
+                        const int t_end = min(b_rows, (tile_b + 1) * BN);
+                        for (int token0 = tile_b * BN; token0 < t_end; token0 += 8) {
+                            float vals[8];
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) vals[c] = 0.f;
+                            const int nv = min(8, t_end - token0);
+                            if (ga < a_rows)
+                                for (int s = 0; s < ep.splits; ++s) {
+                                    const float* src = ep.partial + (size_t)s * plane + (size_t)token0 * ep.features + ga;
+#pragma unroll
+                                    for (int c = 0; c < 8; ++c)
+                                        if (c < nv) vals[c] += __ldcg(src + (size_t)c * ep.features);
+                                }
+                            emit<8>(ep, nullptr, vals, token0, nv, ga, ga < a_rows);
+                        }
+                    } else {
+                        const int r_end = min(a_rows, tile_a * BM + quarter * 32 + 32);
+                        for (int c0 = 0; c0 < BN && tile_b * BN + c0 < b_rows; c0 += 32) {
+                            const int feature = tile_b * BN + c0 + lane;
+                            for (int token0 = tile_a * BM + quarter * 32; token0 < r_end; token0 += 8) {
+                                float vals[8];
+#pragma unroll
+                                for (int c = 0; c < 8; ++c) vals[c] = 0.f;
+                                const int nv = min(8, r_end - token0);
+                                if (feature < b_rows)
+                                    for (int s = 0; s < ep.splits; ++s) {
+                                        const float* src = ep.partial + (size_t)s * plane + (size_t)token0 * ep.features + feature;
+#pragma unroll
+                                        for (int c = 0; c < 8; ++c)
+                                            if (c < nv) vals[c] += __ldcg(src + (size_t)c * ep.features);
+                                    }
+                                emit<8>(ep, nullptr, vals, token0, nv, feature, feature < b_rows);
                             }
                         }
-                        __syncwarp();
                     }
+                    if (lane == 0) ep.counters[tile * 4 + quarter] = 0;
                 }
             }
         }
     }
     bw::tc_fence_before();
     __syncthreads();
-    if (warp == 1) bw::tmem_dealloc(tmem_acc, TMEM_COLS);
-}
-
-// out = (accumulate ? out : 0) + bias + sum over splits of partial, in split order
-__global__ void splitk_reduce_kernel(Epilogue ep, int splits) {
-    const size_t total = (size_t)ep.tokens * ep.features;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        float v = 0.f;
-        for (int s = 0; s < splits; ++s) v += ep.partial[(size_t)s * total + i];
-        const int token = (int)(i / ep.features), feature = (int)(i - (size_t)token * ep.features);
-        store_val(ep, token, feature, v);
-    }
+    if (warp == 1) bw::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -237,17 +330,19 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long K, lon
 }
 
 template <int BN>
-int launch(const CUtensorMap& a, const CUtensorMap& b, const Epilogue& ep, dim3 grid, int kb_total,
-           int kb_per_split, cudaStream_t s) {
+int launch(const CUtensorMap& a, const CUtensorMap& b, const Epilogue& ep, int kb_total, int kb_per_split,
+           int tiles_a, int tiles_b, int num_work, cudaStream_t s) {
     constexpr int STAGES = stages_for<BN>();
-    constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + STAGING_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+    static_assert(smem <= 227 * 1024, "shared memory budget");
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
-    gemm_tc_kernel<BN><<<grid, THREADS, smem, s>>>(a, b, ep, kb_total, kb_per_split);
+    const int grid = num_work < NUM_SMS ? num_work : NUM_SMS;
+    gemm_tc_kernel<BN><<<grid, THREADS, smem, s>>>(a, b, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work);
     BW_LAUNCH_CHECK();
     return 0;
 }
@@ -264,80 +359,81 @@ BW_EXPORT int bw_gemm_tc_supported(const void* x, const void* w, int K, long lon
 
 // Picks the orientation, the tile width and the number of K splits for
 // out[M, N] = x[M, K] . w[N, K]^T.  Returns splits; *transposed and *bn are set.
-BW_EXPORT int bw_gemm_tc_plan(int M, int N, int K, long long workspace_elems, int* transposed, int* bn) {
+BW_EXPORT int bw_gemm_tc_plan(int M, int N, int K, long long workspace_elems, long long n_counters,
+                              int* transposed, int* bn) {
     const int kb_total = ceil_div(K, BK);
     int tr = M <= 256, b;
     if (tr) { b = 16; while (b < M) b *= 2; }
     else {
-        // wave efficiency on 148 SMs picks between 128- and 256-wide tiles
+        // balance over the 148 persistent CTAs picks between 128- and 256-wide tiles
         auto eff = [&](int w) { long long t = (long long)ceil_div(M, BM) * ceil_div(N, w);
-                                return (double)t / ((double)ceil_div(t, 148) * 148) * (w == 256 ? 1.0 : 0.92); };
+                                return (double)t / ((double)ceil_div(t, NUM_SMS) * NUM_SMS) * (w == 256 ? 1.0 : 0.9); };
         b = eff(256) >= eff(128) ? 256 : 128;
     }
     *transposed = tr; *bn = b;
     const long long tiles = tr ? (long long)ceil_div(N, BM) * ceil_div(M, b) : (long long)ceil_div(M, BM) * ceil_div(N, b);
     int best = 1; double best_score = 0;
-    for (int s = 1; s <= 8; ++s) {
-        if (s > 1 && (kb_total / s < 8 || (long long)s * M * N > workspace_elems)) break;
-        const long long ctas = tiles * s, slots = 148LL * ctas_per_sm(b);
-        const double wave = (double)ctas / ((double)ceil_div(ctas, slots) * slots);
+    for (int s = 1; s <= 16; ++s) {
+        if (s > 1 && (kb_total / s < 4 || (long long)s * M * N > workspace_elems || tiles * 4 > n_counters)) break;
+        const long long items = tiles * s;
+        const double balance = (double)items / ((double)ceil_div(items, NUM_SMS) * NUM_SMS);
         const double extra = s > 1 ? 4.0 * s * M / (double)K : 0.0;   // partial traffic relative to the weights
-        const double score = wave / (1.0 + extra);
-        if (score > best_score * 1.02) { best_score = score; best = s; }
+        const double score = balance / (1.0 + extra);
+        if (score > best_score * 1.03) { best_score = score; best = s; }
     }
     return best;
 }
 
 // out[M, N] (=|+=) x[M, K] . w[N, K]^T (+ bias[N]).  x, w bf16; out float32 or bf16
-// (accumulate: float32).  workspace: float32 scratch for split-K partials (may be null).
-// force_splits > 0 overrides the planner (tests).
+// (accumulate: float32).  swiglu != 0: w holds gate and up rows interleaved in blocks of 16
+// (16 gate rows, the 16 up rows of the same features, ...), N = 2 I with I a multiple of 16,
+// and out is bf16 [M, I] = silu(gate) * up.  workspace / counters: scratch for split-K
+// (float32 partial sums; int32 counters that are zero between launches); may be null.
+// force_splits > 0 overrides the planner.
 BW_EXPORT int bw_gemm_tc(const void* x, const void* w, const void* bias, int bias_type, void* out, int out_type,
-                         int M, int N, int K, long long ldx, long long ldo, int accumulate, float* workspace,
-                         long long workspace_elems, int force_splits, void* stream) {
+                         int M, int N, int K, long long ldx, long long ldo, int accumulate, int swiglu,
+                         float* workspace, long long workspace_elems, int* counters, long long n_counters,
+                         int force_splits, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!bw_gemm_tc_supported(x, w, K, ldx)) return BW_ERR_UNSUPPORTED;
     if (accumulate && out_type != BW_F32) return BW_ERR_BAD_ARG;
-    if (ldo < N) return BW_ERR_BAD_ARG;
+    if (swiglu && (N % (2 * SWIGLU_BLOCK) != 0 || out_type != BW_BF16 || accumulate || bias || ldo < N / 2))
+        return BW_ERR_BAD_ARG;
+    if (!swiglu && ldo < N) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
+    const bool can_split = workspace && counters;
     int tr, bn;
-    int splits = bw_gemm_tc_plan(M, N, K, workspace ? workspace_elems : 0, &tr, &bn);
+    int splits = bw_gemm_tc_plan(M, N, K, can_split ? workspace_elems : 0, can_split ? n_counters : 0, &tr, &bn);
     const int kb_total = ceil_div(K, BK);
+    const long long a_rows = tr ? N : M, b_rows = tr ? M : N;
+    const int tiles_a = ceil_div(a_rows, BM), tiles_b = ceil_div(b_rows, bn);
     if (force_splits > 0) {
-        splits = force_splits;
-        if (splits > kb_total) splits = kb_total;
-        if (splits > 1 && (!workspace || (long long)splits * M * N > workspace_elems)) return BW_ERR_BAD_ARG;
+        splits = force_splits > kb_total ? kb_total : force_splits;
+        if (splits > 1 && (!can_split || (long long)splits * M * N > workspace_elems ||
+                           (long long)tiles_a * tiles_b * 4 > n_counters))
+            return BW_ERR_BAD_ARG;
     }
-    int kb_per_split = ceil_div(kb_total, splits);
+    const int kb_per_split = ceil_div(kb_total, splits);
     splits = ceil_div(kb_total, kb_per_split);   // no empty split
 
     CUtensorMap ta, tb;
     const void* a_ptr = tr ? w : x; const void* b_ptr = tr ? x : w;
-    const long long a_rows = tr ? N : M, b_rows = tr ? M : N;
     const long long a_ld = tr ? K : ldx, b_ld = tr ? ldx : K;
     if (!make_map(&ta, a_ptr, a_rows, K, a_ld, BM) || !make_map(&tb, b_ptr, b_rows, K, b_ld, bn)) return BW_ERR_DRIVER;
 
     Epilogue ep;
-    ep.out = out; ep.partial = splits > 1 ? workspace : nullptr; ep.bias = bias; ep.ldo = ldo;
+    ep.out = out; ep.partial = splits > 1 ? workspace : nullptr; ep.counters = counters; ep.bias = bias; ep.ldo = ldo;
     ep.out_type = out_type; ep.bias_type = bias_type; ep.accumulate = accumulate; ep.transposed = tr;
-    ep.tokens = M; ep.features = N;
-    dim3 grid(ceil_div(a_rows, BM), ceil_div(b_rows, bn), splits);
-    int rc;
+    ep.swiglu = swiglu; ep.tokens = M; ep.features = N; ep.splits = splits;
+    const int num_work = tiles_a * tiles_b * splits;
     switch (bn) {
-        case 16: rc = launch<16>(ta, tb, ep, grid, kb_total, kb_per_split, s); break;
-        case 32: rc = launch<32>(ta, tb, ep, grid, kb_total, kb_per_split, s); break;
-        case 64: rc = launch<64>(ta, tb, ep, grid, kb_total, kb_per_split, s); break;
-        case 128: rc = launch<128>(ta, tb, ep, grid, kb_total, kb_per_split, s); break;
-        case 256: rc = launch<256>(ta, tb, ep, grid, kb_total, kb_per_split, s); break;
+        case 16: return launch<16>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s);
+        case 32: return launch<32>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s);
+        case 64: return launch<64>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s);
+        case 128: return launch<128>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s);
+        case 256: return launch<256>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s);
         default: return BW_ERR_BAD_ARG;
     }
-    if (rc) return rc;
-    if (splits > 1) {
-        const size_t total = (size_t)M * N;
-        const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-        splitk_reduce_kernel<<<blocks, 256, 0, s>>>(ep, splits);
-        BW_LAUNCH_CHECK();
-    }
-    return 0;
 }
 
 // Reads and clears the status word (synchronises the device).  0: no wait ever gave up.

@@ -9,13 +9,17 @@
 // runtime (it is not a device address): the address comes from
 // cudaGetSymbolAddress below and is what the kernels receive.
 static __device__ __align__(256) float g_noalloc_scratch[BW_NOALLOC_SCRATCH_FLOATS];
+// Completion counters of the split-K tiles.  They must be zero when a call starts: static device
+// memory starts as zero, and the kernel sets every counter it used back to zero before it ends.
+static __device__ __align__(256) int g_noalloc_counters[BW_NOALLOC_COUNTERS];
 
 namespace {
 constexpr int MAX_DEVICES = 64;
 float* g_scratch_addr[MAX_DEVICES] = {nullptr};
+int* g_counters_addr[MAX_DEVICES] = {nullptr};
 
-// Device address of the scratch array on the current device; looked up once per device.
-int scratch_on_current_device(float** addr) {
+// Device addresses of the scratch arrays on the current device; looked up once per device.
+int scratch_on_current_device(float** addr, int** counters) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
@@ -25,9 +29,15 @@ int scratch_on_current_device(float** addr) {
         e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
         if (e != cudaSuccess) return (int)e;
         if (!p) return BW_ERR_DRIVER;
+        int* c = nullptr;
+        e = cudaGetSymbolAddress((void**)&c, g_noalloc_counters);
+        if (e != cudaSuccess) return (int)e;
+        if (!c) return BW_ERR_DRIVER;
+        g_counters_addr[dev] = c;
         g_scratch_addr[dev] = p;
     }
     *addr = g_scratch_addr[dev];
+    *counters = g_counters_addr[dev];
     return 0;
 }
 }  // namespace
@@ -41,8 +51,9 @@ BW_EXPORT int bw_gemm_tc_noalloc(const void* x, const void* w, const void* bias,
     if (splits > kb_total) splits = kb_total;
     if ((long long)splits * M * N > (long long)BW_NOALLOC_SCRATCH_FLOATS) return BW_NOALLOC_TOO_LARGE;
     float* scratch = nullptr;
-    const int rc = scratch_on_current_device(&scratch);
+    int* counters = nullptr;
+    const int rc = scratch_on_current_device(&scratch, &counters);
     if (rc) return rc;
-    return bw_gemm_tc(x, w, bias, bias_type, out, out_type, M, N, K, ldx, ldo, accumulate, scratch,
-                      (long long)BW_NOALLOC_SCRATCH_FLOATS, splits, stream);
+    return bw_gemm_tc(x, w, bias, bias_type, out, out_type, M, N, K, ldx, ldo, accumulate, /*swiglu=*/0, scratch,
+                      (long long)BW_NOALLOC_SCRATCH_FLOATS, counters, (long long)BW_NOALLOC_COUNTERS, splits, stream);
 }

@@ -26,14 +26,18 @@
 //   * All calls on a device share the one array.  Two calls that overlap on the
 //     GPU (different streams, no dependency between them) race on it and give
 //     wrong sums; order them on one stream or with events.
-//   * The array keeps the last call's contents.  Nothing in it has to start at
-//     zero: every partial sum a call reads was written by that same call.
+//   * The array keeps the last call's contents.  The partial sums need no
+//     clearing: every one a call reads was written by that same call.  Beside
+//     them sit BW_NOALLOC_COUNTERS int32 completion counters (64 KiB) that must be
+//     zero when a call starts; they start as zero and every call puts the ones it
+//     used back to zero before its kernel ends.
 //   * Operands as for bw_gemm_tc: x [M, K] and w [N, K] bfloat16 with K and ldx
 //     multiples of 8 and 16-byte aligned bases; out [M, N] float32 or bfloat16
 //     (type codes 0 / 1), accumulate != 0 adds into a float32 out.
 #pragma once
 
 #define BW_NOALLOC_SCRATCH_FLOATS (4 * 1024 * 1024)
+#define BW_NOALLOC_COUNTERS 16384
 #define BW_NOALLOC_TOO_LARGE (-10)
 
 #ifdef __cplusplus

@@ -63,10 +63,8 @@ def build_dir() -> str:
     for d in cands:
         try:
             os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".w{os.getpid()}")
-            with open(probe, "w"):
+            with tempfile.NamedTemporaryFile(dir=d, prefix=".w"):
                 pass
-            os.remove(probe)
             return d
         except OSError:
             continue

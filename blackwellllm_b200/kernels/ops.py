@@ -279,19 +279,34 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Opt
 
 # ------------------------------------------------------------------ dispatch
 
-_GEMM_TC_ARGS = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_int,
-                 c_void_p, c_ll, c_int, c_void_p]
+_GEMM_TC_ARGS = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int,
+                 c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p]
 _WORKSPACE_BYTES = 64 << 20
+_COUNTERS = 1 << 16
 _workspaces = {}
+SWIGLU_BLOCK = 16  # gate/up rows of a fused SwiGLU weight alternate in blocks of this many
 
 
-def _workspace(device: torch.device) -> torch.Tensor:
-    """Scratch for split-K partial sums, one per device, made at first use."""
+def _workspace(device: torch.device):
+    """Scratch for split-K, one per device, made at first use: float32 partial sums and
+    int32 counters (zero between launches; the kernel returns them to zero)."""
     ws = _workspaces.get(device)
     if ws is None:
-        ws = torch.empty(_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
+        ws = (torch.empty(_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device),
+              torch.zeros(_COUNTERS, dtype=torch.int32, device=device))
         _workspaces[device] = ws
     return ws
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[I, K] gate and up weights -> [2I, K] with 16 gate rows, the 16 up rows of the same
+    features, and so on: the layout of gemm_tc's fused SwiGLU epilogue (I % 16 == 0)."""
+    I, K = gate.shape
+    if I % SWIGLU_BLOCK or up.shape != gate.shape:
+        raise KernelError("interleave_gate_up: both [I, K] with I a multiple of 16")
+    g = gate.reshape(I // SWIGLU_BLOCK, SWIGLU_BLOCK, K)
+    u = up.reshape(I // SWIGLU_BLOCK, SWIGLU_BLOCK, K)
+    return torch.stack([g, u], dim=1).reshape(2 * I, K).contiguous()
 
 
 def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -306,8 +321,10 @@ def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
             out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-            accumulate: bool = False, force_splits: int = 0) -> torch.Tensor:
-    """out (=|+=) x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, float32 sums)."""
+            accumulate: bool = False, force_splits: int = 0, swiglu: bool = False) -> torch.Tensor:
+    """out (=|+=) x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, float32 sums).
+    ``swiglu``: ``w`` is a gate/up weight from :func:`interleave_gate_up`; the result is
+    bfloat16 [M, N / 2] = silu(gate) * up, computed in the epilogue."""
     _dev(x, "x", torch.bfloat16, contiguous=False); _dev(w, "w", torch.bfloat16)
     if not gemm_tc_supports(x, w):
         raise KernelError("gemm_tc: operands must be bfloat16 with K and the row stride multiples of 8 "
@@ -316,22 +333,27 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
     N, K2 = w.shape
     if K != K2:
         raise KernelError(f"gemm: x has {K} columns, w has {K2}")
+    n_out = N
+    if swiglu:
+        if N % (2 * SWIGLU_BLOCK) or bias is not None or accumulate:
+            raise KernelError("gemm_tc: the SwiGLU epilogue needs N = 2 I with I a multiple of 16, no bias, no accumulate")
+        n_out, out_dtype = N // 2, torch.bfloat16
     if out is None:
         if accumulate:
             raise KernelError("gemm: accumulate needs an output tensor")
-        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+        out = torch.empty((M, n_out), dtype=out_dtype or x.dtype, device=x.device)
     _dev(out, "out", contiguous=False)
-    if out.shape != (M, N) or out.stride(1) != 1:
+    if out.shape != (M, n_out) or out.stride(1) != 1 or (swiglu and out.dtype != torch.bfloat16):
         raise KernelError("gemm: out must be [M, N] with contiguous rows")
     if bias is not None:
         _dev(bias, "bias")
         if bias.numel() != N:
             raise KernelError("gemm: bias must have N entries")
-    ws = _workspace(x.device)
+    ws, counters = _workspace(x.device)
     fn = _fn("gemm_tc", "bw_gemm_tc", _GEMM_TC_ARGS, tag=f"{M}x{N}x{K}" if _timings is not None else None)
     _check(fn(_ptr(x), _ptr(w), _ptr(bias), _code(bias, "bias") if bias is not None else 0, _ptr(out),
-              _code(out, "out"), M, N, K, x.stride(0), out.stride(0), int(accumulate), _ptr(ws), ws.numel(),
-              int(force_splits), _stream()), "gemm_tc")
+              _code(out, "out"), M, N, K, x.stride(0), out.stride(0), int(accumulate), int(swiglu), _ptr(ws),
+              ws.numel(), _ptr(counters), counters.numel(), int(force_splits), _stream()), "gemm_tc")
     return out
 
 

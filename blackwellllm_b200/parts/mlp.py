@@ -2,7 +2,11 @@
 
 Reference: src/core/engine.cpp:1010-1024 and src/kernels/swiglu.cu:15-37
 (silu(g) = g / (1 + exp(-g))); no biases.  Gate and up are one matrix made at
-load (rows gate, then up), so the input is read once.
+load, so the input is read once.  On the bfloat16 tensor-core path their rows are
+interleaved in blocks of 16 and the activation is computed in the epilogue of
+that matrix product, so gate and up never travel through memory; otherwise (the
+32-bit path, or sizes the tensor-core kernel refuses) the rows are gate then up
+and a separate kernel applies the activation.
 """
 from __future__ import annotations
 
@@ -20,6 +24,7 @@ class SwiGLU(FeedForward):
         self.intermediate_size = int(spec.intermediate_size)
         self.hidden_size = hidden_size
         self.ctx = ctx
+        self.fused = False
         self.gate_up: Linear = None
         self.down: Linear = None
 
@@ -29,12 +34,20 @@ class SwiGLU(FeedForward):
                 ParamSpec("down_proj.weight", (H, I))]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.gate_up = Linear(torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0))
+        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        self.fused = (g.dtype == torch.bfloat16 and g.is_cuda and self.intermediate_size % ops.SWIGLU_BLOCK == 0
+                      and self.hidden_size % 8 == 0)
+        if self.fused:
+            self.gate_up = Linear(ops.interleave_gate_up(g, u))
+        else:
+            self.gate_up = Linear(torch.cat([g, u], dim=0))
         self.down = Linear(tensors["down_proj.weight"])
 
     def forward(self, x, residual, batch) -> None:
-        gu = self.gate_up(x)
-        a = ops.swiglu(gu)
+        if self.fused:
+            a = ops.gemm_tc(x, self.gate_up.weight, swiglu=True)
+        else:
+            a = ops.swiglu(self.gate_up(x))
         self.down(a, out=residual, accumulate=True)
 
 

@@ -71,6 +71,22 @@ def test_gemm_tc_split_k(ops, M, splits):
     assert torch.equal(out, again)  # split sums are added in a fixed order
 
 
+@pytest.mark.parametrize("M,I,K,splits", [(1, 176, 64, 0), (8, 14336, 4096, 0), (40, 1008, 512, 3), (300, 176, 256, 0),
+                                          (700, 528, 2048, 2), (2048, 1024, 1024, 0)])
+def test_gemm_tc_swiglu_epilogue(ops, M, I, K, splits):
+    """silu(x Wg^T) * (x Wu^T) from the interleaved weight, in both orientations and with split-K."""
+    x = rand(M, K, dtype=torch.bfloat16, seed=1).to(DEV)
+    wg = rand(I, K, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    wu = rand(I, K, dtype=torch.bfloat16, seed=3, scale=0.05).to(DEV)
+    w = ops.interleave_gate_up(wg, wu)
+    assert torch.equal(w[:16], wg[:16]) and torch.equal(w[16:32], wu[:16]) and torch.equal(w[32:48], wg[16:32])
+    out = ops.gemm_tc(x, w, swiglu=True, force_splits=splits)
+    assert out.shape == (M, I) and out.dtype == torch.bfloat16
+    ref = plain_swiglu(x.double() @ wg.double().T, x.double() @ wu.double().T)
+    assert ops.gemm_tc_status() == 0
+    assert float((out.double() - ref).abs().max()) <= 2 ** -7 * float(ref.abs().max())
+
+
 def test_gemm_tc_row_independent_of_batch(ops):
     """A token's row does not depend on which other tokens share the launch."""
     K, N = 1024, 768
