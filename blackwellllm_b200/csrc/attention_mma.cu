@@ -397,24 +397,32 @@ attn_keys_kernel(Params p) {
     }
 }
 
-// sums the slices of every sliced item: grid (sliced items, nkv)
-__global__ void __launch_bounds__(THREADS)
+// sums the slices of every sliced item: grid (sliced items, nkv).  The slices' maxima and sums go
+// to shared memory first; the loads of the partial outputs are then independent of one another.
+constexpr int MAX_SLICES = 64;
+__global__ void __launch_bounds__(256)
 attn_merge_kernel(Params p, const int* merge_items) {
+    __shared__ float sm_m[MAX_SLICES * 16], sm_l[MAX_SLICES * 16];
     const int4 w = reinterpret_cast<const int4*>(merge_items)[blockIdx.x];
     const int r = w.x, n_slices = w.z, item = w.w, g = blockIdx.y;
     const int n_rows = (p.cu_q[r + 1] - p.cu_q[r]) * p.G;
-    for (int idx = threadIdx.x; idx < n_rows * HD; idx += THREADS) {
+    const size_t base0 = ((size_t)item * p.nkv + (size_t)g * n_slices) * 16;
+    for (int i = threadIdx.x; i < n_slices * 16; i += blockDim.x) {
+        const float2 ml = reinterpret_cast<const float2*>(p.part_ml)[base0 + i];
+        sm_m[i] = ml.x; sm_l[i] = ml.y;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_rows * HD; idx += blockDim.x) {
         const int row = idx / HD, c = idx - row * HD;
-        const size_t base = ((size_t)item * p.nkv + (size_t)g * n_slices) * 16 + row;
         float M = -INFINITY;
-        for (int s = 0; s < n_slices; ++s) M = fmaxf(M, p.part_ml[(base + (size_t)s * 16) * 2]);
+        for (int s = 0; s < n_slices; ++s) M = fmaxf(M, sm_m[s * 16 + row]);
         float acc = 0.f, L = 0.f;
+#pragma unroll 8
         for (int s = 0; s < n_slices; ++s) {
-            const size_t pr = base + (size_t)s * 16;
-            const float ms = p.part_ml[pr * 2];
+            const float ms = sm_m[s * 16 + row];
             const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-            acc += p.part_o[pr * HD + c] * f;
-            L += p.part_ml[pr * 2 + 1] * f;
+            acc += p.part_o[(base0 + (size_t)s * 16 + row) * HD + c] * f;
+            L += sm_l[s * 16 + row] * f;
         }
         const int tok = row / p.G, hg = row - tok * p.G;
         p.out[((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
@@ -467,7 +475,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
         attn_keys_kernel<<<dim3(n_keys_items, nkv), THREADS, SMEM_KEYS, s>>>(p);
         BW_LAUNCH_CHECK();
         if (n_merge_items > 0) {
-            attn_merge_kernel<<<dim3(n_merge_items, nkv), THREADS, 0, s>>>(p, merge_work);
+            attn_merge_kernel<<<dim3(n_merge_items, nkv), 256, 0, s>>>(p, merge_work);
             BW_LAUNCH_CHECK();
         }
     }

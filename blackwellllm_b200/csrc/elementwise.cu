@@ -17,7 +17,12 @@ __global__ void embed_gather_kernel(const WT* __restrict__ table, const int* __r
     if (id < 0 || id >= V) id = 0;  // the host rejects such ids before the launch
     const WT* row = table + (size_t)id * H;
     float* o = out + (size_t)t * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = bw::to_f32(row[c]);
+    const int c0 = blockIdx.y * blockDim.x * 4;   // each block copies 4 * blockDim elements of the row
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int c = c0 + k * blockDim.x + threadIdx.x;
+        if (c < H) o[c] = bw::to_f32(row[c]);
+    }
 }
 
 // ---------------------------------------------------------------- RMSNorm
@@ -119,47 +124,36 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
                                    int rotary_dim, OT* __restrict__ q_out, OT* __restrict__ k_pages,
                                    OT* __restrict__ v_pages, int nh, int nkv, int hd,
                                    int page_size, int num_pages) {
-    extern __shared__ float cs[];  // cos[rd/2], sin[rd/2]
-    const int t = blockIdx.x;
+    // one block per (token, head): no thread walks more than head_dim / blockDim elements
+    const int t = blockIdx.x, h = blockIdx.y;
     const int pos = positions[t];
     const int half = rotary_dim >> 1;
-    for (int j = threadIdx.x; j < half; j += blockDim.x) {
-        if (table) {
-            cs[j] = table[(size_t)t * rotary_dim + j];
-            cs[half + j] = table[(size_t)t * rotary_dim + half + j];
-        } else {
-            float s, c;
-            sincosf((float)pos * inv_freq[j], &s, &c);
-            cs[j] = c; cs[half + j] = s;
-        }
-    }
-    __syncthreads();
-    const int r = req_of_token[t];
-    const int page = block_table[(size_t)r * max_blocks + pos / page_size];
-    const int slot = pos % page_size;
-    const bool page_ok = page >= 0 && page < num_pages;
     const int row_w = (nh + 2 * nkv) * hd;
-    const IT* row = qkv + (size_t)t * row_w;
-    const int n_rot = (nh + nkv) * hd;
-    for (int e = threadIdx.x; e < row_w; e += blockDim.x) {
-        const int h = e / hd, c = e - h * hd;
-        float v = bw::to_f32(row[e]);
-        if (e < n_rot && c < rotary_dim) {
-            if (c < half) {
-                const float b = bw::to_f32(row[e + half]);
-                v = v * cs[c] - b * cs[half + c];
-            } else {
-                const float a = bw::to_f32(row[e - half]);
-                v = a * cs[half + (c - half)] + v * cs[c - half];
-            }
+    const IT* row = qkv + (size_t)t * row_w + (size_t)h * hd;
+    const bool rotate = h < nh + nkv;
+    int page = -1, slot = 0;
+    if (h >= nh) {
+        const int r = req_of_token[t];
+        page = block_table[(size_t)r * max_blocks + pos / page_size];
+        slot = pos % page_size;
+        if (page >= num_pages) page = -1;
+    }
+    for (int c = threadIdx.x; c < hd; c += blockDim.x) {
+        float v = bw::to_f32(row[c]);
+        if (rotate && c < rotary_dim) {
+            const int j = c < half ? c : c - half;
+            float sn, cs;
+            if (table) { cs = table[(size_t)t * rotary_dim + j]; sn = table[(size_t)t * rotary_dim + half + j]; }
+            else sincosf((float)pos * inv_freq[j], &sn, &cs);
+            if (c < half) v = v * cs - bw::to_f32(row[c + half]) * sn;
+            else v = bw::to_f32(row[c - half]) * sn + v * cs;
         }
         if (h < nh) {
-            q_out[(size_t)t * nh * hd + e] = bw::from_f32<OT>(v);
-        } else if (page_ok) {
+            q_out[((size_t)t * nh + h) * hd + c] = bw::from_f32<OT>(v);
+        } else if (page >= 0) {
             const bool is_k = h < nh + nkv;
             const int kvh = is_k ? h - nh : h - nh - nkv;
-            OT* dst = (is_k ? k_pages : v_pages) +
-                      (((size_t)page * nkv + kvh) * page_size + slot) * hd + c;
+            OT* dst = (is_k ? k_pages : v_pages) + (((size_t)page * nkv + kvh) * page_size + slot) * hd + c;
             *dst = bw::from_f32<OT>(v);
         }
     }
@@ -175,8 +169,9 @@ BW_EXPORT int bw_embed_gather(const void* table, int table_type, const int* ids,
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
-    if (table_type == BW_F32) embed_gather_kernel<float><<<T, threads, 0, s>>>(cp<float>(table), ids, out, H, V);
-    else if (table_type == BW_BF16) embed_gather_kernel<bf16><<<T, threads, 0, s>>>(cp<bf16>(table), ids, out, H, V);
+    const dim3 grid(T, (H + threads * 4 - 1) / (threads * 4));
+    if (table_type == BW_F32) embed_gather_kernel<float><<<grid, threads, 0, s>>>(cp<float>(table), ids, out, H, V);
+    else if (table_type == BW_BF16) embed_gather_kernel<bf16><<<grid, threads, 0, s>>>(cp<bf16>(table), ids, out, H, V);
     else return BW_ERR_BAD_ARG;
     BW_LAUNCH_CHECK();
     return 0;
@@ -232,9 +227,9 @@ BW_EXPORT int bw_rope_append(const void* qkv, int in_type, const int* positions,
     if (T <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = 256;
-    const size_t smem = (size_t)rotary_dim * sizeof(float);
-#define BW_RA(IT, OT) rope_append_kernel<IT, OT><<<T, threads, smem, s>>>(cp<IT>(qkv), positions, req_of_token, \
+    const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
+    const dim3 grid(T, nh + 2 * nkv);
+#define BW_RA(IT, OT) rope_append_kernel<IT, OT><<<grid, threads, 0, s>>>(cp<IT>(qkv), positions, req_of_token, \
         block_table, max_blocks, inv_freq, table, rotary_dim, mp<OT>(q_out), mp<OT>(k_pages), mp<OT>(v_pages), \
         nh, nkv, hd, page_size, num_pages)
     if (in_type == BW_F32 && out_type == BW_F32) BW_RA(float, float);

@@ -33,6 +33,7 @@ constexpr int THREADS = 192;
 constexpr int NUM_SMS = 148;
 constexpr int STAGING_BYTES = 4 * 32 * 33 * 4;          // one 32 x 33 float block per epilogue warp
 constexpr int SMEM_BUDGET = 226 * 1024 - STAGING_BYTES - 2048;
+constexpr int FUSED_REDUCE_MAX_TOKENS = 16;   // split-K sums inside the kernel up to this many tokens
 constexpr int SWIGLU_BLOCK = 16;   // gate/up features are interleaved in blocks of 16 rows of the weight
 
 __device__ int g_status = 0;  // 0 ok; else the code of the first wait that gave up
@@ -243,12 +244,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             __syncwarp();
             if (lane == 0) bw::mbar_arrive(tempty0 + 8 * acc);
 
-            if (part) {
-                // split-K: the warp that completes this (tile, quarter) last sums all partials
-                __threadfence();
+            if (part && ep.counters) {
+                // split-K, reduced here: the warp that completes this (tile, quarter) last sums all
+                // partials.  (Without counters a second kernel does the sums, in parallel: better for
+                // many tokens.)  The warp's writes happen before lane 0's fence and counter update.
                 __syncwarp();
                 int last = 0;
-                if (lane == 0) last = atomicAdd(&ep.counters[tile * 4 + quarter], 1) == ep.splits - 1;
+                if (lane == 0) {
+                    __threadfence();
+                    last = atomicAdd(&ep.counters[tile * 4 + quarter], 1) == ep.splits - 1;
+                }
                 last = __shfl_sync(0xffffffffu, last, 0);
                 if (last) {
                     __threadfence();
@@ -297,6 +302,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bw::tc_fence_before();
     __syncthreads();
     if (warp == 1) bw::tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// Split-K with many tokens: out = epilogue(sum over splits of partial), one thread per (token,
+// feature), splits added in order.  SwiGLU: one thread per (token, output feature) reads its gate
+// and up sums from the interleaved layout.
+__global__ void splitk_reduce_kernel(Epilogue ep) {
+    const size_t plane = (size_t)ep.tokens * ep.features;
+    const int width = ep.swiglu ? ep.features / 2 : ep.features;
+    const size_t total = (size_t)ep.tokens * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int token = (int)(i / width), j = (int)(i - (size_t)token * width);
+        if (ep.swiglu) {
+            const int fg = (j / SWIGLU_BLOCK) * 2 * SWIGLU_BLOCK + j % SWIGLU_BLOCK, fu = fg + SWIGLU_BLOCK;
+            float g = 0.f, u = 0.f;
+            for (int s = 0; s < ep.splits; ++s) {
+                g += ep.partial[(size_t)s * plane + (size_t)token * ep.features + fg];
+                u += ep.partial[(size_t)s * plane + (size_t)token * ep.features + fu];
+            }
+            ((bf16*)ep.out)[(size_t)token * ep.ldo + j] = __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+            continue;
+        }
+        float v = 0.f;
+        for (int s = 0; s < ep.splits; ++s) v += ep.partial[(size_t)s * plane + i];
+        if (ep.bias) v += ep.bias_type == BW_F32 ? ((const float*)ep.bias)[j] : __bfloat162float(((const bf16*)ep.bias)[j]);
+        const size_t off = (size_t)token * ep.ldo + j;
+        if (ep.out_type == BW_F32) {
+            float* o = (float*)ep.out + off;
+            *o = ep.accumulate ? *o + v : v;
+        } else {
+            ((bf16*)ep.out)[off] = __float2bfloat16_rn(v);
+        }
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -372,14 +409,18 @@ BW_EXPORT int bw_gemm_tc_plan(int M, int N, int K, long long workspace_elems, lo
     }
     *transposed = tr; *bn = b;
     const long long tiles = tr ? (long long)ceil_div(N, BM) * ceil_div(M, b) : (long long)ceil_div(M, BM) * ceil_div(N, b);
-    int best = 1; double best_score = 0;
-    for (int s = 1; s <= 16; ++s) {
-        if (s > 1 && (kb_total / s < 4 || (long long)s * M * N > workspace_elems || tiles * 4 > n_counters)) break;
-        const long long items = tiles * s;
-        const double balance = (double)items / ((double)ceil_div(items, NUM_SMS) * NUM_SMS);
-        const double extra = s > 1 ? 4.0 * s * M / (double)K : 0.0;   // partial traffic relative to the weights
-        const double score = balance / (1.0 + extra);
-        if (score > best_score * 1.03) { best_score = score; best = s; }
+    // Timings of the decode shapes on a B200 (back-to-back launches in a CUDA graph, cold weights)
+    // say: with at least one tile per SM do not split; with fewer, split so that one round of
+    // items just fills the SMs, keeping 8 or more k-blocks per item, and the float32 partial
+    // sums (2 * s * M * N * 4 bytes written and read) well below the weight bytes (N * K * 2).
+    int best = 1;
+    if (tiles < NUM_SMS) {
+        best = (int)(NUM_SMS / tiles);
+        if (best > kb_total / 8) best = kb_total / 8;
+        if (M > 64 && best > K / (8 * M)) best = K / (8 * M);
+        if (best > 16) best = 16;
+        while (best > 1 && ((long long)best * M * N > workspace_elems || tiles * 4 > n_counters)) --best;
+        if (best < 1) best = 1;
     }
     return best;
 }
@@ -422,18 +463,31 @@ BW_EXPORT int bw_gemm_tc(const void* x, const void* w, const void* bias, int bia
     if (!make_map(&ta, a_ptr, a_rows, K, a_ld, BM) || !make_map(&tb, b_ptr, b_rows, K, b_ld, bn)) return BW_ERR_DRIVER;
 
     Epilogue ep;
-    ep.out = out; ep.partial = splits > 1 ? workspace : nullptr; ep.counters = counters; ep.bias = bias; ep.ldo = ldo;
+    // few tokens: the last warp of each tile sums the splits inside the kernel; more: a second kernel
+    const bool fused_reduce = M <= FUSED_REDUCE_MAX_TOKENS;
+    ep.out = out; ep.partial = splits > 1 ? workspace : nullptr; ep.counters = fused_reduce ? counters : nullptr;
+    ep.bias = bias; ep.ldo = ldo;
     ep.out_type = out_type; ep.bias_type = bias_type; ep.accumulate = accumulate; ep.transposed = tr;
     ep.swiglu = swiglu; ep.tokens = M; ep.features = N; ep.splits = splits;
     const int num_work = tiles_a * tiles_b * splits;
+    int rc;
     switch (bn) {
-        case 16: return launch<16>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s);
-        case 32: return launch<32>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s);
-        case 64: return launch<64>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s);
-        case 128: return launch<128>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s);
-        case 256: return launch<256>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s);
+        case 16: rc = launch<16>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break;
+        case 32: rc = launch<32>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break;
+        case 64: rc = launch<64>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break;
+        case 128: rc = launch<128>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break;
+        case 256: rc = launch<256>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break;
         default: return BW_ERR_BAD_ARG;
     }
+    if (rc) return rc;
+    if (splits > 1 && !fused_reduce) {
+        const size_t total = (size_t)M * (swiglu ? N / 2 : N);
+        const size_t want = (total + 255) / 256;
+        const int blocks = (int)(want < (size_t)NUM_SMS * 8 ? want : (size_t)NUM_SMS * 8);
+        splitk_reduce_kernel<<<blocks, 256, 0, s>>>(ep);
+        BW_LAUNCH_CHECK();
+    }
+    return 0;
 }
 
 // Reads and clears the status word (synchronises the device).  0: no wait ever gave up.
