@@ -230,6 +230,8 @@ __device__ __forceinline__ void init_rows(const Params& p, RowState& st, int row
 // work item: (request, first token of the tile within the request's segment, -, -)
 __global__ void __launch_bounds__(THREADS)
 attn_rows_kernel(Params p, int toks_per_tile) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* q_tile = smem;                       // 64 rows
     uint8_t* kv = smem + BN * ROW_BYTES;          // [2 stages][K, V]
@@ -303,6 +305,8 @@ attn_rows_kernel(Params p, int toks_per_tile) {
 // work item: (request, slice, number of slices, item index for the partial buffers)
 __global__ void __launch_bounds__(THREADS)
 attn_keys_kernel(Params p) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* q_tile = smem;                       // 16 rows
     uint8_t* kv = smem + 16 * ROW_BYTES;          // [2 stages][K, V]
@@ -402,6 +406,8 @@ attn_keys_kernel(Params p) {
 constexpr int MAX_SLICES = 64;
 __global__ void __launch_bounds__(256)
 attn_merge_kernel(Params p, const int* merge_items) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     __shared__ float sm_m[MAX_SLICES * 16], sm_l[MAX_SLICES * 16];
     const int4 w = reinterpret_cast<const int4*>(merge_items)[blockIdx.x];
     const int r = w.x, n_slices = w.z, item = w.w, g = blockIdx.y;
@@ -467,15 +473,15 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
     p.scale_log2 = scale * 1.4426950408889634f;
     if (n_rows_items > 0) {
         p.work = rows_work;
-        attn_rows_kernel<<<dim3(n_rows_items, nkv), THREADS, SMEM_ROWS, s>>>(p, 64 / G);
+        bw::launch((attn_rows_kernel), dim3(dim3(n_rows_items, nkv)), dim3(THREADS), SMEM_ROWS, s, p, 64 / G);
         BW_LAUNCH_CHECK();
     }
     if (n_keys_items > 0) {
         p.work = keys_work;
-        attn_keys_kernel<<<dim3(n_keys_items, nkv), THREADS, SMEM_KEYS, s>>>(p);
+        bw::launch((attn_keys_kernel), dim3(dim3(n_keys_items, nkv)), dim3(THREADS), SMEM_KEYS, s, p);
         BW_LAUNCH_CHECK();
         if (n_merge_items > 0) {
-            attn_merge_kernel<<<dim3(n_merge_items, nkv), 256, 0, s>>>(p, merge_work);
+            bw::launch((attn_merge_kernel), dim3(dim3(n_merge_items, nkv)), dim3(256), 0, s, p, merge_work);
             BW_LAUNCH_CHECK();
         }
     }

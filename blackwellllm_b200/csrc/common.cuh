@@ -19,9 +19,39 @@
 #define BW_F32  0
 #define BW_BF16 1
 
+// Programmatic dependent launch: a kernel launched through bw::launch may start while the kernel
+// before it in the stream is still draining.  Such a kernel calls BW_PDL_TRIGGER() early (the next
+// kernel may start launching) and BW_PDL_WAIT() before its first access to memory that an earlier
+// kernel may write (everything but weights); the wait returns once all earlier kernels are
+// complete and their writes visible.  Both are no-ops for ordinary launches.  BW_PDL=0 in the
+// environment turns the early launch off.
+#define BW_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+#define BW_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
+
 #define BW_LAUNCH_CHECK() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) return (int)e__; } while (0)
 
+#include <stdlib.h>
+#include <utility>
+
 namespace bw {
+
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("BW_PDL"); v = (e && e[0] == '0') ? 0 : 1; }
+    return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -12,6 +12,8 @@ namespace {
 template <typename WT>
 __global__ void embed_gather_kernel(const WT* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, int V) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= V) id = 0;  // the host rejects such ids before the launch
@@ -32,6 +34,8 @@ template <typename WT, typename OT>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict__ w,
                                const int* __restrict__ rows, OT* __restrict__ out,
                                int H, float eps) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     __shared__ float scratch[32];
     const int i = blockIdx.x;
     const int src = rows ? rows[i] : i;
@@ -65,6 +69,8 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 template <typename WT, typename OT>
 __global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, const WT* __restrict__ w,
                                     const int* __restrict__ rows, OT* __restrict__ out, int H, float eps) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     __shared__ float scratch[32];
     const int i = blockIdx.x;
     const int src = rows ? rows[i] : i;
@@ -87,6 +93,8 @@ __global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, const WT* __res
 // in: [T, 2I] with gate in columns [0, I) and up in [I, 2I); out: [T, I].
 template <typename IT, typename OT>
 __global__ void swiglu_kernel(const IT* __restrict__ gu, OT* __restrict__ out, int I, size_t total) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I; const int c = (int)(idx - t * I);
@@ -106,6 +114,8 @@ __global__ void swiglu_kernel(const IT* __restrict__ gu, OT* __restrict__ out, i
 // All layers with the same rotary parameters share one table per step.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float* __restrict__ table, int rotary_dim, int T) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     const int half = rotary_dim >> 1;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * half) return;
@@ -124,6 +134,8 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
                                    int rotary_dim, OT* __restrict__ q_out, OT* __restrict__ k_pages,
                                    OT* __restrict__ v_pages, int nh, int nkv, int hd,
                                    int page_size, int num_pages) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     // one block per (token, head): no thread walks more than head_dim / blockDim elements
     const int t = blockIdx.x, h = blockIdx.y;
     const int pos = positions[t];
@@ -170,8 +182,8 @@ BW_EXPORT int bw_embed_gather(const void* table, int table_type, const int* ids,
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
     const dim3 grid(T, (H + threads * 4 - 1) / (threads * 4));
-    if (table_type == BW_F32) embed_gather_kernel<float><<<grid, threads, 0, s>>>(cp<float>(table), ids, out, H, V);
-    else if (table_type == BW_BF16) embed_gather_kernel<bf16><<<grid, threads, 0, s>>>(cp<bf16>(table), ids, out, H, V);
+    if (table_type == BW_F32) bw::launch((embed_gather_kernel<float>), dim3(grid), dim3(threads), 0, s, cp<float>(table), ids, out, H, V);
+    else if (table_type == BW_BF16) bw::launch((embed_gather_kernel<bf16>), dim3(grid), dim3(threads), 0, s, cp<bf16>(table), ids, out, H, V);
     else return BW_ERR_BAD_ARG;
     BW_LAUNCH_CHECK();
     return 0;
@@ -183,8 +195,8 @@ BW_EXPORT int bw_rmsnorm(const float* x, const void* w, int w_type, const int* r
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = H % 4 == 0 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
     const int threads = vec ? (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
-#define BW_RMS(WT, OT) do { if (vec) rmsnorm_vec4_kernel<WT, OT><<<n_rows, threads, 0, s>>>(x, cp<WT>(w), rows, mp<OT>(out), H, eps); \
-        else rmsnorm_kernel<WT, OT><<<n_rows, threads, 0, s>>>(x, cp<WT>(w), rows, mp<OT>(out), H, eps); } while (0)
+#define BW_RMS(WT, OT) do { if (vec) bw::launch((rmsnorm_vec4_kernel<WT, OT>), dim3(n_rows), dim3(threads), 0, s, x, cp<WT>(w), rows, mp<OT>(out), H, eps); \
+        else bw::launch((rmsnorm_kernel<WT, OT>), dim3(n_rows), dim3(threads), 0, s, x, cp<WT>(w), rows, mp<OT>(out), H, eps); } while (0)
     if (w_type == BW_F32 && out_type == BW_F32) BW_RMS(float, float);
     else if (w_type == BW_F32 && out_type == BW_BF16) BW_RMS(float, bf16);
     else if (w_type == BW_BF16 && out_type == BW_F32) BW_RMS(bf16, float);
@@ -201,9 +213,9 @@ BW_EXPORT int bw_swiglu(const void* gu, int in_type, void* out, int out_type, in
     const size_t total = (size_t)T * I;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-    if (in_type == BW_F32 && out_type == BW_F32) swiglu_kernel<float, float><<<blocks, threads, 0, s>>>(cp<float>(gu), mp<float>(out), I, total);
-    else if (in_type == BW_BF16 && out_type == BW_BF16) swiglu_kernel<bf16, bf16><<<blocks, threads, 0, s>>>(cp<bf16>(gu), mp<bf16>(out), I, total);
-    else if (in_type == BW_F32 && out_type == BW_BF16) swiglu_kernel<float, bf16><<<blocks, threads, 0, s>>>(cp<float>(gu), mp<bf16>(out), I, total);
+    if (in_type == BW_F32 && out_type == BW_F32) bw::launch((swiglu_kernel<float, float>), dim3(blocks), dim3(threads), 0, s, cp<float>(gu), mp<float>(out), I, total);
+    else if (in_type == BW_BF16 && out_type == BW_BF16) bw::launch((swiglu_kernel<bf16, bf16>), dim3(blocks), dim3(threads), 0, s, cp<bf16>(gu), mp<bf16>(out), I, total);
+    else if (in_type == BW_F32 && out_type == BW_BF16) bw::launch((swiglu_kernel<float, bf16>), dim3(blocks), dim3(threads), 0, s, cp<float>(gu), mp<bf16>(out), I, total);
     else return BW_ERR_BAD_ARG;
     BW_LAUNCH_CHECK();
     return 0;
@@ -214,7 +226,7 @@ BW_EXPORT int bw_rope_table(const int* positions, const float* inv_freq, float* 
     if (T <= 0 || rotary_dim <= 0) return 0;
     if (rotary_dim & 1) return BW_ERR_BAD_ARG;
     const int total = T * (rotary_dim / 2);
-    rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, table, rotary_dim, T);
+    bw::launch((rope_table_kernel), dim3((total + 255) / 256), dim3(256), 0, (cudaStream_t)stream, positions, inv_freq, table, rotary_dim, T);
     BW_LAUNCH_CHECK();
     return 0;
 }
@@ -229,7 +241,7 @@ BW_EXPORT int bw_rope_append(const void* qkv, int in_type, const int* positions,
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     const dim3 grid(T, nh + 2 * nkv);
-#define BW_RA(IT, OT) rope_append_kernel<IT, OT><<<grid, threads, 0, s>>>(cp<IT>(qkv), positions, req_of_token, \
+#define BW_RA(IT, OT) bw::launch((rope_append_kernel<IT, OT>), dim3(grid), dim3(threads), 0, s, cp<IT>(qkv), positions, req_of_token, \
         block_table, max_blocks, inv_freq, table, rotary_dim, mp<OT>(q_out), mp<OT>(k_pages), mp<OT>(v_pages), \
         nh, nkv, hd, page_size, num_pages)
     if (in_type == BW_F32 && out_type == BW_F32) BW_RA(float, float);

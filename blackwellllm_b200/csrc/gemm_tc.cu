@@ -51,7 +51,9 @@ struct Epilogue {
 template <int BN> __host__ __device__ constexpr int stages_for() {
     constexpr int per = A_BYTES + BN * BK * 2;
     constexpr int s = SMEM_BUDGET / per;
-    return s > 8 ? 8 : s;
+    // the narrowest tile (decode with up to 16 tokens) keeps 5 stages, so that two CTAs fit on an
+    // SM and the next product's CTAs can start loading weights while this one's drain
+    return BN <= 16 ? 5 : (s > 8 ? 8 : s);
 }
 
 // The lane holds the finished sums vals[0..N) of ONE feature for N consecutive tokens (token0 + c);
@@ -120,6 +122,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
 
+    BW_PDL_TRIGGER();   // the next kernel in the stream may start launching
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = bw::smem_u32(bars), empty0 = bw::smem_u32(bars + STAGES);
     const uint32_t tfull0 = bw::smem_u32(bars + 2 * STAGES), tempty0 = bw::smem_u32(bars + 2 * STAGES + 2);
@@ -146,6 +149,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            // In the transposed orientation A is the weight matrix, which no kernel writes: its tiles
+            // for the first stages are requested before the wait for the earlier kernels, whose
+            // results (the activations in B) are loaded after it.
+            int ahead = 0;
+            if (ep.transposed && blockIdx.x < num_work) {
+                const int w = blockIdx.x;
+                const int tile = w % tiles, split = w / tiles;
+                const int tile_a = tile % tiles_a;
+                const int kb0 = split * kb_per_split;
+                const int nkb = min(kb_total, kb0 + kb_per_split) - kb0;
+                ahead = min(nkb, STAGES);
+                for (int i = 0; i < ahead; ++i) {
+                    bw::mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                    bw::tma_load_2d(bw::smem_u32(smem + i * STAGE_BYTES), &tmA, full0 + 8 * i, (kb0 + i) * BK, tile_a * BM);
+                }
+            }
+            BW_PDL_WAIT();
             for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
                 const int tile = w % tiles, split = w / tiles;
                 const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;
@@ -154,9 +174,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int i = 0; i < nkb; ++i, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
+                    const uint32_t a_dst = bw::smem_u32(smem + s * STAGE_BYTES);
+                    if ((int)it < ahead) {   // A of this stage is already on its way
+                        bw::tma_load_2d(a_dst + A_BYTES, &tmB, full0 + 8 * s, (kb0 + i) * BK, tile_b * BN);
+                        continue;
+                    }
                     if (!bw::mbar_wait(empty0 + 8 * s, ph ^ 1, &g_status, 1)) { ok = false; break; }
                     bw::mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                    const uint32_t a_dst = bw::smem_u32(smem + s * STAGE_BYTES);
                     bw::tma_load_2d(a_dst, &tmA, full0 + 8 * s, (kb0 + i) * BK, tile_a * BM);
                     bw::tma_load_2d(a_dst + A_BYTES, &tmB, full0 + 8 * s, (kb0 + i) * BK, tile_b * BN);
                 }
@@ -193,6 +217,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         }
     } else {
+        BW_PDL_WAIT();   // the outputs, the split-K scratch and its counters belong to earlier kernels until here
         const int quarter = warp & 3;              // TMEM lanes 32 * quarter .. + 31
         float* stage = staging + (warp - 2) * (32 * 33);
         const int a_rows = ep.transposed ? ep.features : ep.tokens;
@@ -308,6 +333,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // feature), splits added in order.  SwiGLU: one thread per (token, output feature) reads its gate
 // and up sums from the interleaved layout.
 __global__ void splitk_reduce_kernel(Epilogue ep) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     const size_t plane = (size_t)ep.tokens * ep.features;
     const int width = ep.swiglu ? ep.features / 2 : ep.features;
     const size_t total = (size_t)ep.tokens * width;
@@ -379,7 +406,7 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const Epilogue& ep, int k
         attr_done = true;
     }
     const int grid = num_work < NUM_SMS ? num_work : NUM_SMS;
-    gemm_tc_kernel<BN><<<grid, THREADS, smem, s>>>(a, b, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work);
+    bw::launch((gemm_tc_kernel<BN>), dim3(grid), dim3(THREADS), smem, s, a, b, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work);
     BW_LAUNCH_CHECK();
     return 0;
 }
@@ -484,7 +511,7 @@ BW_EXPORT int bw_gemm_tc(const void* x, const void* w, const void* bias, int bia
         const size_t total = (size_t)M * (swiglu ? N / 2 : N);
         const size_t want = (total + 255) / 256;
         const int blocks = (int)(want < (size_t)NUM_SMS * 8 ? want : (size_t)NUM_SMS * 8);
-        splitk_reduce_kernel<<<blocks, 256, 0, s>>>(ep);
+        bw::launch((splitk_reduce_kernel), dim3(blocks), dim3(256), 0, s, ep);
         BW_LAUNCH_CHECK();
     }
     return 0;

@@ -55,6 +55,8 @@ __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const float* __restrict__ u, int* __restrict__ out,
               int V, size_t ld) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
     __shared__ float sf[32];
     __shared__ int si[32];
     __shared__ float seg[THREADS];
@@ -132,7 +134,7 @@ BW_EXPORT int bw_sample(const float* logits, const float* temperature, const flo
     if (R <= 0) return 0;
     if (V <= 0 || ld < V) return BW_ERR_BAD_ARG;
     if (temperature && !u) return BW_ERR_BAD_ARG;
-    sample_kernel<<<R, THREADS, 0, (cudaStream_t)stream>>>(logits, temperature, top_p, u, out, V, (size_t)ld);
+    bw::launch((sample_kernel), dim3(R), dim3(THREADS), 0, (cudaStream_t)stream, logits, temperature, top_p, u, out, V, (size_t)ld);
     BW_LAUNCH_CHECK();
     return 0;
 }
