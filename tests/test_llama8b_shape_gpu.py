@@ -1,0 +1,104 @@
+"""The 8B-class shape (Llama-3.1-8B layer sizes: hidden 4096, 32 heads, 8 kv heads, head 128,
+intermediate 14336, vocabulary 128256, rope theta 500000 with llama3 scaling), two layers,
+random weights N(0, 0.02): logits of the engine against the plain implementation, in 32-bit
+and in bfloat16, whole, in portions, token by token and mixed; and rotation at far positions."""
+import pytest
+import torch
+
+import tiny
+from plain_model import plain_logits
+
+pytestmark = pytest.mark.gpu
+
+RAW = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "intermediate_size": 14336, "num_hidden_layers": 2, "vocab_size": 128256,
+    "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+}
+
+
+@pytest.fixture(scope="module")
+def weights():
+    from blackwellllm_b200.weights.random_init import model_param_specs, random_tensors
+    W = random_tensors(model_param_specs(RAW), seed=3, std=0.02, dtype=torch.bfloat16)
+    return W  # bfloat16 values: both dtypes of the engine and the plain implementation use the same numbers
+
+
+@pytest.fixture(scope="module")
+def case(weights):
+    ids_a = tiny.prompt(75, RAW["vocab_size"], 11)
+    ids_b = tiny.prompt(40, RAW["vocab_size"], 12)
+    with torch.no_grad():
+        ref = {"a": plain_logits(RAW, weights, ids_a, dtype=torch.float64),
+               "b": plain_logits(RAW, weights, ids_b, dtype=torch.float64)}
+    return {"a": ids_a, "b": ids_b}, ref
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_8b_shape_every_way_of_cutting(weights, case, dtype):
+    from blackwellllm_b200 import Engine, StepEntry
+    ids, ref = case
+    eng = Engine.from_tensors(RAW, weights, dtype=dtype, page_size=16, max_tokens=512, max_requests=4)
+    tol = tiny.TOL[dtype]
+
+    def check(rows, rid, start):
+        r = ref[rid][start:start + rows.shape[0]]
+        err = float((rows.double().cpu() - r).abs().max()) / float(ref[rid].abs().max())
+        assert err <= tol, (rid, start, err)
+
+    # whole
+    a = ids["a"]
+    check(eng.step([StepEntry("w", a, list(range(len(a))))]), "a", 0)
+    eng.end_request("w")
+    # portions of changing size, then token by token
+    at = 0
+    for n in (17, 2, 30, 3):
+        check(eng.step([StepEntry("p", a[at:at + n], list(range(n)))]), "a", at)
+        at += n
+    while at < len(a):
+        check(eng.step([StepEntry("p", [a[at]], [0])]), "a", at)
+        at += 1
+    # mixed: b's prompt in two portions beside a's decode tokens (request "p" rewound by 10 tokens)
+    eng.cache.truncate("p", len(a) - 10)
+    b = ids["b"]
+    out = eng.step([StepEntry("p", [a[-10]], [0]), StepEntry("q", b[:25], list(range(25)))])
+    check(out[:1], "a", len(a) - 10)
+    check(out[1:], "b", 0)
+    out = eng.step([StepEntry("q", b[25:], list(range(15))), StepEntry("p", [a[-9]], [0])])
+    check(out[:15], "b", 25)
+    check(out[15:], "a", len(a) - 9)
+
+
+def test_rope_scaling_at_far_positions():
+    """llama3 scaling and theta 500000 at positions up to 16,640 (where float32 angles are coarse):
+    rotated queries and keys of the engine's kernel against the plain rotation."""
+    from blackwellllm_b200.config.specs import Llama3RopeScaling, RopeSpec
+    from blackwellllm_b200.kernels import ops
+    from blackwellllm_b200.parts.rope import rotary_inv_freq
+    from plain_model import plain_inv_freq, plain_rope
+    dev = "cuda:0"
+    hd, nh, nkv = 128, 4, 2
+    positions = [0, 1, 8191, 8192, 12345, 16639]
+    T = len(positions)
+    inv = rotary_inv_freq(500000.0, hd, Llama3RopeScaling(8.0, 1.0, 4.0, 8192)).to(dev)
+    g = torch.Generator().manual_seed(0)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g)
+    pos = torch.tensor(positions, dtype=torch.int32, device=dev)
+    pages = 16640 // 16 + 1
+    kp = torch.zeros(pages, nkv, 16, hd, device=dev)
+    vp = torch.zeros_like(kp)
+    table = torch.arange(pages, dtype=torch.int32, device=dev).repeat(T, 1)
+    req = torch.arange(T, dtype=torch.int32, device=dev)
+    tab = ops.rope_table(pos, inv, hd)
+    q = ops.rope_append(qkv.to(dev), pos, req, table, inv, hd, kp, vp, nh, nkv, hd, table=tab)
+    x = qkv.double().view(T, nh + 2 * nkv, hd)
+    ref_inv = plain_inv_freq(hd, 500000.0, (8.0, 1.0, 4.0, 8192))
+    q_ref = plain_rope(x[:, :nh], torch.tensor(positions), ref_inv).reshape(T, nh * hd)
+    k_ref = plain_rope(x[:, nh:nh + nkv], torch.tensor(positions), ref_inv)
+    assert float((q.double().cpu() - q_ref).abs().max()) < 1e-5
+    for t, p in enumerate(positions):
+        got = kp[p // 16, :, p % 16].double().cpu()
+        assert float((got - k_ref[t]).abs().max()) < 1e-5
