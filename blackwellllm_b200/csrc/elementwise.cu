@@ -126,6 +126,8 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     table[(size_t)t * rotary_dim + half + j] = s;
 }
 
+constexpr int ROPE_HPB = 8;   // heads per block of rope_append_kernel
+
 template <typename IT, typename OT>
 __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __restrict__ positions,
                                    const int* __restrict__ req_of_token,
@@ -136,37 +138,49 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
                                    int page_size, int num_pages) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
-    // one block per (token, head): no thread walks more than head_dim / blockDim elements
-    const int t = blockIdx.x, h = blockIdx.y;
+    // A block takes ROPE_HPB heads of one token; a thread takes one channel of each of them: the
+    // loads of the heads are independent and in flight together, the angle is looked up once.
+    const int t = blockIdx.x, h0 = blockIdx.y * ROPE_HPB;
+    const int n_heads = nh + 2 * nkv;
     const int pos = positions[t];
     const int half = rotary_dim >> 1;
-    const int row_w = (nh + 2 * nkv) * hd;
-    const IT* row = qkv + (size_t)t * row_w + (size_t)h * hd;
-    const bool rotate = h < nh + nkv;
+    const IT* row = qkv + (size_t)t * n_heads * hd;
     int page = -1, slot = 0;
-    if (h >= nh) {
+    if (h0 + ROPE_HPB > nh) {   // this block holds key or value heads
         const int r = req_of_token[t];
         page = block_table[(size_t)r * max_blocks + pos / page_size];
         slot = pos % page_size;
         if (page >= num_pages) page = -1;
     }
     for (int c = threadIdx.x; c < hd; c += blockDim.x) {
-        float v = bw::to_f32(row[c]);
-        if (rotate && c < rotary_dim) {
+        float sn = 0.f, cs = 1.f;
+        const bool rot_c = c < rotary_dim;
+        if (rot_c) {
             const int j = c < half ? c : c - half;
-            float sn, cs;
             if (table) { cs = table[(size_t)t * rotary_dim + j]; sn = table[(size_t)t * rotary_dim + half + j]; }
             else sincosf((float)pos * inv_freq[j], &sn, &cs);
-            if (c < half) v = v * cs - bw::to_f32(row[c + half]) * sn;
-            else v = bw::to_f32(row[c - half]) * sn + v * cs;
+            if (c < half) sn = -sn;   // first half: x cos - partner sin; second half: partner sin + x cos
         }
-        if (h < nh) {
-            q_out[((size_t)t * nh + h) * hd + c] = bw::from_f32<OT>(v);
-        } else if (page >= 0) {
-            const bool is_k = h < nh + nkv;
-            const int kvh = is_k ? h - nh : h - nh - nkv;
-            OT* dst = (is_k ? k_pages : v_pages) + (((size_t)page * nkv + kvh) * page_size + slot) * hd + c;
-            *dst = bw::from_f32<OT>(v);
+        const int pc = rot_c ? (c < half ? c + half : c - half) : c;
+        float v[ROPE_HPB], w[ROPE_HPB];
+#pragma unroll
+        for (int k = 0; k < ROPE_HPB; ++k) {
+            const int h = h0 + k;
+            v[k] = h < n_heads ? bw::to_f32(row[(size_t)h * hd + c]) : 0.f;
+            w[k] = (h < nh + nkv && rot_c) ? bw::to_f32(row[(size_t)h * hd + pc]) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < ROPE_HPB; ++k) {
+            const int h = h0 + k;
+            if (h >= n_heads) break;
+            const float o = (h < nh + nkv && rot_c) ? v[k] * cs + w[k] * sn : v[k];
+            if (h < nh) {
+                q_out[((size_t)t * nh + h) * hd + c] = bw::from_f32<OT>(o);
+            } else if (page >= 0) {
+                const bool is_k = h < nh + nkv;
+                const int kvh = is_k ? h - nh : h - nh - nkv;
+                (is_k ? k_pages : v_pages)[(((size_t)page * nkv + kvh) * page_size + slot) * hd + c] = bw::from_f32<OT>(o);
+            }
         }
     }
 }
@@ -239,8 +253,8 @@ BW_EXPORT int bw_rope_append(const void* qkv, int in_type, const int* positions,
     if (T <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
-    const dim3 grid(T, nh + 2 * nkv);
+    const int threads = hd >= 256 ? 256 : (hd >= 128 ? 128 : (hd >= 64 ? 64 : 32));
+    const dim3 grid(T, (nh + 2 * nkv + ROPE_HPB - 1) / ROPE_HPB);
 #define BW_RA(IT, OT) bw::launch((rope_append_kernel<IT, OT>), dim3(grid), dim3(threads), 0, s, cp<IT>(qkv), positions, req_of_token, \
         block_table, max_blocks, inv_freq, table, rotary_dim, mp<OT>(q_out), mp<OT>(k_pages), mp<OT>(v_pages), \
         nh, nkv, hd, page_size, num_pages)

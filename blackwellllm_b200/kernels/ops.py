@@ -387,17 +387,17 @@ _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_vo
 _TARGET_CTAS = 148 * 4
 
 
-def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128):
+def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128, rows_tile: int = 64):
     """Work lists of the tensor-core attention for this batch and group size, made
     once per step and shared by all layers: segments of more than 16 stacked rows
     (tokens x heads of a group) are cut into 64-row tiles; the others (decode tokens)
     are cut into key slices so that the GPU is filled.  With ``batch.static_bound``
     (graph replay) the number of slices depends on that bound, not on the lengths."""
-    key = ("attn_work", G, nkv, window, hd)
+    key = ("attn_work", G, nkv, window, hd, rows_tile)
     cached = batch.static_extras.get(key)
     if cached is not None:
         return cached
-    tpt = 64 // G
+    tpt = rows_tile // G   # tokens of one tile of stacked rows
     rows_items, keys_items, merge_items = [], [], []
     small = [r for r in range(batch.R) if batch.h_q_len[r] * G <= 16]
     # CTAs of the key-slice kernel that fit on the GPU at once (shared memory bound)
@@ -422,6 +422,8 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
         if n > 1:
             merge_items.append((r, 0, n, total_slices))
         total_slices += n
+    # the tiles with the most keys to walk (the latest tokens) go first, so the last wave is light
+    rows_items.sort(key=lambda it: -(batch.h_q_start[it[0]] + it[1]))
     dev = batch.token_ids.device
 
     def up(items):
@@ -446,15 +448,53 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     G = nh // nkv
     if G > 16:
         raise KernelError(f"attention: {G} query heads per kv head exceed the kernel's limit of 16")
-    rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices = attention_work(batch, G, nkv, window, hd)
+    # prompt portions: the tcgen05 kernel (128-row tiles) where it takes the geometry, else mma.sync (64-row tiles)
+    use_tc = attention_tc_supports(hd, G, page_size)
+    rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices = attention_work(
+        batch, G, nkv, window, hd, rows_tile=128 if use_tc else 64)
     out = torch.empty_like(q)
     part_o = part_ml = None
     if n_merge:
         part_o = torch.empty((slices * nkv * 16, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((slices * nkv * 16, 2), dtype=torch.float32, device=q.device)
+    if use_tc and n_rows:
+        tc = _fn("attention_tc", "bw_attention_tc", _ATTN_TC_ARGS, macros={"HEAD_DIM": hd})
+        _check(tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
+                  _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, q.shape[0],
+                  nh, nkv, page_size, num_pages, int(window or 0), float(scale), _stream()), "attention_tc")
+        n_rows = 0
+        if not n_keys:
+            return out
     fn = _fn("attention_mma", "bw_attention_mma", _ATTN_MMA_ARGS, macros={"HEAD_DIM": hd})
     _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
               _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, _ptr(keys_w),
               n_keys, _ptr(merge_w), n_merge, _ptr(part_o), _ptr(part_ml), nh, nkv, page_size, num_pages,
               int(window or 0), float(scale), _stream()), "attention_mma")
     return out
+
+
+_ATTN_TC_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+
+
+def attention_tc_supports(hd: int, G: int, page_size: int) -> bool:
+    """Whether the tcgen05 prompt-attention kernel takes this geometry (head size a multiple of 64,
+    pages of 8, 16, 32 or 64 tokens).  BW_ATTN_TC=0 in the environment keeps the mma.sync kernel."""
+    import os
+    if os.environ.get("BW_ATTN_TC", "1") == "0":
+        return False
+    return hd % 64 == 0 and hd <= 256 and G <= 128 and page_size in (8, 16, 32, 64)
+
+
+def attention_tc_status() -> int:
+    """0 if no bounded wait in the tcgen05 attention kernels ever gave up (synchronises the device)."""
+    total = 0
+    for key, lib in list(_loaded_libs().items()):
+        if key.startswith("attention_tc"):
+            lib.bw_attention_tc_status.restype = c_int
+            total |= int(lib.bw_attention_tc_status())
+    return total
+
+
+def _loaded_libs():
+    from . import build
+    return build._loaded
