@@ -21,6 +21,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..parts.base import FixedStateRequest, PagedKVRequest
@@ -58,6 +59,19 @@ class _Request:
     # per group: block table (page id, or -1 once given back) and first block still held
     blocks: List[List[int]] = field(default_factory=list)
     first_live: List[int] = field(default_factory=list)
+    # int32 mirrors of `blocks` (with spare capacity), so that packing a step's batch is a memory copy
+    mirrors: List[np.ndarray] = field(default_factory=list)
+
+    def sync_mirror(self, gi: int, start: int = 0) -> None:
+        """Copies blocks[gi][start:] into the mirror, growing it if needed."""
+        n = len(self.blocks[gi])
+        m = self.mirrors[gi]
+        if n > m.shape[0]:
+            grown = np.full(max(n, 2 * m.shape[0], 64), -1, dtype=np.int32)
+            grown[:start] = m[:start]
+            self.mirrors[gi] = m = grown
+        if n > start:
+            m[start:n] = self.blocks[gi][start:n]
 
 
 class CacheManager:
@@ -132,7 +146,8 @@ class CacheManager:
         for sv in self._states:
             if sv.state is not None:
                 sv.state[slot].zero_()
-        self._requests[rid] = _Request(slot, 0, [[] for _ in self.groups], [0] * len(self.groups))
+        self._requests[rid] = _Request(slot, 0, [[] for _ in self.groups], [0] * len(self.groups),
+                                       [np.full(64, -1, dtype=np.int32) for _ in self.groups])
         return slot
 
     def _first_needed_block(self, grp: _Group, q_start: int) -> int:
@@ -161,7 +176,10 @@ class CacheManager:
             if n > g.allocator.num_free:
                 raise OutOfPages(f"request {rid!r} needs {n} more pages, {g.allocator.num_free} are free")
         for gi, (n, g) in enumerate(zip(need, self.groups)):
-            rq.blocks[gi].extend(g.allocator.allocate(n))
+            if n:
+                had = len(rq.blocks[gi])
+                rq.blocks[gi].extend(g.allocator.allocate(n))
+                rq.sync_mirror(gi, had)
         old = rq.length
         rq.length += n_new
         return old
@@ -181,6 +199,7 @@ class CacheManager:
                 g.allocator.free(pages)
                 for i in range(first, keep_from):
                     rq.blocks[gi][i] = -1
+                rq.mirrors[gi][first:keep_from] = -1
                 rq.first_live[gi] = keep_from
                 freed += len(pages)
         return freed
@@ -218,6 +237,11 @@ class CacheManager:
 
     def block_table(self, rid, group: int) -> List[int]:
         return self._requests[rid].blocks[group]
+
+    def block_row(self, rid, group: int) -> np.ndarray:
+        """The same as an int32 array (a view: valid until the request changes)."""
+        rq = self._requests[rid]
+        return rq.mirrors[group][:len(rq.blocks[group])]
 
     # ------------------------------------------------------------------ accounting
     def free_pages(self) -> List[int]:

@@ -108,18 +108,28 @@ class BatchBuilder:
         a_cu, a_qs, a_kv, a_sl = take(R + 1), take(R), take(R), take(R)
         a_lr = take(n_want)
         a_bt = {g: take(R * w) for g, w in widths.items()}
-        t = 0
-        h[a_cu[0]] = 0
-        for r, (rid, toks, q_start, kv_len, slot) in enumerate(segments):
-            n = len(toks)
-            h[a_tok[0] + t: a_tok[0] + t + n] = toks
-            h[a_pos[0] + t: a_pos[0] + t + n] = range(q_start, q_start + n)
-            h[a_req[0] + t: a_req[0] + t + n] = r
-            t += n
-            h[a_cu[0] + r + 1] = t
-            h[a_qs[0] + r] = q_start
-            h[a_kv[0] + r] = kv_len
-            h[a_sl[0] + r] = slot
+        import numpy as np
+        q_lens = np.fromiter((len(sg[1]) for sg in segments), dtype=np.int32, count=R)
+        q_starts = np.fromiter((sg[2] for sg in segments), dtype=np.int32, count=R)
+        cu = np.zeros(R + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=cu[1:])
+        h[a_cu[0]:a_cu[1]] = cu
+        h[a_qs[0]:a_qs[1]] = q_starts
+        h[a_kv[0]:a_kv[1]] = np.fromiter((sg[3] for sg in segments), dtype=np.int32, count=R)
+        h[a_sl[0]:a_sl[1]] = np.fromiter((sg[4] for sg in segments), dtype=np.int32, count=R)
+        if T == R:   # one token per request (a decode step): no per-segment loops
+            h[a_tok[0]:a_tok[1]] = np.fromiter((sg[1][0] for sg in segments), dtype=np.int32, count=R)
+            h[a_pos[0]:a_pos[1]] = q_starts
+            h[a_req[0]:a_req[1]] = np.arange(R, dtype=np.int32)
+        else:
+            req = np.repeat(np.arange(R, dtype=np.int32), q_lens)
+            h[a_req[0]:a_req[1]] = req
+            h[a_pos[0]:a_pos[1]] = np.arange(T, dtype=np.int32) - cu[:-1][req] + q_starts[req]
+            t = 0
+            for sg in segments:
+                n = len(sg[1])
+                h[a_tok[0] + t: a_tok[0] + t + n] = sg[1]
+                t += n
         if n_want:
             h[a_lr[0]:a_lr[1]] = logit_rows
         for g, rows in block_rows.items():

@@ -202,7 +202,7 @@ class Engine:
                              self.cache.slot(e.rid)))
             rows.extend(t0 + int(w) for w in e.want)
             t0 += len(e.tokens)
-        block_rows = {g: [self.cache.block_table(e.rid, g) for e in entries] for g in range(n_groups)}
+        block_rows = {g: [self.cache.block_row(e.rid, g) for e in entries] for g in range(n_groups)}
         return self._builder.build(segments, rows, block_rows, min_blocks=min_blocks, into=into)
 
     # A decode-only step (one token and one wanted place per request) has the same
