@@ -15,7 +15,7 @@
 //     merged at the end; slices are merged by attn_merge_kernel.  For decode tokens.
 // Keys beyond the request's length and pages the block table no longer holds are
 // zero-filled in shared memory and masked, so stale cache contents never matter.
-#include "common.cuh"
+#include "tcgen05.cuh"   // mbarrier and TMA helpers (and common.cuh)
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<multiple of 16>"
@@ -34,6 +34,7 @@ constexpr int ROW_BYTES = HD * 2 + 16; // padded row: ldmatrix rows land in dist
 constexpr int KSTEPS = HD / 16;
 constexpr int CPR = HD / 8;            // 16-byte chunks per row
 constexpr int TILE_BYTES = BN * ROW_BYTES;
+constexpr int SMEM_KEYS_MERGE_BYTES = (2 * NWARPS * 16 + NWARPS * 16 * HD) * 4;   // finish_keys
 
 struct Params {
     const bf16* q; const bf16* k_pages; const bf16* v_pages; bf16* out;
@@ -67,6 +68,9 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// barrier among the 128 compute threads only (a TMA producer warp, where there is one, stays out)
+__device__ __forceinline__ void sync_compute_warps() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -301,6 +305,56 @@ attn_rows_kernel(Params p, int toks_per_tile) {
     }
 }
 
+// Merges the four warps of a key-slice CTA (each saw a quarter of every tile's keys) through shared
+// memory and writes the result: the final rows if the request has one slice, else this slice's
+// partial sums.  `smem` may overlay the tiles: the caller's loop has ended.
+__device__ __forceinline__ void finish_keys(const Params& p, const RowState& st, const float (&o)[HD / 8][4],
+                                            uint8_t* smem, int r, int g, int slice, int n_slices, int item, int n_rows) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* ms = reinterpret_cast<float*>(smem);            // [4][16]
+    float* ls = ms + NWARPS * 16;                          // [4][16]
+    float* os = ls + NWARPS * 16;                          // [4][16][HD]
+    sync_compute_warps();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float l = st.l[h];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = (lane >> 2) + 8 * h;
+        if ((lane & 3) == 0) { ms[warp * 16 + row] = st.m[h]; ls[warp * 16 + row] = l; }
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) {
+            float* d = os + ((size_t)(warp * 16 + row)) * HD + j * 8 + 2 * (lane & 3);
+            d[0] = o[j][2 * h]; d[1] = o[j][2 * h + 1];
+        }
+    }
+    sync_compute_warps();
+    for (int idx = threadIdx.x; idx < n_rows * HD; idx += THREADS) {
+        const int row = idx / HD, c = idx - row * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int wv = 0; wv < NWARPS; ++wv) M = fmaxf(M, ms[wv * 16 + row]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < NWARPS; ++wv) {
+            const float mw = ms[wv * 16 + row];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            acc += os[((size_t)(wv * 16 + row)) * HD + c] * f;
+            L += ls[wv * 16 + row] * f;
+        }
+        const int tok = row / p.G, hg = row - tok * p.G;
+        if (n_slices == 1) {
+            p.out[((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + c] =
+                __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            // `item` counts the slices of all earlier items, so every (item, kv head, slice) has its own slot
+            const size_t pr = ((size_t)item * p.nkv + (size_t)g * n_slices + slice) * 16 + row;
+            p.part_o[pr * HD + c] = acc;
+            if (c == 0) { p.part_ml[pr * 2] = M; p.part_ml[pr * 2 + 1] = L; }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // work item: (request, slice, number of slices, item index for the partial buffers)
 __global__ void __launch_bounds__(THREADS)
@@ -356,50 +410,214 @@ attn_keys_kernel(Params p) {
             __syncthreads();
         }
     }
-    // merge the four warps (each saw a quarter of every tile's keys) through shared memory
-    float* ms = reinterpret_cast<float*>(smem);            // [4][16]
-    float* ls = ms + NWARPS * 16;                          // [4][16]
-    float* os = ls + NWARPS * 16;                          // [4][16][HD]
-    __syncthreads();
+    finish_keys(p, st, o, smem, r, g, slice, n_slices, item, n_rows);
+}
+
+#if HEAD_DIM % 64 == 0
+// ---------------------------------------------------------------------------------------------
+// The same key-slice kernel with the K and V tiles brought in by TMA: one box per page and
+// 128-byte column slice (a single instruction per 2 KB instead of 128 cp.async), 128-byte
+// swizzle instead of padded rows, completion on an mbarrier.  Head sizes that are multiples of
+// 64 and pages of 8, 16, 32 or 64 tokens.
+constexpr int NSL = HD / 64;             // column slices
+constexpr int SLICE_BYTES = BN * 128;    // one slice of a tile: 64 keys x 128 bytes
+constexpr int TMA_TILE = NSL * SLICE_BYTES;
+
+__device__ int g_tma_status = 0;
+
+template <int NK>
+__device__ __forceinline__ void process_keys_swz(const uint32_t (&qf)[KSTEPS][4], const uint8_t* k_tile,
+                                                 const uint8_t* v_tile, int k_off, int key_pos0, bool need_mask,
+                                                 float scale_log2, RowState& st, float (&o)[HD / 8][4]) {
+    const int lane = threadIdx.x & 31, x7 = lane & 7;
+    float s[NK / 8][4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        float l = st.l[h];
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
-        const int row = (lane >> 2) + 8 * h;
-        if ((lane & 3) == 0) { ms[warp * 16 + row] = st.m[h]; ls[warp * 16 + row] = l; }
+    for (int j = 0; j < NK / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+    // row & 7 == lane & 7 for every row this lane addresses (all other terms are multiples of 8)
+    const uint32_t kb = smem_u32(k_tile) + (k_off + x7 + 8 * (lane >> 4)) * 128;
 #pragma unroll
-        for (int j = 0; j < HD / 8; ++j) {
-            float* d = os + ((size_t)(warp * 16 + row)) * HD + j * 8 + 2 * (lane & 3);
-            d[0] = o[j][2 * h]; d[1] = o[j][2 * h + 1];
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int chunk = ks * 2 + ((lane >> 3) & 1);
+        const uint32_t col = (chunk >> 3) * SLICE_BYTES + (((chunk & 7) ^ x7) << 4);
+#pragma unroll
+        for (int nb = 0; nb < NK / 16; ++nb) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(kb + nb * 16 * 128 + col, b0, b1, b2, b3);
+            mma_bf16(s[2 * nb], qf[ks], b0, b1);
+            mma_bf16(s[2 * nb + 1], qf[ks], b2, b3);
         }
     }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < n_rows * HD; idx += THREADS) {
-        const int row = idx / HD, c = idx - row * HD;
-        float M = -INFINITY;
+    float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int wv = 0; wv < NWARPS; ++wv) M = fmaxf(M, ms[wv * 16 + row]);
-        float acc = 0.f, L = 0.f;
+    for (int j = 0; j < NK / 8; ++j) {
 #pragma unroll
-        for (int wv = 0; wv < NWARPS; ++wv) {
-            const float mw = ms[wv * 16 + row];
-            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-            acc += os[((size_t)(wv * 16 + row)) * HD + c] * f;
-            L += ls[wv * 16 + row] * f;
+        for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            float v = s[j][e] * scale_log2;
+            if (need_mask) {
+                const int kp = key_pos0 + k_off + j * 8 + 2 * (lane & 3) + (e & 1);
+                if (kp > st.qpos[h] || kp < st.lo[h]) v = -INFINITY;
+            }
+            s[j][e] = v;
+            mx[h] = fmaxf(mx[h], v);
         }
-        const int tok = row / p.G, hg = row - tok * p.G;
-        if (n_slices == 1) {
-            p.out[((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + c] =
-                __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-        } else {
-            // `item` counts the slices of all earlier items, so every (item, kv head, slice) has its own slot
-            const size_t pr = ((size_t)item * p.nkv + (size_t)g * n_slices + slice) * 16 + row;
-            p.part_o[pr * HD + c] = acc;
-            if (c == 0) { p.part_ml[pr * 2] = M; p.part_ml[pr * 2 + 1] = L; }
+    }
+    float corr[2], mu[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(st.m[h], mx[h]);
+        mu[h] = m_new == -INFINITY ? 0.f : m_new;
+        corr[h] = exp2f(st.m[h] - mu[h]);
+        st.m[h] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float pv = exp2f(s[j][e] - mu[e >> 1]);
+            s[j][e] = pv;
+            sum[e >> 1] += pv;
+        }
+    }
+    st.l[0] = st.l[0] * corr[0] + sum[0];
+    st.l[1] = st.l[1] * corr[1] + sum[1];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) { o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1]; }
+    const uint32_t vb = smem_u32(v_tile) + (k_off + x7 + 8 * ((lane >> 3) & 1)) * 128;
+#pragma unroll
+    for (int kk = 0; kk < NK / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int nb = 0; nb < HD / 16; ++nb) {
+            const int chunk = nb * 2 + (lane >> 4);
+            const uint32_t col = (chunk >> 3) * SLICE_BYTES + (((chunk & 7) ^ x7) << 4);
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t(vb + kk * 16 * 128 + col, b0, b1, b2, b3);
+            mma_bf16(o[2 * nb], a, b0, b1);
+            mma_bf16(o[2 * nb + 1], a, b2, b3);
         }
     }
 }
+
+constexpr int KEYS_TMA_TILES = 4 * TMA_TILE;                      // 2 stages of K and V
+constexpr int KEYS_TMA_LOOP = KEYS_TMA_TILES + 16 * ROW_BYTES + 64 + 1024;   // + query rows + barriers + alignment slack
+constexpr int SMEM_KEYS_TMA = KEYS_TMA_LOOP > SMEM_KEYS_MERGE_BYTES + 1024 ? KEYS_TMA_LOOP : SMEM_KEYS_MERGE_BYTES + 1024;
+
+// Thread 0 issues the boxes of the next tile while all four warps work on the current one.  (A
+// separate producer warp with deeper stages was measured slower: its registers cost the third
+// CTA per SM, and this kernel lives on the number of warps in flight.)
+__global__ void __launch_bounds__(THREADS)
+attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, Params p) {
+    BW_PDL_TRIGGER();
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* kv = smem;                           // [2 stages][K tile, V tile], each 1024-aligned (swizzle)
+    uint8_t* q_tile = smem + KEYS_TMA_TILES;      // 16 padded rows
+    uint64_t* bars = reinterpret_cast<uint64_t*>(q_tile + 16 * ROW_BYTES);
+    const uint32_t full0 = smem_u32(bars);
+    if (threadIdx.x == 0) {
+        bw::mbar_init(full0, 1); bw::mbar_init(full0 + 8, 1);
+        bw::fence_barrier_init();
+        bw::tma_prefetch_desc(&tmK); bw::tma_prefetch_desc(&tmV);
+    }
+    __syncthreads();
+    BW_PDL_WAIT();
+    const int4 w = reinterpret_cast<const int4*>(p.work)[blockIdx.x];
+    const int r = w.x, slice = w.y, n_slices = w.z, item = w.w, g = blockIdx.y;
+    const int warp = threadIdx.x >> 5;
+    const int q_len = p.cu_q[r + 1] - p.cu_q[r];
+    const int kv_len = p.kv_len[r];
+    const int n_rows = q_len * p.G;               // <= 16
+    const int q_pos0 = p.q_start[r];
+    const int* bt = p.block_table + (size_t)r * p.max_blocks;
+    const int last_pos = q_pos0 + q_len - 1;
+    const int first_key = p.window > 0 ? max(0, q_pos0 - p.window + 1) : 0;
+    const int t_first = first_key / BN, t_end = last_pos / BN + 1;
+    const int per = (t_end - t_first + n_slices - 1) / n_slices;
+    const int t_lo = t_first + slice * per, t_hi = min(t_end, t_lo + per) - 1;   // inclusive; may be empty
+    const int ppt = BN / p.page_size;
+
+    // thread 0: page ids are looked up one tile before their boxes are issued, so the lookup's
+    // latency is off the path; pages that do not exist are skipped (the warps clear their rows)
+    int pages[8];
+    auto lookup = [&](int t) {
+        for (int pg = 0; pg < ppt; ++pg) {
+            const int key = t * BN + pg * p.page_size;
+            const int page = (t <= t_hi && key < kv_len) ? bt[key / p.page_size] : -1;
+            pages[pg] = page < p.num_pages ? page : -1;
+        }
+    };
+    auto issue_tile = [&](int stage) {
+        uint8_t* k_tile = kv + stage * 2 * TMA_TILE;
+        int n_ok = 0;
+        for (int pg = 0; pg < ppt; ++pg) n_ok += pages[pg] >= 0;
+        const uint32_t bar = full0 + 8 * stage;
+        bw::mbar_expect_tx(bar, n_ok * 2 * NSL * p.page_size * 128);
+        for (int pg = 0; pg < ppt; ++pg) {
+            if (pages[pg] < 0) continue;
+            const int y = (pages[pg] * p.nkv + g) * p.page_size;
+            const uint32_t off = pg * p.page_size * 128;
+#pragma unroll
+            for (int h = 0; h < NSL; ++h) {
+                bw::tma_load_2d(smem_u32(k_tile + h * SLICE_BYTES + off), &tmK, bar, h * 64, y);
+                bw::tma_load_2d(smem_u32(k_tile + TMA_TILE + h * SLICE_BYTES + off), &tmV, bar, h * 64, y);
+            }
+        }
+    };
+
+    RowState st;
+    init_rows(p, st, 0, n_rows, q_pos0);
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+
+    if (t_lo <= t_hi) {
+        if (threadIdx.x == 0) { lookup(t_lo); issue_tile(0); lookup(t_lo + 1); }
+        load_q_rows(p, p.cu_q[r], g, 0, n_rows, q_tile, 16);
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+        uint32_t qf[KSTEPS][4];
+        load_q_frags(q_tile, qf);
+        bool ok = true;
+        for (int t = t_lo; t <= t_hi && ok; ++t) {
+            const int i = t - t_lo, stage = i & 1;
+            uint8_t* k_tile = kv + stage * 2 * TMA_TILE;
+            uint8_t* v_tile = k_tile + TMA_TILE;
+            if (threadIdx.x == 0 && t < t_hi) { issue_tile(stage ^ 1); lookup(t + 2); }
+            ok = bw::mbar_wait(full0 + 8 * stage, (i >> 1) & 1, &g_tma_status, 21);
+            // Rows of keys that do not exist hold whatever was there: values times a probability of
+            // 0 must still be 0, so those rows of V are cleared (only in a request's last tile or at
+            // a window's edge).
+            if (t * BN + BN > kv_len || (p.window > 0 && t * BN < first_key)) {
+                for (int idx = threadIdx.x; idx < BN * NSL * 8; idx += THREADS) {
+                    const int rk = idx / (NSL * 8), rem = idx - rk * (NSL * 8);
+                    const int key = t * BN + rk;
+                    if (key >= kv_len || bt[key / p.page_size] < 0)
+                        *reinterpret_cast<uint4*>(v_tile + (rem >> 3) * SLICE_BYTES + rk * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                __syncthreads();
+            }
+            const int k_off = warp * 16;
+            if (ok && t * BN + k_off <= last_pos) {
+                const bool need_mask = (t * BN + BN - 1 > q_pos0) || (p.window > 0 && t * BN < last_pos - p.window + 1);
+                process_keys_swz<16>(qf, k_tile, v_tile, k_off, t * BN, need_mask, p.scale_log2, st, o);
+            }
+            // every warp is done with this stage before it is loaded again; a timeout ends the loop for all
+            ok = __syncthreads_and(ok) != 0;
+        }
+    }
+    __syncthreads();
+    finish_keys(p, st, o, smem, r, g, slice, n_slices, item, n_rows);
+}
+#endif  // HEAD_DIM % 64 == 0
 
 // sums the slices of every sliced item: grid (sliced items, nkv).  The slices' maxima and sums go
 // to shared memory first; the loads of the partial outputs are then independent of one another.
@@ -437,7 +655,7 @@ attn_merge_kernel(Params p, const int* merge_items) {
 
 constexpr int SMEM_ROWS = (BN + 4 * BN) * ROW_BYTES;     // q tile of 64 rows + 2 stages of K and V
 constexpr int SMEM_KEYS_LOOP = (16 + 4 * BN) * ROW_BYTES;
-constexpr int SMEM_KEYS_MERGE = (2 * NWARPS * 16 + NWARPS * 16 * HD) * 4;
+constexpr int SMEM_KEYS_MERGE = SMEM_KEYS_MERGE_BYTES;
 constexpr int SMEM_KEYS = SMEM_KEYS_LOOP > SMEM_KEYS_MERGE ? SMEM_KEYS_LOOP : SMEM_KEYS_MERGE;
 
 }  // namespace
@@ -478,8 +696,32 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
     }
     if (n_keys_items > 0) {
         p.work = keys_work;
-        bw::launch((attn_keys_kernel), dim3(dim3(n_keys_items, nkv)), dim3(THREADS), SMEM_KEYS, s, p);
-        BW_LAUNCH_CHECK();
+        bool launched = false;
+#if HEAD_DIM % 64 == 0
+        if ((page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
+            (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0) {
+            static bool tma_attr_done = false;
+            if (!tma_attr_done) {
+                cudaError_t e = cudaFuncSetAttribute(attn_keys_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_KEYS_TMA);
+                if (e != cudaSuccess) return (int)e;
+                tma_attr_done = true;
+            }
+            CUtensorMap tk, tv;
+            cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)num_pages * nkv * page_size};
+            cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+            cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+            if (!bw::encode_bf16_sw128(&tk, k_pages, 2, dims, strides, box) ||
+                !bw::encode_bf16_sw128(&tv, v_pages, 2, dims, strides, box))
+                return BW_ERR_DRIVER;
+            bw::launch((attn_keys_tma_kernel), dim3(n_keys_items, nkv), dim3(THREADS), SMEM_KEYS_TMA, s, tk, tv, p);
+            BW_LAUNCH_CHECK();
+            launched = true;
+        }
+#endif
+        if (!launched) {
+            bw::launch((attn_keys_kernel), dim3(dim3(n_keys_items, nkv)), dim3(THREADS), SMEM_KEYS, s, p);
+            BW_LAUNCH_CHECK();
+        }
         if (n_merge_items > 0) {
             bw::launch((attn_merge_kernel), dim3(dim3(n_merge_items, nkv)), dim3(256), 0, s, p, merge_work);
             BW_LAUNCH_CHECK();

@@ -387,13 +387,14 @@ _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_vo
 _TARGET_CTAS = 148 * 4
 
 
-def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128, rows_tile: int = 64):
+def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128, rows_tile: int = 64,
+                   page_size: int = 16):
     """Work lists of the tensor-core attention for this batch and group size, made
     once per step and shared by all layers: segments of more than 16 stacked rows
     (tokens x heads of a group) are cut into 64-row tiles; the others (decode tokens)
     are cut into key slices so that the GPU is filled.  With ``batch.static_bound``
     (graph replay) the number of slices depends on that bound, not on the lengths."""
-    key = ("attn_work", G, nkv, window, hd, rows_tile)
+    key = ("attn_work", G, nkv, window, hd, rows_tile, page_size)
     cached = batch.static_extras.get(key)
     if cached is not None:
         return cached
@@ -401,7 +402,11 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
     rows_items, keys_items, merge_items = [], [], []
     small = [r for r in range(batch.R) if batch.h_q_len[r] * G <= 16]
     # CTAs of the key-slice kernel that fit on the GPU at once (shared memory bound)
-    slots = 148 * max(1, min(8, (227 * 1024) // ((16 + 4 * 64) * (hd * 2 + 16) + 1024)))
+    if hd % 64 == 0 and page_size in (8, 16, 32, 64):   # the TMA-fed kernel: 2 stages of unpadded tiles
+        smem = 2 * 2 * 64 * hd * 2 + 16 * (hd * 2 + 16) + 2048
+    else:
+        smem = (16 + 4 * 64) * (hd * 2 + 16)
+    slots = 148 * max(1, min(8, (227 * 1024) // (smem + 1024)))
     heads = max(1, len(small) * nkv)
     if heads <= slots:
         want = slots // heads            # one full wave: all slices run side by side, no tail
@@ -451,7 +456,7 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     # prompt portions: the tcgen05 kernel (128-row tiles) where it takes the geometry, else mma.sync (64-row tiles)
     use_tc = attention_tc_supports(hd, G, page_size)
     rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices = attention_work(
-        batch, G, nkv, window, hd, rows_tile=128 if use_tc else 64)
+        batch, G, nkv, window, hd, rows_tile=128 if use_tc else 64, page_size=page_size)
     out = torch.empty_like(q)
     part_o = part_ml = None
     if n_merge:
