@@ -510,7 +510,7 @@ constexpr int KEYS_TMA_TILES = 4 * TMA_TILE;                      // 2 stages of
 constexpr int KEYS_TMA_LOOP = KEYS_TMA_TILES + 16 * ROW_BYTES + 64 + 1024;   // + query rows + barriers + alignment slack
 constexpr int SMEM_KEYS_TMA = KEYS_TMA_LOOP > SMEM_KEYS_MERGE_BYTES + 1024 ? KEYS_TMA_LOOP : SMEM_KEYS_MERGE_BYTES + 1024;
 
-// Thread 0 issues the boxes of the next tile while all four warps work on the current one.  (A
+// Warp 0 issues the boxes of the next tile while all four warps work on the current one.  (A
 // separate producer warp with deeper stages was measured slower: its registers cost the third
 // CTA per SM, and this kernel lives on the number of warps in flight.)
 __global__ void __launch_bounds__(THREADS)
@@ -544,26 +544,25 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const int t_lo = t_first + slice * per, t_hi = min(t_end, t_lo + per) - 1;   // inclusive; may be empty
     const int ppt = BN / p.page_size;
 
-    // thread 0: page ids are looked up one tile before their boxes are issued, so the lookup's
-    // latency is off the path; pages that do not exist are skipped (the warps clear their rows)
-    int pages[8];
+    // Warp 0 feeds the tiles: lane pg owns page pg of a tile.  Its page id is looked up one tile
+    // before its boxes are issued, so the lookup's latency is off the path; pages that do not
+    // exist are skipped (the warps clear their rows).
+    const int lane = threadIdx.x & 31;
+    int my_page = -1;
     auto lookup = [&](int t) {
-        for (int pg = 0; pg < ppt; ++pg) {
-            const int key = t * BN + pg * p.page_size;
-            const int page = (t <= t_hi && key < kv_len) ? bt[key / p.page_size] : -1;
-            pages[pg] = page < p.num_pages ? page : -1;
-        }
+        const int key = t * BN + lane * p.page_size;
+        const int page = (lane < ppt && t <= t_hi && key < kv_len) ? bt[key / p.page_size] : -1;
+        my_page = page < p.num_pages ? page : -1;
     };
     auto issue_tile = [&](int stage) {
         uint8_t* k_tile = kv + stage * 2 * TMA_TILE;
-        int n_ok = 0;
-        for (int pg = 0; pg < ppt; ++pg) n_ok += pages[pg] >= 0;
+        const int n_ok = __popc(__ballot_sync(0xffffffffu, my_page >= 0));
         const uint32_t bar = full0 + 8 * stage;
-        bw::mbar_expect_tx(bar, n_ok * 2 * NSL * p.page_size * 128);
-        for (int pg = 0; pg < ppt; ++pg) {
-            if (pages[pg] < 0) continue;
-            const int y = (pages[pg] * p.nkv + g) * p.page_size;
-            const uint32_t off = pg * p.page_size * 128;
+        if (lane == 0) bw::mbar_expect_tx(bar, n_ok * 2 * NSL * p.page_size * 128);
+        __syncwarp();
+        if (my_page >= 0) {
+            const int y = (my_page * p.nkv + g) * p.page_size;
+            const uint32_t off = lane * p.page_size * 128;
 #pragma unroll
             for (int h = 0; h < NSL; ++h) {
                 bw::tma_load_2d(smem_u32(k_tile + h * SLICE_BYTES + off), &tmK, bar, h * 64, y);
@@ -579,7 +578,7 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
 
     if (t_lo <= t_hi) {
-        if (threadIdx.x == 0) { lookup(t_lo); issue_tile(0); lookup(t_lo + 1); }
+        if (warp == 0) { lookup(t_lo); issue_tile(0); lookup(t_lo + 1); }
         load_q_rows(p, p.cu_q[r], g, 0, n_rows, q_tile, 16);
         cp_async_commit();
         cp_async_wait<0>();
@@ -591,7 +590,7 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             const int i = t - t_lo, stage = i & 1;
             uint8_t* k_tile = kv + stage * 2 * TMA_TILE;
             uint8_t* v_tile = k_tile + TMA_TILE;
-            if (threadIdx.x == 0 && t < t_hi) { issue_tile(stage ^ 1); lookup(t + 2); }
+            if (warp == 0 && t < t_hi) { issue_tile(stage ^ 1); lookup(t + 2); }
             ok = bw::mbar_wait(full0 + 8 * stage, (i >> 1) & 1, &g_tma_status, 21);
             // Rows of keys that do not exist hold whatever was there: values times a probability of
             // 0 must still be 0, so those rows of V are cleared (only in a request's last tile or at
@@ -619,37 +618,76 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 }
 #endif  // HEAD_DIM % 64 == 0
 
-// sums the slices of every sliced item: grid (sliced items, nkv).  The slices' maxima and sums go
-// to shared memory first; the loads of the partial outputs are then independent of one another.
+// Sums the slices of every sliced item: grid (sliced items, nkv, 16 rows), one row of one head per
+// CTA.  The threads form MERGE_GROUPS groups of HD / 4; group j takes slices j, j + MERGE_GROUPS, ...
+// with one float4 each, so all loads of a row are in flight together; shared memory adds the groups
+// (in slice order within a group, groups in order: the same sum whatever ran beside it).
 constexpr int MAX_SLICES = 64;
-__global__ void __launch_bounds__(256)
+constexpr int MERGE_THREADS = 256;
+constexpr int MERGE_QUADS = HD / 4;
+constexpr int MERGE_GROUPS = MERGE_THREADS / MERGE_QUADS < MAX_SLICES ? MERGE_THREADS / MERGE_QUADS : MAX_SLICES;
+constexpr int MERGE_PER = (MAX_SLICES + MERGE_GROUPS - 1) / MERGE_GROUPS;
+__global__ void __launch_bounds__(MERGE_THREADS)
 attn_merge_kernel(Params p, const int* merge_items) {
     BW_PDL_TRIGGER();
+    const int4 w = reinterpret_cast<const int4*>(merge_items)[blockIdx.x];   // written before the step's first kernel
+    const int r = w.x, n_slices = w.z, item = w.w, g = blockIdx.y, row = blockIdx.z;
     BW_PDL_WAIT();
-    __shared__ float sm_m[MAX_SLICES * 16], sm_l[MAX_SLICES * 16];
-    const int4 w = reinterpret_cast<const int4*>(merge_items)[blockIdx.x];
-    const int r = w.x, n_slices = w.z, item = w.w, g = blockIdx.y;
     const int n_rows = (p.cu_q[r + 1] - p.cu_q[r]) * p.G;
-    const size_t base0 = ((size_t)item * p.nkv + (size_t)g * n_slices) * 16;
-    for (int i = threadIdx.x; i < n_slices * 16; i += blockDim.x) {
-        const float2 ml = reinterpret_cast<const float2*>(p.part_ml)[base0 + i];
-        sm_m[i] = ml.x; sm_l[i] = ml.y;
+    if (row >= n_rows) return;
+    __shared__ float sm_m[MAX_SLICES], sm_f[MAX_SLICES], sm_lf[MAX_SLICES];
+    __shared__ float4 red[MERGE_GROUPS][MERGE_QUADS];
+    const size_t base0 = ((size_t)item * p.nkv + (size_t)g * n_slices) * 16 + row;
+    const int tid = threadIdx.x, quad = tid % MERGE_QUADS, group = tid / MERGE_QUADS;
+    // this thread's partial outputs: issued before anything that depends on the maxima
+    float4 part[MERGE_PER];
+    if (group < MERGE_GROUPS) {
+#pragma unroll
+        for (int i = 0; i < MERGE_PER; ++i) {
+            const int sl = group + i * MERGE_GROUPS;
+            part[i] = sl < n_slices ? reinterpret_cast<const float4*>(p.part_o + (base0 + (size_t)sl * 16) * HD)[quad]
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    float l_mine = 0.f;
+    if (tid < n_slices) {
+        const float2 ml = reinterpret_cast<const float2*>(p.part_ml)[base0 + (size_t)tid * 16];
+        sm_m[tid] = ml.x; l_mine = ml.y;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n_rows * HD; idx += blockDim.x) {
-        const int row = idx / HD, c = idx - row * HD;
-        float M = -INFINITY;
-        for (int s = 0; s < n_slices; ++s) M = fmaxf(M, sm_m[s * 16 + row]);
-        float acc = 0.f, L = 0.f;
-#pragma unroll 8
-        for (int s = 0; s < n_slices; ++s) {
-            const float ms = sm_m[s * 16 + row];
-            const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-            acc += p.part_o[(base0 + (size_t)s * 16 + row) * HD + c] * f;
-            L += sm_l[s * 16 + row] * f;
+    float M = -INFINITY;
+    for (int sl = 0; sl < n_slices; ++sl) M = fmaxf(M, sm_m[sl]);
+    if (tid < n_slices) {
+        const float f = sm_m[tid] == -INFINITY ? 0.f : exp2f(sm_m[tid] - M);
+        sm_f[tid] = f; sm_lf[tid] = l_mine * f;
+    }
+    __syncthreads();
+    if (group < MERGE_GROUPS) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < MERGE_PER; ++i) {
+            const int sl = group + i * MERGE_GROUPS;
+            if (sl < n_slices) {
+                const float f = sm_f[sl];
+                acc.x += part[i].x * f; acc.y += part[i].y * f; acc.z += part[i].z * f; acc.w += part[i].w * f;
+            }
         }
+        red[group][quad] = acc;
+    }
+    __syncthreads();
+    if (tid < MERGE_QUADS) {
+        float4 acc = red[0][tid];
+        for (int j = 1; j < MERGE_GROUPS; ++j) {
+            const float4 v = red[j][tid];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        float L = 0.f;
+        for (int sl = 0; sl < n_slices; ++sl) L += sm_lf[sl];
+        const float inv = L > 0.f ? 1.f / L : 0.f;
         const int tok = row / p.G, hg = row - tok * p.G;
-        p.out[((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + tid * 4;
+        const uint2 packed = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+        *reinterpret_cast<uint2*>(dst) = packed;
     }
 }
 
@@ -723,7 +761,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
             BW_LAUNCH_CHECK();
         }
         if (n_merge_items > 0) {
-            bw::launch((attn_merge_kernel), dim3(dim3(n_merge_items, nkv)), dim3(256), 0, s, p, merge_work);
+            bw::launch((attn_merge_kernel), dim3(n_merge_items, nkv, 16), dim3(MERGE_THREADS), 0, s, p, merge_work);
             BW_LAUNCH_CHECK();
         }
     }
