@@ -126,6 +126,20 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     table[(size_t)t * rotary_dim + half + j] = s;
 }
 
+// Where each token of the step keeps its keys and values: page * page_size + slot of its position,
+// or -1 when the block table names no page there.  The same for all layers of a cache group.
+__global__ void kv_slots_kernel(const int* __restrict__ positions, const int* __restrict__ req_of_token,
+                                const int* __restrict__ block_table, int max_blocks, int page_size, int num_pages,
+                                int* __restrict__ kv_slot, int T) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const int pos = positions[t];
+    const int page = block_table[(size_t)req_of_token[t] * max_blocks + pos / page_size];
+    kv_slot[t] = (page >= 0 && page < num_pages) ? page * page_size + pos % page_size : -1;
+}
+
 constexpr int ROPE_HPB = 8;   // heads per block of rope_append_kernel
 
 template <typename IT, typename OT>
@@ -135,7 +149,7 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
                                    const float* __restrict__ inv_freq, const float* __restrict__ table,
                                    int rotary_dim, OT* __restrict__ q_out, OT* __restrict__ k_pages,
                                    OT* __restrict__ v_pages, int nh, int nkv, int hd,
-                                   int page_size, int num_pages) {
+                                   int page_size, int num_pages, int paired) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     // A block takes ROPE_HPB heads of one token; a thread takes one channel of each of them: the
@@ -161,12 +175,15 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
             else sincosf((float)pos * inv_freq[j], &sn, &cs);
             if (c < half) sn = -sn;   // first half: x cos - partner sin; second half: partner sin + x cos
         }
-        const int pc = rot_c ? (c < half ? c + half : c - half) : c;
+        // paired: in the q and k heads the input holds channel j and its partner j + half side by side
+        // (at 2j and 2j + 1), the order the fused projection's weight rows have
+        const int sc = (paired && rot_c) ? (c < half ? 2 * c : 2 * (c - half) + 1) : c;
+        const int pc = rot_c ? (paired ? (sc ^ 1) : (c < half ? c + half : c - half)) : c;
         float v[ROPE_HPB], w[ROPE_HPB];
 #pragma unroll
         for (int k = 0; k < ROPE_HPB; ++k) {
             const int h = h0 + k;
-            v[k] = h < n_heads ? bw::to_f32(row[(size_t)h * hd + c]) : 0.f;
+            v[k] = h < n_heads ? bw::to_f32(row[(size_t)h * hd + (h < nh + nkv ? sc : c)]) : 0.f;
             w[k] = (h < nh + nkv && rot_c) ? bw::to_f32(row[(size_t)h * hd + pc]) : 0.f;
         }
 #pragma unroll
@@ -245,11 +262,22 @@ BW_EXPORT int bw_rope_table(const int* positions, const float* inv_freq, float* 
     return 0;
 }
 
-// table: [T, rotary_dim] from bw_rope_table, or null to compute the angles here.
+BW_EXPORT int bw_kv_slots(const int* positions, const int* req_of_token, const int* block_table, int max_blocks,
+                          int page_size, int num_pages, int* kv_slot, int T, void* stream) {
+    if (T <= 0) return 0;
+    if (page_size <= 0 || (long long)num_pages * page_size > 2147483647LL) return BW_ERR_BAD_ARG;
+    bw::launch((kv_slots_kernel), dim3((T + 127) / 128), dim3(128), 0, (cudaStream_t)stream, positions, req_of_token,
+               block_table, max_blocks, page_size, num_pages, kv_slot, T);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+// table: [T, rotary_dim] from bw_rope_table, or null to compute the angles here.  paired != 0: the
+// rotated channels of the q and k heads come as (channel j, channel j + rotary_dim / 2) pairs.
 BW_EXPORT int bw_rope_append(const void* qkv, int in_type, const int* positions, const int* req_of_token,
                              const int* block_table, int max_blocks, const float* inv_freq, const float* table,
                              int rotary_dim, void* q_out, void* k_pages, void* v_pages, int out_type,
-                             int T, int nh, int nkv, int hd, int page_size, int num_pages, void* stream) {
+                             int T, int nh, int nkv, int hd, int page_size, int num_pages, int paired, void* stream) {
     if (T <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
@@ -257,7 +285,7 @@ BW_EXPORT int bw_rope_append(const void* qkv, int in_type, const int* positions,
     const dim3 grid(T, (nh + 2 * nkv + ROPE_HPB - 1) / ROPE_HPB);
 #define BW_RA(IT, OT) bw::launch((rope_append_kernel<IT, OT>), dim3(grid), dim3(threads), 0, s, cp<IT>(qkv), positions, req_of_token, \
         block_table, max_blocks, inv_freq, table, rotary_dim, mp<OT>(q_out), mp<OT>(k_pages), mp<OT>(v_pages), \
-        nh, nkv, hd, page_size, num_pages)
+        nh, nkv, hd, page_size, num_pages, paired)
     if (in_type == BW_F32 && out_type == BW_F32) BW_RA(float, float);
     else if (in_type == BW_F32 && out_type == BW_BF16) BW_RA(float, bf16);
     else if (in_type == BW_BF16 && out_type == BW_BF16) BW_RA(bf16, bf16);

@@ -14,7 +14,8 @@
 // quarter) a counter tells the warp that finishes last to add the partials IN SPLIT
 // ORDER (deterministic) and run the epilogue.  Counters return to zero by themselves.
 // Epilogue: + bias[feature], then store float32 | bfloat16, or add into float32 out
-// (the residual stream), or SwiGLU over interleaved gate/up features -> bfloat16.
+// (the residual stream), or SwiGLU over interleaved gate/up features -> bfloat16, or rotary
+// position encoding of a fused q/k/v projection with the keys and values written to their pages.
 //
 // Roles (192 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps
 // 2..5 epilogue (TMEM lane quarter = warp % 4).  Every wait is bounded; a timeout sets
@@ -38,6 +39,18 @@ constexpr int SWIGLU_BLOCK = 16;   // gate/up features are interleaved in blocks
 
 __device__ int g_status = 0;  // 0 ok; else the code of the first wait that gave up
 
+// Rotary epilogue of a fused q/k/v projection: features are (q heads, k heads, v heads) x hd.  In
+// the rotated heads the weight rows are ordered so that features 2j and 2j + 1 are channel j and
+// its partner j + rd / 2: a lane finds the partner in its neighbour.  Queries go to q_out
+// [tokens, nh * hd]; keys and values to the page of the token's position
+// ([num_pages, nkv, page_size, hd]) that kv_slot names; without kv_slot no keys or values are written.
+struct RopeOut {
+    const float* table;          // [tokens, rd]: cos (rd / 2), then sin (rd / 2) of the token's angles
+    const int* kv_slot;          // [tokens]: page * page_size + slot of the token's position, -1: none; null: no append
+    bf16* q_out; bf16* k_pages; bf16* v_pages;
+    int nh, nkv, hd, rd, page_size;
+};
+
 struct Epilogue {
     void* out;            // [tokens, features] (SwiGLU: [tokens, features / 2]), row stride ldo (elements)
     float* partial;       // split-K: [splits, tokens, features] dense float32; else null
@@ -46,7 +59,54 @@ struct Epilogue {
     long long ldo;
     int out_type, bias_type, accumulate, transposed, swiglu;
     int tokens, features, splits;
+    int rope_on;
+    RopeOut rope;
 };
+
+__device__ __forceinline__ float bias_at(const Epilogue& ep, int feature) {
+    if (!ep.bias) return 0.f;
+    return ep.bias_type == BW_F32 ? ((const float*)ep.bias)[feature] : __bfloat162float(((const bf16*)ep.bias)[feature]);
+}
+
+// Where the rotary epilogue puts feature `feature` of a token: the head, the channel within it,
+// whether it is rotated and the sign of its partner's sine.
+struct RopeSlot { int head, channel, j; bool rot, second; };
+__device__ __forceinline__ RopeSlot rope_slot(const RopeOut& ro, int feature) {
+    RopeSlot s;
+    s.head = feature / ro.hd;
+    const int li = feature - s.head * ro.hd;
+    s.rot = s.head < ro.nh + ro.nkv && li < ro.rd;
+    s.j = li >> 1; s.second = (li & 1) != 0;
+    s.channel = s.rot ? s.j + (s.second ? (ro.rd >> 1) : 0) : li;
+    return s;
+}
+
+// row of the pages ([page, kv head, slot]) where a key / value of kv head `kvh` goes, from the token's
+// kv_slot value (page * page_size + slot), or -1
+__device__ __forceinline__ long long rope_page_row(const RopeOut& ro, int kv_slot, int kvh) {
+    if (kv_slot < 0) return -1;
+    const int page = kv_slot / ro.page_size;
+    return ((long long)page * ro.nkv + kvh) * ro.page_size + (kv_slot - page * ro.page_size);
+}
+
+// cosine and signed sine of a rotated channel (first half: x cos - partner sin; second: x cos + partner sin)
+__device__ __forceinline__ float2 rope_angle(const RopeOut& ro, const RopeSlot& sl, int token) {
+    if (!sl.rot) return make_float2(1.f, 0.f);
+    const float cs = __ldg(ro.table + (size_t)token * ro.rd + sl.j);
+    const float sn = __ldg(ro.table + (size_t)token * ro.rd + (ro.rd >> 1) + sl.j);
+    return make_float2(cs, sl.second ? sn : -sn);
+}
+
+__device__ __forceinline__ void rope_store(const RopeOut& ro, const RopeSlot& sl, int token, long long page_row,
+                                           float2 angle, float x, float partner) {
+    const float y = sl.rot ? x * angle.x + partner * angle.y : x;
+    if (sl.head < ro.nh) {
+        ro.q_out[((size_t)token * ro.nh + sl.head) * ro.hd + sl.channel] = __float2bfloat16_rn(y);
+    } else if (page_row >= 0) {
+        bf16* pages = sl.head < ro.nh + ro.nkv ? ro.k_pages : ro.v_pages;
+        pages[(size_t)page_row * ro.hd + sl.channel] = __float2bfloat16_rn(y);
+    }
+}
 
 template <int BN> __host__ __device__ constexpr int stages_for() {
     constexpr int per = A_BYTES + BN * BK * 2;
@@ -56,11 +116,44 @@ template <int BN> __host__ __device__ constexpr int stages_for() {
     return BN <= 16 ? 5 : (s > 8 ? 8 : s);
 }
 
+// The rotary epilogue of G consecutive tokens of one feature (one lane), in two halves: what does
+// not depend on the sums (the tokens' cache slots and angles) is fetched first, so a caller that
+// still has sums to form can overlap the two.
+template <int G> struct RopeCtx { RopeSlot sl; float b, bp; int kvh; int kv[G]; float2 ang[G]; };
+
+template <int G>
+__device__ __forceinline__ void rope_prefetch(const Epilogue& ep, RopeCtx<G>& cx, int token0, int nvalid,
+                                              int feature, bool fvalid) {
+    const RopeOut& ro = ep.rope;
+    cx.sl = rope_slot(ro, fvalid ? feature : 0);
+    cx.b = fvalid ? bias_at(ep, feature) : 0.f;
+    cx.bp = fvalid ? bias_at(ep, feature ^ 1) : 0.f;   // the partner's (the feature count is even)
+    cx.kvh = cx.sl.head < ro.nh + ro.nkv ? cx.sl.head - ro.nh : cx.sl.head - ro.nh - ro.nkv;
+    const bool paged = fvalid && cx.sl.head >= ro.nh && ro.kv_slot;
+#pragma unroll
+    for (int k = 0; k < G; ++k) {
+        const bool live = k < nvalid && fvalid;
+        cx.kv[k] = (paged && live) ? __ldg(ro.kv_slot + token0 + k) : -1;
+        cx.ang[k] = live ? rope_angle(ro, cx.sl, token0 + k) : make_float2(1.f, 0.f);
+    }
+}
+
+template <int G>
+__device__ __forceinline__ void rope_finish(const Epilogue& ep, const RopeCtx<G>& cx, const float* vals, int token0,
+                                            int nvalid, bool fvalid) {
+#pragma unroll
+    for (int k = 0; k < G; ++k) {
+        const float partner = __shfl_xor_sync(0xffffffffu, vals[k], 1) + cx.bp;
+        if (k < nvalid && fvalid)
+            rope_store(ep.rope, cx.sl, token0 + k, rope_page_row(ep.rope, cx.kv[k], cx.kvh), cx.ang[k], vals[k] + cx.b, partner);
+    }
+}
+
 // The lane holds the finished sums vals[0..N) of ONE feature for N consecutive tokens (token0 + c);
 // the 32 lanes of the warp hold 32 consecutive features.  nvalid (the same in all lanes) of the
 // tokens exist.  When the result is added to `out`, all old values are fetched before the first
 // store, so the loads are in flight together instead of one round trip per token.
-template <int N>
+template <int N, bool ROPE>
 __device__ __forceinline__ void emit(const Epilogue& ep, float* part, const float (&vals)[N], int token0,
                                      int nvalid, int feature, bool fvalid) {
     if (part) {
@@ -82,10 +175,19 @@ __device__ __forceinline__ void emit(const Epilogue& ep, float* part, const floa
         }
         return;
     }
+    if constexpr (ROPE) {
+        // eight tokens at a time: their cache slots and angles are fetched before the first store
+        constexpr int G = N < 8 ? N : 8;
+#pragma unroll
+        for (int c0 = 0; c0 < N; c0 += G) {
+            RopeCtx<G> cx;
+            rope_prefetch<G>(ep, cx, token0 + c0, nvalid - c0, feature, fvalid);
+            rope_finish<G>(ep, cx, &vals[c0], token0 + c0, nvalid - c0, fvalid);
+        }
+        return;
+    }
     if (!fvalid) return;
-    float b = 0.f;
-    if (ep.bias) b = ep.bias_type == BW_F32 ? ((const float*)ep.bias)[feature]
-                                             : __bfloat162float(((const bf16*)ep.bias)[feature]);
+    const float b = bias_at(ep, feature);
     const size_t off = (size_t)token0 * ep.ldo + feature;
     if (ep.out_type == BW_F32) {
         float* o = (float*)ep.out + off;
@@ -105,8 +207,77 @@ __device__ __forceinline__ void emit(const Epilogue& ep, float* part, const floa
     }
 }
 
-template <int BN>
-__global__ void __launch_bounds__(THREADS, 1)
+// Rotary epilogue in the normal orientation: the thread holds 32 consecutive features f0 .. f0 + 31
+// of ONE token (v, float32 bits straight from TMEM).  Partners are neighbours in its registers, the
+// cache slot of the token is read once per tile (kv_slot < 0: no keys and values are written), and
+// every store is 16 bytes when rd is a multiple of 16.
+__device__ __forceinline__ void rope_direct(const Epilogue& ep, const uint32_t (&v)[32], int token, int f0,
+                                         int kv_slot) {
+    const RopeOut& ro = ep.rope;
+    const int half = ro.rd >> 1;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int fh = f0 + 16 * h;
+        if (fh >= ep.features) break;
+        const int head = fh / ro.hd, li0 = fh - head * ro.hd;
+        bf16* dst;
+        if (head < ro.nh) dst = ro.q_out + ((size_t)token * ro.nh + head) * ro.hd;
+        else {
+            if (kv_slot < 0) continue;
+            const bool is_k = head < ro.nh + ro.nkv;
+            const int kvh = is_k ? head - ro.nh : head - ro.nh - ro.nkv;
+            dst = (is_k ? ro.k_pages : ro.v_pages) + (size_t)rope_page_row(ro, kv_slot, kvh) * ro.hd;
+        }
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = __uint_as_float(v[16 * h + i]) + bias_at(ep, fh + i);
+        const bool rotated_head = head < ro.nh + ro.nkv;
+        if ((ro.rd & 15) == 0) {
+            if (rotated_head && li0 < ro.rd) {
+                const int j0 = li0 >> 1;
+                const float4* tc = reinterpret_cast<const float4*>(ro.table + (size_t)token * ro.rd + j0);
+                const float4* ts = reinterpret_cast<const float4*>(ro.table + (size_t)token * ro.rd + half + j0);
+                const float4 c0 = __ldg(tc), c1 = __ldg(tc + 1), s0 = __ldg(ts), s1 = __ldg(ts + 1);
+                const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                float lo[8], hi[8];
+#pragma unroll
+                for (int p = 0; p < 8; ++p) {
+                    lo[p] = x[2 * p] * cs[p] - x[2 * p + 1] * sn[p];
+                    hi[p] = x[2 * p + 1] * cs[p] + x[2 * p] * sn[p];
+                }
+                *reinterpret_cast<uint4*>(dst + j0) = make_uint4(bw::pack_bf16x2(lo[0], lo[1]), bw::pack_bf16x2(lo[2], lo[3]),
+                                                                 bw::pack_bf16x2(lo[4], lo[5]), bw::pack_bf16x2(lo[6], lo[7]));
+                *reinterpret_cast<uint4*>(dst + j0 + half) = make_uint4(bw::pack_bf16x2(hi[0], hi[1]), bw::pack_bf16x2(hi[2], hi[3]),
+                                                                        bw::pack_bf16x2(hi[4], hi[5]), bw::pack_bf16x2(hi[6], hi[7]));
+            } else {
+                *reinterpret_cast<uint4*>(dst + li0) = make_uint4(bw::pack_bf16x2(x[0], x[1]), bw::pack_bf16x2(x[2], x[3]),
+                                                                  bw::pack_bf16x2(x[4], x[5]), bw::pack_bf16x2(x[6], x[7]));
+                *reinterpret_cast<uint4*>(dst + li0 + 8) = make_uint4(bw::pack_bf16x2(x[8], x[9]), bw::pack_bf16x2(x[10], x[11]),
+                                                                      bw::pack_bf16x2(x[12], x[13]), bw::pack_bf16x2(x[14], x[15]));
+            }
+        } else {
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const int li = li0 + 2 * p;
+                if (rotated_head && li < ro.rd) {
+                    const int j = li >> 1;
+                    const float cs = __ldg(ro.table + (size_t)token * ro.rd + j);
+                    const float sn = __ldg(ro.table + (size_t)token * ro.rd + half + j);
+                    dst[j] = __float2bfloat16_rn(x[2 * p] * cs - x[2 * p + 1] * sn);
+                    dst[j + half] = __float2bfloat16_rn(x[2 * p + 1] * cs + x[2 * p] * sn);
+                } else {
+                    dst[li] = __float2bfloat16_rn(x[2 * p]);
+                    dst[li + 1] = __float2bfloat16_rn(x[2 * p + 1]);
+                }
+            }
+        }
+    }
+}
+
+// ROPE: the rotary epilogue (a kernel of its own, so that the plain one carries none of its registers)
+template <int BN, bool ROPE>
+__global__ void __launch_bounds__(THREADS, BN <= 16 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                Epilogue ep, int kb_total, int kb_per_split, int tiles_a, int tiles_b, int num_work) {
     constexpr int STAGES = stages_for<BN>();
@@ -234,6 +405,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t lane_addr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
             const int ga = tile_a * BM + quarter * 32 + lane;   // this lane's row of A
             float* part = ep.partial ? ep.partial + (size_t)split * plane : nullptr;
+            int rope_kv = -1;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += CH) {
                 uint32_t v[CH];
@@ -246,7 +418,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                     for (int c = 0; c < CH; ++c) vals[c] = __uint_as_float(v[c]);
                     const int token0 = tile_b * BN + c0;
-                    emit<CH>(ep, part, vals, token0, min(CH, b_rows - token0), ga, ga < a_rows);
+                    emit<CH, ROPE>(ep, part, vals, token0, min(CH, b_rows - token0), ga, ga < a_rows);
+                } else if (ROPE && !part) {
+                    if constexpr (CH == 32 && ROPE) {
+                        const int token = tile_a * BM + quarter * 32 + lane;
+                        if (c0 == 0)   // once per tile: where this thread's token keeps its keys and values
+                            rope_kv = (token < a_rows && ep.rope.kv_slot) ? __ldg(ep.rope.kv_slot + token) : -1;
+                        if (token < a_rows && tile_b * BN + c0 < b_rows) rope_direct(ep, v, token, tile_b * BN + c0, rope_kv);
+                    }
                 } else {
                     if constexpr (CH == 32) {
                         // turn the 32 x 32 block through shared memory so that a warp stores whole rows
@@ -260,7 +439,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         for (int r = 0; r < 32; ++r) vals[r] = stage[r * 33 + lane];
                         __syncwarp();
                         if (tile_b * BN + c0 < b_rows)
-                            emit<32>(ep, part, vals, token0, min(32, a_rows - token0), feature, feature < b_rows);
+                            emit<32, ROPE>(ep, part, vals, token0, min(32, a_rows - token0), feature, feature < b_rows);
                     }
                 }
             }
@@ -290,6 +469,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                             for (int c = 0; c < 8; ++c) vals[c] = 0.f;
                             const int nv = min(8, t_end - token0);
+                            RopeCtx<8> cx;
+                            if constexpr (ROPE) rope_prefetch<8>(ep, cx, token0, nv, ga, ga < a_rows);
                             if (ga < a_rows)
                                 for (int s = 0; s < ep.splits; ++s) {
                                     const float* src = ep.partial + (size_t)s * plane + (size_t)token0 * ep.features + ga;
@@ -297,7 +478,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                     for (int c = 0; c < 8; ++c)
                                         if (c < nv) vals[c] += __ldcg(src + (size_t)c * ep.features);
                                 }
-                            emit<8>(ep, nullptr, vals, token0, nv, ga, ga < a_rows);
+                            if constexpr (ROPE) rope_finish<8>(ep, cx, vals, token0, nv, ga < a_rows);
+                            else emit<8, false>(ep, nullptr, vals, token0, nv, ga, ga < a_rows);
                         }
                     } else {
                         const int r_end = min(a_rows, tile_a * BM + quarter * 32 + 32);
@@ -315,7 +497,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                         for (int c = 0; c < 8; ++c)
                                             if (c < nv) vals[c] += __ldcg(src + (size_t)c * ep.features);
                                     }
-                                emit<8>(ep, nullptr, vals, token0, nv, feature, feature < b_rows);
+                                emit<8, ROPE>(ep, nullptr, vals, token0, nv, feature, feature < b_rows);
                             }
                         }
                     }
@@ -348,6 +530,18 @@ __global__ void splitk_reduce_kernel(Epilogue ep) {
                 u += ep.partial[(size_t)s * plane + (size_t)token * ep.features + fu];
             }
             ((bf16*)ep.out)[(size_t)token * ep.ldo + j] = __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+            continue;
+        }
+        if (ep.rope_on) {
+            const RopeSlot sl = rope_slot(ep.rope, j);
+            float x = 0.f, partner = 0.f;
+            for (int s = 0; s < ep.splits; ++s) {
+                x += ep.partial[(size_t)s * plane + i];
+                if (sl.rot) partner += ep.partial[(size_t)s * plane + (i ^ 1)];
+            }
+            const int kvh = sl.head < ep.rope.nh + ep.rope.nkv ? sl.head - ep.rope.nh : sl.head - ep.rope.nh - ep.rope.nkv;
+            const long long row = (sl.head >= ep.rope.nh && ep.rope.kv_slot) ? rope_page_row(ep.rope, __ldg(ep.rope.kv_slot + token), kvh) : -1;
+            rope_store(ep.rope, sl, token, row, rope_angle(ep.rope, sl, token), x + bias_at(ep, j), partner + bias_at(ep, j ^ 1));
             continue;
         }
         float v = 0.f;
@@ -393,7 +587,7 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long K, lon
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN>
+template <int BN, bool ROPE>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const Epilogue& ep, int kb_total, int kb_per_split,
            int tiles_a, int tiles_b, int num_work, cudaStream_t s) {
     constexpr int STAGES = stages_for<BN>();
@@ -401,12 +595,12 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const Epilogue& ep, int k
     static_assert(smem <= 227 * 1024, "shared memory budget");
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
     const int grid = num_work < NUM_SMS ? num_work : NUM_SMS;
-    bw::launch((gemm_tc_kernel<BN>), dim3(grid), dim3(THREADS), smem, s, a, b, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work);
+    bw::launch((gemm_tc_kernel<BN, ROPE>), dim3(grid), dim3(THREADS), smem, s, a, b, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work);
     BW_LAUNCH_CHECK();
     return 0;
 }
@@ -458,16 +652,17 @@ BW_EXPORT int bw_gemm_tc_plan(int M, int N, int K, long long workspace_elems, lo
 // and out is bf16 [M, I] = silu(gate) * up.  workspace / counters: scratch for split-K
 // (float32 partial sums; int32 counters that are zero between launches); may be null.
 // force_splits > 0 overrides the planner.
-BW_EXPORT int bw_gemm_tc(const void* x, const void* w, const void* bias, int bias_type, void* out, int out_type,
-                         int M, int N, int K, long long ldx, long long ldo, int accumulate, int swiglu,
-                         float* workspace, long long workspace_elems, int* counters, long long n_counters,
-                         int force_splits, void* stream) {
+static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_type, void* out, int out_type,
+                       int M, int N, int K, long long ldx, long long ldo, int accumulate, int swiglu,
+                       float* workspace, long long workspace_elems, int* counters, long long n_counters,
+                       int force_splits, const RopeOut* rope, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!bw_gemm_tc_supported(x, w, K, ldx)) return BW_ERR_UNSUPPORTED;
     if (accumulate && out_type != BW_F32) return BW_ERR_BAD_ARG;
     if (swiglu && (N % (2 * SWIGLU_BLOCK) != 0 || out_type != BW_BF16 || accumulate || bias || ldo < N / 2))
         return BW_ERR_BAD_ARG;
-    if (!swiglu && ldo < N) return BW_ERR_BAD_ARG;
+    if (rope && (swiglu || accumulate)) return BW_ERR_BAD_ARG;
+    if (!swiglu && !rope && ldo < N) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const bool can_split = workspace && counters;
     int tr, bn;
@@ -496,16 +691,19 @@ BW_EXPORT int bw_gemm_tc(const void* x, const void* w, const void* bias, int bia
     ep.bias = bias; ep.ldo = ldo;
     ep.out_type = out_type; ep.bias_type = bias_type; ep.accumulate = accumulate; ep.transposed = tr;
     ep.swiglu = swiglu; ep.tokens = M; ep.features = N; ep.splits = splits;
+    ep.rope_on = rope ? 1 : 0;
+    if (rope) ep.rope = *rope; else ep.rope = RopeOut{};
     const int num_work = tiles_a * tiles_b * splits;
     int rc;
-    switch (bn) {
-        case 16: rc = launch<16>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break;
-        case 32: rc = launch<32>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break;
-        case 64: rc = launch<64>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break;
-        case 128: rc = launch<128>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break;
-        case 256: rc = launch<256>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break;
-        default: return BW_ERR_BAD_ARG;
-    }
+#define BW_GEMM_LAUNCH(R) switch (bn) { \
+        case 16: rc = launch<16, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 32: rc = launch<32, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 64: rc = launch<64, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 128: rc = launch<128, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 256: rc = launch<256, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        default: return BW_ERR_BAD_ARG; }
+    if (rope) BW_GEMM_LAUNCH(true) else BW_GEMM_LAUNCH(false)
+#undef BW_GEMM_LAUNCH
     if (rc) return rc;
     if (splits > 1 && !fused_reduce) {
         const size_t total = (size_t)M * (swiglu ? N / 2 : N);
@@ -515,6 +713,36 @@ BW_EXPORT int bw_gemm_tc(const void* x, const void* w, const void* bias, int bia
         BW_LAUNCH_CHECK();
     }
     return 0;
+}
+
+BW_EXPORT int bw_gemm_tc(const void* x, const void* w, const void* bias, int bias_type, void* out, int out_type,
+                         int M, int N, int K, long long ldx, long long ldo, int accumulate, int swiglu,
+                         float* workspace, long long workspace_elems, int* counters, long long n_counters,
+                         int force_splits, void* stream) {
+    return run_gemm_tc(x, w, bias, bias_type, out, out_type, M, N, K, ldx, ldo, accumulate, swiglu, workspace,
+                       workspace_elems, counters, n_counters, force_splits, nullptr, stream);
+}
+
+// The fused q/k/v projection with rotary position encoding: x[M, K] . w[N, K]^T (+ bias), N =
+// (nh + 2 nkv) * hd, the rows of w (and bias) of every q and k head ordered so that rows 2j and
+// 2j + 1 are channels j and j + rd / 2 (rows from rd on, and the v heads, in place).  Rotated
+// queries go to q_out [M, nh * hd] (bf16), rotated keys and raw values (bf16) to the pages
+// [num_pages, nkv, page_size, hd] at kv_slot[token] = page * page_size + slot (-1: nowhere; a null
+// kv_slot writes no keys or values).  table: float32 [M, rd], cosines then sines of every
+// token's angles.
+BW_EXPORT int bw_gemm_tc_rope(const void* x, const void* w, const void* bias, int bias_type, int M, int K,
+                              long long ldx, const float* table, const int* kv_slot, void* q_out, void* k_pages,
+                              void* v_pages, int nh, int nkv, int hd, int rd, int page_size,
+                              float* workspace, long long workspace_elems, int* counters, long long n_counters,
+                              int force_splits, void* stream) {
+    if (nh <= 0 || nkv <= 0 || hd <= 0 || hd % 2 || rd < 0 || rd % 2 || rd > hd || page_size <= 0 || (rd > 0 && !table))
+        return BW_ERR_BAD_ARG;
+    RopeOut ro;
+    ro.table = table; ro.kv_slot = kv_slot;
+    ro.q_out = (bf16*)q_out; ro.k_pages = (bf16*)k_pages; ro.v_pages = (bf16*)v_pages;
+    ro.nh = nh; ro.nkv = nkv; ro.hd = hd; ro.rd = rd; ro.page_size = page_size;
+    return run_gemm_tc(x, w, bias, bias_type, nullptr, BW_BF16, M, (nh + 2 * nkv) * hd, K, ldx, 0, 0, 0, workspace,
+                       workspace_elems, counters, n_counters, force_splits, &ro, stream);
 }
 
 // Reads and clears the status word (synchronises the device).  0: no wait ever gave up.

@@ -159,14 +159,30 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int)
     return table
 
 
+def kv_slots(positions: torch.Tensor, req_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
+             num_pages: int) -> torch.Tensor:
+    """int32 [T]: ``page * page_size + slot`` of every token's position in its request's block table
+    (-1 where the table names no page): where the token's keys and values go, for every layer of
+    the cache group."""
+    _dev(positions, "positions", torch.int32); _dev(req_of_token, "req_of_token", torch.int32)
+    _dev(block_table, "block_table", torch.int32)
+    T = positions.numel()
+    out = torch.empty(T, dtype=torch.int32, device=positions.device)
+    fn = _fn("elementwise", "bw_kv_slots", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(positions), _ptr(req_of_token), _ptr(block_table), block_table.shape[1], page_size, num_pages,
+              _ptr(out), T, _stream()), "kv_slots")
+    return out
+
+
 def rope_append(qkv: torch.Tensor, positions: torch.Tensor, req_of_token: torch.Tensor,
                 block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int,
                 k_pages: torch.Tensor, v_pages: torch.Tensor, nh: int, nkv: int, hd: int,
                 q_out: Optional[torch.Tensor] = None, append: bool = True,
-                table: Optional[torch.Tensor] = None) -> torch.Tensor:
+                table: Optional[torch.Tensor] = None, paired: bool = False) -> torch.Tensor:
     """Rotates q and k heads of ``qkv`` [T, (nh+2nkv)*hd], returns q [T, nh*hd] in the
     pages' dtype, and writes rotated k and raw v to pages [num_pages, nkv, page, hd].
-    ``table``: the step's cos/sin table from :func:`rope_table` (else computed here)."""
+    ``table``: the step's cos/sin table from :func:`rope_table` (else computed here).
+    ``paired``: the q and k heads of ``qkv`` are in the order of :func:`rotary_row_order`."""
     _dev(qkv, "qkv"); _dev(positions, "positions", torch.int32)
     _dev(req_of_token, "req_of_token", torch.int32); _dev(block_table, "block_table", torch.int32)
     _dev(k_pages, "k_pages"); _dev(v_pages, "v_pages", k_pages.dtype)
@@ -189,10 +205,10 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, req_of_token: torch.
             raise KernelError("rope_append: the cos/sin table must be [T, rotary_dim]")
     fn = _fn("elementwise", "bw_rope_append",
              [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(qkv), _code(qkv, "qkv"), _ptr(positions), _ptr(req_of_token), _ptr(block_table),
               block_table.shape[1], _ptr(inv_freq), _ptr(table), rotary_dim, _ptr(q_out), _ptr(k_pages), _ptr(v_pages),
-              _code(k_pages, "pages"), T, nh, nkv, hd, page_size, num_pages if append else 0, _stream()),
+              _code(k_pages, "pages"), T, nh, nkv, hd, page_size, num_pages if append else 0, int(paired), _stream()),
            "rope_append")
     return q_out
 
@@ -284,6 +300,7 @@ _GEMM_TC_ARGS = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_
 _WORKSPACE_BYTES = 64 << 20
 _COUNTERS = 1 << 16
 _workspaces = {}
+GEMM_FUSED_REDUCE_MAX_TOKENS = 16  # up to here gemm_tc sums its K splits inside the kernel
 SWIGLU_BLOCK = 16  # gate/up rows of a fused SwiGLU weight alternate in blocks of this many
 
 
@@ -355,6 +372,65 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
               _code(out, "out"), M, N, K, x.stride(0), out.stride(0), int(accumulate), int(swiglu), _ptr(ws),
               ws.numel(), _ptr(counters), counters.numel(), int(force_splits), _stream()), "gemm_tc")
     return out
+
+
+def rotary_row_order(nh: int, nkv: int, hd: int, rotary_dim: int) -> torch.Tensor:
+    """Row order of a fused q/k/v weight for :func:`gemm_tc_rope`: in every q and k head rows 2j
+    and 2j + 1 are channels j and j + rotary_dim / 2; the other rows and the v heads stay."""
+    half = rotary_dim // 2
+    head = torch.arange(hd)
+    head[:rotary_dim] = torch.stack([torch.arange(half), torch.arange(half) + half], dim=1).reshape(-1)
+    plain = torch.arange(hd)
+    rows = [head + h * hd for h in range(nh + nkv)] + [plain + h * hd for h in range(nh + nkv, nh + 2 * nkv)]
+    return torch.cat(rows)
+
+
+_GEMM_TC_ROPE_ARGS = ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll] + [c_void_p] * 5 + [c_int] * 5
+                      + [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p])
+
+
+def gemm_tc_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], table: Optional[torch.Tensor],
+                 kv_slot: Optional[torch.Tensor], k_pages: torch.Tensor, v_pages: torch.Tensor, nh: int, nkv: int,
+                 hd: int, rotary_dim: int, force_splits: int = 0) -> torch.Tensor:
+    """The q/k/v projection, the rotation and the append to the cache in one kernel: ``w`` (and
+    ``bias``) in the row order of :func:`rotary_row_order`; ``table`` from :func:`rope_table`;
+    ``kv_slot`` from :func:`kv_slots` (None: nothing is appended).  Returns the rotated queries
+    [T, nh * hd] (bfloat16); rotated keys and raw values are written to the pages
+    [num_pages, nkv, page_size, hd] (bfloat16)."""
+    _dev(x, "x", torch.bfloat16, contiguous=False); _dev(w, "w", torch.bfloat16)
+    _dev(k_pages, "k_pages", torch.bfloat16); _dev(v_pages, "v_pages", torch.bfloat16)
+    if not gemm_tc_supports(x, w):
+        raise KernelError("gemm_tc_rope: operands must be bfloat16 with K and the row stride multiples of 8 "
+                          "and 16-byte aligned")
+    T, K = x.shape
+    if w.shape != ((nh + 2 * nkv) * hd, K):
+        raise KernelError(f"gemm_tc_rope: w must be [(nh + 2 nkv) * hd, K] = [{(nh + 2 * nkv) * hd}, {K}]")
+    num_pages, pk, page_size, phd = k_pages.shape
+    if pk != nkv or phd != hd or v_pages.shape != k_pages.shape:
+        raise KernelError("gemm_tc_rope: pages must be [num_pages, nkv, page_size, head_dim]")
+    if rotary_dim % 2 or not 0 <= rotary_dim <= hd or hd % 16:
+        raise KernelError("gemm_tc_rope: rotary_dim must be even and at most head_dim, head_dim a multiple of 16")
+    if rotary_dim:
+        _dev(table, "table", torch.float32)
+        if tuple(table.shape) != (T, rotary_dim):
+            raise KernelError("gemm_tc_rope: the cos/sin table must be [T, rotary_dim]")
+    if kv_slot is not None:
+        _dev(kv_slot, "kv_slot", torch.int32)
+        if kv_slot.numel() != T:
+            raise KernelError("gemm_tc_rope: kv_slot must have one entry per token")
+    if bias is not None:
+        _dev(bias, "bias")
+        if bias.numel() != w.shape[0]:
+            raise KernelError("gemm_tc_rope: bias must have one entry per row of w")
+    q_out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=x.device)
+    ws, counters = _workspace(x.device)
+    fn = _fn("gemm_tc", "bw_gemm_tc_rope", _GEMM_TC_ROPE_ARGS,
+             tag=f"rope{T}x{w.shape[0]}x{K}" if _timings is not None else None)
+    _check(fn(_ptr(x), _ptr(w), _ptr(bias), _code(bias, "bias") if bias is not None else 0, T, K, x.stride(0),
+              _ptr(table), _ptr(kv_slot), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), nh, nkv, hd, rotary_dim,
+              page_size, _ptr(ws), ws.numel(), _ptr(counters), counters.numel(), int(force_splits), _stream()),
+           "gemm_tc_rope")
+    return q_out
 
 
 def gemm_tc_status() -> int:

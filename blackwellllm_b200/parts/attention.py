@@ -33,6 +33,7 @@ class GQAAttention(Mixer):
         self.position = build_position(spec.position, self.hd, ctx)
         ops.check_attention_supported(ctx.dtype, self.hd)
         self.qkv: Linear = None
+        self.project = None
         self.o: Linear = None
 
     def cache_request(self):
@@ -55,12 +56,17 @@ class GQAAttention(Mixer):
             bs = [tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]]
             dt = bs[0].dtype if all(t.dtype == bs[0].dtype for t in bs) else torch.float32
             b = torch.cat([t.to(dt) for t in bs], dim=0)
-        self.qkv = Linear(w, b)
+        # an encoding that runs inside the projection takes the weight over; else project, then encode
+        self.project = self.position.fuse_projection(w, b, self.nh, self.nkv, self.hd)
+        self.qkv = Linear(w, b) if self.project is None else None
         self.o = Linear(tensors["o_proj.weight"])
 
     def forward(self, x, residual, batch, cache, owns_cache: bool = True) -> None:
-        qkv = self.qkv(x, out_dtype=torch.float32)
-        q = self.position.rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, append=owns_cache)
+        if self.project is not None:
+            q = self.project(x, batch, cache, owns_cache)
+        else:
+            qkv = self.qkv(x, out_dtype=torch.float32)
+            q = self.position.rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, append=owns_cache)
         o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, batch.block_tables[cache.group],
                                 self.nh, self.window, self.scale)
         self.o(o, out=residual, accumulate=True)

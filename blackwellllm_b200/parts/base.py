@@ -86,7 +86,16 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     def rotate_append(self, qkv, batch, cache, nh: int, nkv: int, hd: int, append: bool = True) -> torch.Tensor:
+        """qkv [T, (nh + 2 nkv) * hd] float32 -> encoded queries [T, nh * hd]; encoded keys and raw
+        values are written to the cache when ``append``."""
         raise NotImplementedError
+
+    def fuse_projection(self, weight: torch.Tensor, bias: Optional[torch.Tensor], nh: int, nkv: int, hd: int):
+        """Optional: an encoding that can run inside the q/k/v projection returns a callable
+        ``project(x, batch, cache, append) -> queries`` that replaces projection plus
+        :meth:`rotate_append` (it may keep its own copy of ``weight`` and ``bias`` in another
+        row order).  None: the mixer projects and calls :meth:`rotate_append`."""
+        return None
 
 
 class Mixer(Part):

@@ -44,16 +44,49 @@ class RotaryEncoding(PositionEncoding):
         self.inv_freq = rotary_inv_freq(spec.theta, self.rotary_dim, spec.scaling).to(ctx.device)
         self._key = ("rope_table", float(spec.theta), self.rotary_dim, spec.scaling)
 
-    def rotate_append(self, qkv, batch, cache, nh, nkv, hd, append=True):
+    def _table(self, batch):
         # the cosines and sines of the step's positions are the same in every layer with these
         # rotary parameters: computed by the first one, kept on the batch for the others
         table = batch.extras.get(self._key)
         if table is None:
             table = ops.rope_table(batch.positions, self.inv_freq, self.rotary_dim)
             batch.extras[self._key] = table
+        return table
+
+    def rotate_append(self, qkv, batch, cache, nh, nkv, hd, append=True):
+        table = self._table(batch)
         return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
                                self.inv_freq, self.rotary_dim, cache.k_pages, cache.v_pages, nh, nkv, hd,
                                append=append, table=table)
+
+
+    def fuse_projection(self, weight, bias, nh, nkv, hd):
+        # bfloat16 on the tensor-core product: rotation and append run in its epilogue
+        if weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.shape[1] % 8:
+            return None
+        order = ops.rotary_row_order(nh, nkv, hd, self.rotary_dim).to(weight.device)
+        w = weight.index_select(0, order).contiguous()
+        b = bias.index_select(0, order).contiguous() if bias is not None else None
+
+        def project(x, batch, cache, append=True):
+            if batch.T <= ops.GEMM_FUSED_REDUCE_MAX_TOKENS:
+                # few tokens: the product sums its K splits in its last warps, and the rotation on
+                # top of that was measured slower than a kernel of its own on the paired layout
+                qkv = ops.gemm_tc(x, w, b, out_dtype=torch.float32)
+                return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
+                                       self.inv_freq, self.rotary_dim, cache.k_pages, cache.v_pages, nh, nkv, hd,
+                                       append=append, table=self._table(batch), paired=True)
+            slots = None
+            if append:   # where the step's tokens go in this cache group: the same for all its layers
+                key = ("kv_slots", cache.group)
+                slots = batch.extras.get(key)
+                if slots is None:
+                    slots = ops.kv_slots(batch.positions, batch.req_of_token, batch.block_tables[cache.group],
+                                         cache.k_pages.shape[2], cache.k_pages.shape[0])
+                    batch.extras[key] = slots
+            return ops.gemm_tc_rope(x, w, b, self._table(batch), slots, cache.k_pages, cache.v_pages, nh, nkv, hd,
+                                    self.rotary_dim)
+        return project
 
 
 class NoPosition(PositionEncoding):

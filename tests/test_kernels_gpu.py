@@ -87,6 +87,57 @@ def test_gemm_tc_swiglu_epilogue(ops, M, I, K, splits):
     assert float((out.double() - ref).abs().max()) <= 2 ** -7 * float(ref.abs().max())
 
 
+@pytest.mark.parametrize("M,splits", [(3, 0), (16, 3), (40, 2), (300, 0)])
+@pytest.mark.parametrize("nh,nkv,hd,rd,page", [(5, 1, 48, 32, 8), (4, 2, 64, 64, 16), (2, 2, 16, 6, 4)])
+def test_gemm_tc_rotary_epilogue(ops, M, splits, nh, nkv, hd, rd, page):
+    """Projection + rotation + append in the product's epilogue, in every place it is written: sums
+    inside the kernel (few tokens), the second kernel (more), the other orientation (many);
+    head sizes where a warp of 32 features spans two heads, rotary sizes below the head size."""
+    K = 264
+    N = (nh + 2 * nkv) * hd
+    w = rand(N, K, seed=1, scale=0.1).to(torch.bfloat16)
+    b = rand(N, seed=2, scale=0.5).to(torch.bfloat16)
+    x = rand(M, K, seed=3).to(torch.bfloat16)
+    positions = torch.arange(M, dtype=torch.int32) * 3 + 1000          # far, and not consecutive
+    n_blocks = (int(positions.max()) // page) + 1
+    g = torch.Generator().manual_seed(4)
+    num_pages = n_blocks + 5
+    table = torch.randperm(num_pages, generator=g)[:n_blocks].to(torch.int32).view(1, n_blocks)
+    req = torch.zeros(M, dtype=torch.int32)
+    inv = plain_inv_freq(hd, 10000.0, None, rotary_dim=rd)
+    order = ops.rotary_row_order(nh, nkv, hd, rd)
+    kp = torch.zeros(num_pages, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    tab = ops.rope_table(positions.to(DEV), inv.float().to(DEV), rd)
+    slots = ops.kv_slots(positions.to(DEV), req.to(DEV), table.to(DEV), page, num_pages)
+    q = ops.gemm_tc_rope(x.to(DEV), w[order].contiguous().to(DEV), b[order].contiguous().to(DEV), tab, slots, kp, vp,
+                         nh, nkv, hd, rd, force_splits=splits)
+    qkv = (x.double() @ w.double().T + b.double()).view(M, nh + 2 * nkv, hd)
+    q_ref = plain_rope(qkv[:, :nh], positions, inv).reshape(M, nh * hd)
+    k_ref = plain_rope(qkv[:, nh:nh + nkv], positions, inv)
+    v_ref = qkv[:, nh + nkv:]
+    tol = 2 ** -7
+    assert float((q.double().cpu() - q_ref).abs().max()) <= tol * float(q_ref.abs().max())
+    kc, vc = kp.double().cpu(), vp.double().cpu()
+    for t in range(M):
+        p_ = int(positions[t])
+        pg = int(table[0, p_ // page])
+        assert float((kc[pg, :, p_ % page] - k_ref[t]).abs().max()) <= tol * float(k_ref.abs().max())
+        assert float((vc[pg, :, p_ % page] - v_ref[t]).abs().max()) <= tol * float(v_ref.abs().max())
+    # nothing else in the pages was touched
+    written = torch.zeros(num_pages, page, dtype=torch.bool)
+    for t in range(M):
+        p_ = int(positions[t])
+        written[int(table[0, p_ // page]), p_ % page] = True
+    assert float(kc.abs().amax(dim=(1, 3))[~written].max()) == 0.0
+    # the same without an append: queries only
+    kp.zero_()
+    q2 = ops.gemm_tc_rope(x.to(DEV), w[order].contiguous().to(DEV), b[order].contiguous().to(DEV), tab, None, kp, vp,
+                          nh, nkv, hd, rd, force_splits=splits)
+    assert torch.equal(q2, q) and float(kp.abs().max()) == 0.0
+    assert ops.gemm_tc_status() == 0
+
+
 def test_gemm_tc_row_independent_of_batch(ops):
     """A token's row does not depend on which other tokens share the launch."""
     K, N = 1024, 768

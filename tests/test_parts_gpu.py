@@ -99,6 +99,54 @@ def test_rotary_encoding_and_append(dtype, rotary_dim, scaling):
         assert float((v_got - v_ref[t]).abs().max()) <= tol * float(v_ref.abs().max())
 
 
+@pytest.mark.parametrize("lens", [(1, 2), (19, 30), (150, 171)])
+@pytest.mark.parametrize("rotary_dim,bias", [(48, True), (24, False)])
+def test_rotary_encoding_inside_the_projection(lens, rotary_dim, bias):
+    """bfloat16: projection, rotation and append in one kernel (few tokens with K splits summed
+    inside the kernel, more with the second kernel, many in the other orientation) against
+    plain projection + plain rotation."""
+    from blackwellllm_b200.cache.manager import CacheManager
+    from blackwellllm_b200.config.specs import RopeSpec
+    from blackwellllm_b200.parts import BuildContext, PagedKVRequest, build_position
+    nh, nkv, hd, page, K = 6, 2, 48, 8, 1096
+    dtype = torch.bfloat16
+    pos_enc = build_position(RopeSpec(theta=10000.0, rotary_dim=rotary_dim, scaling=None), hd, BuildContext(DEV, dtype))
+    cache = CacheManager([PagedKVRequest(nkv, hd)], page, 700, 4, dtype=dtype, device=DEV)
+    cache.add_request("far")
+    cache.append("far", 5000)
+    batch = make_batch(cache, [("far", lens[0]), ("new", lens[1])])
+    T = sum(lens)
+    w = rnd((nh + 2 * nkv) * hd, K, seed=5, scale=0.05).to(dtype)
+    b = rnd((nh + 2 * nkv) * hd, seed=6, scale=0.5).to(dtype) if bias else None
+    x = rnd(T, K, seed=7).to(dtype)
+    project = pos_enc.fuse_projection(w.to(DEV), None if b is None else b.to(DEV), nh, nkv, hd)
+    assert project is not None
+    q = project(x.to(DEV), batch, cache.views[0], True)
+    positions = torch.tensor(list(range(5000, 5000 + lens[0])) + list(range(lens[1])))
+    inv = plain_inv_freq(hd, 10000.0, None, rotary_dim=rotary_dim)
+    qkv = x.double() @ w.double().T + (0 if b is None else b.double())
+    qkv = qkv.view(T, nh + 2 * nkv, hd)
+    q_ref = plain_rope(qkv[:, :nh], positions, inv).reshape(T, nh * hd)
+    k_ref = plain_rope(qkv[:, nh:nh + nkv], positions, inv)
+    v_ref = qkv[:, nh + nkv:]
+    tol = 2 ** -7    # bfloat16 results of float32 sums over 1096 products
+    assert float((q.double().cpu() - q_ref).abs().max()) <= tol * float(q_ref.abs().max())
+    view = cache.views[0]
+    kp, vp = view.k_pages.double().cpu(), view.v_pages.double().cpu()
+    for t in range(T):
+        rid = "far" if t < lens[0] else "new"
+        p_ = int(positions[t])
+        pg = cache.block_table(rid, 0)[p_ // page]
+        assert float((kp[pg, :, p_ % page] - k_ref[t]).abs().max()) <= tol * float(k_ref.abs().max())
+        assert float((vp[pg, :, p_ % page] - v_ref[t]).abs().max()) <= tol * float(v_ref.abs().max())
+    assert ops_status() == 0
+
+
+def ops_status():
+    from blackwellllm_b200.kernels import ops
+    return ops.gemm_tc_status()
+
+
 def attention_weights(H, nh, nkv, hd, bias, dtype, seed):
     t = {"q_proj.weight": rnd(nh * hd, H, seed=seed, scale=0.1), "k_proj.weight": rnd(nkv * hd, H, seed=seed + 1, scale=0.1),
          "v_proj.weight": rnd(nkv * hd, H, seed=seed + 2, scale=0.1), "o_proj.weight": rnd(H, nh * hd, seed=seed + 3, scale=0.1)}
