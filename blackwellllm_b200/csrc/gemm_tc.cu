@@ -208,17 +208,17 @@ __device__ __forceinline__ void emit(const Epilogue& ep, float* part, const floa
 }
 
 // Rotary epilogue in the normal orientation: the thread holds 32 consecutive features f0 .. f0 + 31
-// of ONE token (v, float32 bits straight from TMEM).  Partners are neighbours in its registers, the
+// (the first n_features of them belong to this tile; a multiple of 16) of ONE token (v, float32 bits straight from TMEM).  Partners are neighbours in its registers, the
 // cache slot of the token is read once per tile (kv_slot < 0: no keys and values are written), and
 // every store is 16 bytes when rd is a multiple of 16.
 __device__ __forceinline__ void rope_direct(const Epilogue& ep, const uint32_t (&v)[32], int token, int f0,
-                                         int kv_slot) {
+                                         int n_features, int kv_slot) {
     const RopeOut& ro = ep.rope;
     const int half = ro.rd >> 1;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int fh = f0 + 16 * h;
-        if (fh >= ep.features) break;
+        if (fh >= ep.features || 16 * h >= n_features) break;
         const int head = fh / ro.hd, li0 = fh - head * ro.hd;
         bf16* dst;
         if (head < ro.nh) dst = ro.q_out + ((size_t)token * ro.nh + head) * ro.hd;
@@ -283,7 +283,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr int STAGES = stages_for<BN>();
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators
+    // two accumulators; a tile width that is no power of two takes the next one (TMEM is handed out in
+    // powers of two)
+    constexpr uint32_t ACC_COLS = BN <= 16 ? 16 : BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
     constexpr uint32_t IDESC = bw::umma_idesc_bf16(BM, BN);
 
     extern __shared__ uint8_t smem_raw[];
@@ -368,7 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t acc = n & 1, accph = (n >> 1) & 1;
                 if (!bw::mbar_wait(tempty0 + 8 * acc, accph ^ 1, &g_status, 4)) break;   // epilogue drained it
                 bw::tc_fence_after();
-                const uint32_t tmem_acc = tmem_base + acc * BN;
+                const uint32_t tmem_acc = tmem_base + acc * ACC_COLS;
                 for (int i = 0; i < nkb; ++i, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -402,7 +405,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t acc = n & 1, accph = (n >> 1) & 1;
             if (!bw::mbar_wait(tfull0 + 8 * acc, accph, &g_status, 3)) break;
             bw::tc_fence_after();
-            const uint32_t lane_addr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t lane_addr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             const int ga = tile_a * BM + quarter * 32 + lane;   // this lane's row of A
             float* part = ep.partial ? ep.partial + (size_t)split * plane : nullptr;
             int rope_kv = -1;
@@ -424,7 +427,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const int token = tile_a * BM + quarter * 32 + lane;
                         if (c0 == 0)   // once per tile: where this thread's token keeps its keys and values
                             rope_kv = (token < a_rows && ep.rope.kv_slot) ? __ldg(ep.rope.kv_slot + token) : -1;
-                        if (token < a_rows && tile_b * BN + c0 < b_rows) rope_direct(ep, v, token, tile_b * BN + c0, rope_kv);
+                        if (token < a_rows && tile_b * BN + c0 < b_rows)
+                            rope_direct(ep, v, token, tile_b * BN + c0, min(32, BN - c0), rope_kv);
                     }
                 } else {
                     if constexpr (CH == 32) {
@@ -439,7 +443,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         for (int r = 0; r < 32; ++r) vals[r] = stage[r * 33 + lane];
                         __syncwarp();
                         if (tile_b * BN + c0 < b_rows)
-                            emit<32, ROPE>(ep, part, vals, token0, min(32, a_rows - token0), feature, feature < b_rows);
+                            emit<32, ROPE>(ep, part, vals, token0, min(32, a_rows - token0), feature,
+                                           feature < b_rows && c0 + lane < BN);
                     }
                 }
             }
@@ -490,14 +495,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                                 for (int c = 0; c < 8; ++c) vals[c] = 0.f;
                                 const int nv = min(8, r_end - token0);
-                                if (feature < b_rows)
+                                if (feature < b_rows && c0 + lane < BN)
                                     for (int s = 0; s < ep.splits; ++s) {
                                         const float* src = ep.partial + (size_t)s * plane + (size_t)token0 * ep.features + feature;
 #pragma unroll
                                         for (int c = 0; c < 8; ++c)
                                             if (c < nv) vals[c] += __ldcg(src + (size_t)c * ep.features);
                                     }
-                                emit<8, ROPE>(ep, nullptr, vals, token0, nv, feature, feature < b_rows);
+                                emit<8, ROPE>(ep, nullptr, vals, token0, nv, feature, feature < b_rows && c0 + lane < BN);
                             }
                         }
                     }
@@ -617,16 +622,25 @@ BW_EXPORT int bw_gemm_tc_supported(const void* x, const void* w, int K, long lon
 
 // Picks the orientation, the tile width and the number of K splits for
 // out[M, N] = x[M, K] . w[N, K]^T.  Returns splits; *transposed and *bn are set.
-BW_EXPORT int bw_gemm_tc_plan(int M, int N, int K, long long workspace_elems, long long n_counters,
+BW_EXPORT int bw_gemm_tc_plan(int M, int N, int K, int swiglu, long long workspace_elems, long long n_counters,
                               int* transposed, int* bn) {
     const int kb_total = ceil_div(K, BK);
     int tr = M <= 256, b;
     if (tr) { b = 16; while (b < M) b *= 2; }
     else {
-        // balance over the 148 persistent CTAs picks between 128- and 256-wide tiles
-        auto eff = [&](int w) { long long t = (long long)ceil_div(M, BM) * ceil_div(N, w);
-                                return (double)t / ((double)ceil_div(t, NUM_SMS) * NUM_SMS) * (w == 256 ? 1.0 : 0.9); };
-        b = eff(256) >= eff(128) ? 256 : 128;
+        // The width of the tile (a multiple of 16; of 32 for SwiGLU, whose epilogue works on 16 gate
+        // and 16 up features at a time) is the one whose rounds over the 148 persistent CTAs cost
+        // least: a round costs its width, a 128-wide tile 10 % more per column (both operands then
+        // stream from shared memory at the same rate as the MMA consumes them).
+        const int widths[4] = {256, 240, 224, 128};   // (176 was measured: slower per column than it saves)
+        double best_cost = 0.0; b = 256;
+        for (int i = 0; i < 4; ++i) {
+            const int wd = widths[i];
+            if (swiglu && wd % 32) continue;
+            const long long t = (long long)ceil_div(M, BM) * ceil_div(N, wd);
+            const double cost = (double)ceil_div(t, NUM_SMS) * wd * (wd == 128 ? 1.0 / 0.9 : 1.0);
+            if (i == 0 || cost < best_cost * 0.995) { best_cost = cost; b = wd; }
+        }
     }
     *transposed = tr; *bn = b;
     const long long tiles = tr ? (long long)ceil_div(N, BM) * ceil_div(M, b) : (long long)ceil_div(M, BM) * ceil_div(N, b);
@@ -666,7 +680,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     cudaStream_t s = (cudaStream_t)stream;
     const bool can_split = workspace && counters;
     int tr, bn;
-    int splits = bw_gemm_tc_plan(M, N, K, can_split ? workspace_elems : 0, can_split ? n_counters : 0, &tr, &bn);
+    int splits = bw_gemm_tc_plan(M, N, K, swiglu, can_split ? workspace_elems : 0, can_split ? n_counters : 0, &tr, &bn);
     const int kb_total = ceil_div(K, BK);
     const long long a_rows = tr ? N : M, b_rows = tr ? M : N;
     const int tiles_a = ceil_div(a_rows, BM), tiles_b = ceil_div(b_rows, bn);
@@ -700,6 +714,8 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
         case 32: rc = launch<32, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         case 64: rc = launch<64, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         case 128: rc = launch<128, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 224: rc = launch<224, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 240: rc = launch<240, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         case 256: rc = launch<256, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         default: return BW_ERR_BAD_ARG; }
     if (rope) BW_GEMM_LAUNCH(true) else BW_GEMM_LAUNCH(false)

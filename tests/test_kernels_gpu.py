@@ -26,7 +26,8 @@ def rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 300, 176), (8, 4096, 4096), (17, 136, 80), (64, 1000, 2048),
                                    (100, 6144, 1024), (256, 384, 96), (257, 512, 256), (300, 260, 200),
-                                   (1000, 1111, 520), (2048, 1024, 4096)])
+                                   (1000, 1111, 520), (2048, 1024, 4096),
+                                   (2048, 4096, 64), (2048, 6144 + 48, 64)])   # tiles 240 wide, the last one of a row cut
 @pytest.mark.parametrize("mode", ["plain", "bias_f32out", "accumulate"])
 def test_gemm_tc(ops, M, N, K, mode):
     x = rand(M, K, dtype=torch.bfloat16, seed=1).to(DEV)
@@ -71,8 +72,19 @@ def test_gemm_tc_split_k(ops, M, splits):
     assert torch.equal(out, again)  # split sums are added in a fixed order
 
 
+def test_gemm_tc_split_k_on_a_tile_width_that_is_no_power_of_two(ops):
+    M, N, K = 2048, 4096, 256     # 16 x 18 tiles of 240 columns: the last one of a row is cut at 4096
+    x = rand(M, K, dtype=torch.bfloat16, seed=5).to(DEV)
+    w = rand(N, K, dtype=torch.bfloat16, seed=6, scale=0.05).to(DEV)
+    out = ops.gemm_tc(x, w, out_dtype=torch.float32, force_splits=2)
+    ref = x.double() @ w.double().T
+    assert ops.gemm_tc_status() == 0
+    assert float((out.double() - ref).abs().max()) / float(ref.abs().max()) <= 1e-5
+
+
 @pytest.mark.parametrize("M,I,K,splits", [(1, 176, 64, 0), (8, 14336, 4096, 0), (40, 1008, 512, 3), (300, 176, 256, 0),
-                                          (700, 528, 2048, 2), (2048, 1024, 1024, 0)])
+                                          (700, 528, 2048, 2), (2048, 1024, 1024, 0),
+                                          (2048, 14336, 64, 0)])   # tiles 224 wide
 def test_gemm_tc_swiglu_epilogue(ops, M, I, K, splits):
     """silu(x Wg^T) * (x Wu^T) from the interleaved weight, in both orientations and with split-K."""
     x = rand(M, K, dtype=torch.bfloat16, seed=1).to(DEV)
