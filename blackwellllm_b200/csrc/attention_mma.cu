@@ -153,18 +153,27 @@ __device__ __forceinline__ void process_keys(const uint32_t (&qf)[KSTEPS][4], co
     }
     // scale, mask, online softmax
     float mx[2] = {-INFINITY, -INFINITY};
+    if (need_mask) {   // one branch per tile, not one per score
 #pragma unroll
-    for (int j = 0; j < NK / 8; ++j) {
+        for (int j = 0; j < NK / 8; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int h = e >> 1;
-            float v = s[j][e] * scale_log2;
-            if (need_mask) {
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
                 const int kp = key_pos0 + k_off + j * 8 + 2 * (lane & 3) + (e & 1);
-                if (kp > st.qpos[h] || kp < st.lo[h]) v = -INFINITY;
+                const float v = (kp > st.qpos[h] || kp < st.lo[h]) ? -INFINITY : s[j][e] * scale_log2;
+                s[j][e] = v;
+                mx[h] = fmaxf(mx[h], v);
             }
-            s[j][e] = v;
-            mx[h] = fmaxf(mx[h], v);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float v = s[j][e] * scale_log2;
+                s[j][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
         }
     }
     float corr[2], mu[2];
@@ -448,18 +457,27 @@ __device__ __forceinline__ void process_keys_swz(const uint32_t (&qf)[KSTEPS][4]
         }
     }
     float mx[2] = {-INFINITY, -INFINITY};
+    if (need_mask) {   // one branch per tile, not one per score
 #pragma unroll
-    for (int j = 0; j < NK / 8; ++j) {
+        for (int j = 0; j < NK / 8; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int h = e >> 1;
-            float v = s[j][e] * scale_log2;
-            if (need_mask) {
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
                 const int kp = key_pos0 + k_off + j * 8 + 2 * (lane & 3) + (e & 1);
-                if (kp > st.qpos[h] || kp < st.lo[h]) v = -INFINITY;
+                const float v = (kp > st.qpos[h] || kp < st.lo[h]) ? -INFINITY : s[j][e] * scale_log2;
+                s[j][e] = v;
+                mx[h] = fmaxf(mx[h], v);
             }
-            s[j][e] = v;
-            mx[h] = fmaxf(mx[h], v);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float v = s[j][e] * scale_log2;
+                s[j][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
         }
     }
     float corr[2], mu[2];

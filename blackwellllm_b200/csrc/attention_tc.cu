@@ -6,15 +6,18 @@
 // of 64 up to the causal diagonal:
 //   * TMA brings the query tile (3-D box: channels x heads x tokens) and, page by page through the
 //     block table, the K and V tiles into 128-byte-swizzled shared memory (2 stages);
-//   * S = Q K^T: tcgen05.mma (M 128, N 64) into TMEM;
+//   * S = Q K^T: tcgen05.mma (M 128, N 64) into one of two TMEM buffers, so that S of the next tile
+//     is computed while the softmax warps work on this one;
 //   * four softmax warps, one thread per row (no shuffles): tcgen05.ld of the row of S, scale,
 //     mask, running maximum and sum in float32, P rounded to bfloat16 into swizzled shared memory;
-//   * O_tile = P V: tcgen05.mma with V as an MN-major operand (keys are its K dimension), result
-//     in TMEM, read back and folded into float32 accumulators in registers with the row's
-//     correction factor (no read-modify-write of TMEM).
-// Warp 4 issues all TMA and MMA instructions; S(i+1) is computed while the softmax warps fold O(i).
-// Keys past the request's length are never loaded (a resident page stands in, so the tile holds
-// finite numbers) and are masked by position.  Every wait is bounded and sets a status word.
+//   * O += P V: tcgen05.mma with V as an MN-major operand (keys are its K dimension), accumulated
+//     in TMEM over all tiles.  The exponent's reference m follows the row maximum lazily: only
+//     when the maximum has grown by more than 8 (a factor 256) since m was set does the warp
+//     rescale its rows of O in TMEM (tcgen05.ld, multiply, tcgen05.st); P stays below 2^8, the
+//     sums are float32, and O / l at the end is the same quotient.
+// Warp 4 issues the MMAs, warp 5 the TMA loads.  Keys past the request's length are never loaded
+// (a resident page stands in, so the tile holds finite numbers) and are masked by position.
+// Every wait is bounded and sets a status word.
 #include "tcgen05.cuh"
 
 #ifndef HEAD_DIM
@@ -29,11 +32,11 @@ constexpr int HD = HEAD_DIM;
 static_assert(HD % 64 == 0 && HD >= 64 && HD <= 256, "head size must be a multiple of 64 in [64, 256]");
 constexpr int NS = HD / 64;            // 128-byte column slices of a row
 constexpr int BM = 128, BN = 64, STAGES = 2;
-constexpr int THREADS = 160;
+constexpr int THREADS = 192;
 constexpr int Q_SLICE = BM * 128, KV_SLICE = BN * 128;   // bytes of one column slice of a tile
 constexpr int Q_BYTES = NS * Q_SLICE, KV_BYTES = NS * KV_SLICE, P_BYTES = BM * 128;
 constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES + 16 * 8 + 16;   // 2 CTAs per SM at head size 128
-constexpr uint32_t TMEM_COLS = (64 + HD) <= 128 ? 128 : ((64 + HD) <= 256 ? 256 : 512);
+constexpr uint32_t TMEM_COLS = (128 + HD) <= 256 ? 256 : 512;   // S (two buffers of 64 columns), then O
 constexpr uint32_t IDESC_QK = bw::umma_idesc_bf16(BM, BN, false);
 constexpr uint32_t IDESC_PV = bw::umma_idesc_bf16(BM, 64, true);
 
@@ -68,17 +71,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     uint8_t* v_s = k_s + STAGES * KV_BYTES;
     uint8_t* p_s = v_s + STAGES * KV_BYTES;
     uint64_t* bars = (uint64_t*)(p_s + P_BYTES);
-    // 0 q_full, 1..2 kv_full, 3..4 kv_empty, 5 s_full, 6 p_full, 7 o_full
+    // 0 q_full, 1..2 k_full, 3..4 v_full, 5..6 k_empty, 7..8 v_empty, 9..10 s_full, 11 p_full, 12 pv_done
     uint32_t* tmem_slot = (uint32_t*)(bars + 16);
     const uint32_t bar0 = bw::smem_u32(bars);
-    const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = bar0 + 24, s_full = bar0 + 40,
-                   p_full = bar0 + 48, o_full = bar0 + 56;
+    const uint32_t q_full = bar0, k_full = bar0 + 8, v_full = bar0 + 24, k_empty = bar0 + 40, v_empty = bar0 + 56,
+                   s_full = bar0 + 72, p_full = bar0 + 88, pv_done = bar0 + 96;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         bw::mbar_init(q_full, 1);
-        for (int s = 0; s < STAGES; ++s) { bw::mbar_init(kv_full + 8 * s, 1); bw::mbar_init(kv_empty + 8 * s, 1); }
-        bw::mbar_init(s_full, 1); bw::mbar_init(p_full, 4); bw::mbar_init(o_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            bw::mbar_init(k_full + 8 * s, 1); bw::mbar_init(v_full + 8 * s, 1); bw::mbar_init(k_empty + 8 * s, 1);
+            bw::mbar_init(v_empty + 8 * s, 1); bw::mbar_init(s_full + 8 * s, 1);
+        }
+        bw::mbar_init(p_full, 4); bw::mbar_init(pv_done, 1);
         bw::fence_barrier_init();
         bw::tma_prefetch_desc(&tmQ); bw::tma_prefetch_desc(&tmK); bw::tma_prefetch_desc(&tmV);
         tmem_slot[1] = (uint32_t)g_status;
@@ -90,10 +96,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     BW_PDL_WAIT();   // queries, keys and values of this step come from the kernels before
     const uint32_t tmem_base = *tmem_slot;
     const bool dead = tmem_slot[1] != 0;
-    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 64;
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;   // S buffer b at tmem_S + 64 b
 
-    const int4 wk = reinterpret_cast<const int4*>(p.work)[blockIdx.x];
-    const int r = wk.x, tok0 = wk.y, g = blockIdx.y;
+    // the kv heads of one work item are neighbours in the launch order, so the items (longest first)
+    // start in that order across all heads
+    const int4 wk = reinterpret_cast<const int4*>(p.work)[blockIdx.x / p.nkv];
+    const int r = wk.x, tok0 = wk.y, g = blockIdx.x % p.nkv;
     const int q_len = p.cu_q[r + 1] - p.cu_q[r];
     const int kv_len = p.kv_len[r];
     const int ntok = min(p.tpt, q_len - tok0);
@@ -106,35 +114,62 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
     if (dead) {
         // an earlier launch timed out: do nothing
+    } else if (warp == 5) {
+        if (lane == 0) {
+            // queries: one 3-D box per column slice (channels x the G heads of this kv head x tokens)
+            bw::mbar_expect_tx(q_full, NS * p.G * p.tpt * 128);
+#pragma unroll
+            for (int h = 0; h < NS; ++h)
+                bw::tma_load_3d(bw::smem_u32(q_s + h * Q_SLICE), &tmQ, q_full, h * 64, g * p.G, p.cu_q[r] + tok0);
+        }
+        // Lane pg owns page pg of every tile: its page id is looked up one tile ahead (the lookup's
+        // latency is off the path) and its boxes are issued beside the other lanes'.
+        const int ppt = BN / p.page_size;   // pages per tile
+        auto lookup = [&](int i) {
+            const int key = (t_lo + i) * BN + lane * p.page_size;
+            int page = (lane < ppt && i < n_tiles && key < kv_len) ? bt[key / p.page_size] : -1;
+            return page < 0 ? 0 : page;      // never read: a resident page keeps the tile finite
+        };
+        // Keys and values have stages of their own: a key stage is free as soon as Q K^T of the tile
+        // before last has run, a value stage only after its P V, so the keys run one tile ahead of
+        // the values and neither load is waited for in the steady state.
+        auto load = [&](const CUtensorMap* tm, uint8_t* base, uint32_t full, int i, int page) {
+            const int s = i & 1;
+            if (lane == 0) bw::mbar_expect_tx(full + 8 * s, KV_BYTES);
+            __syncwarp();
+            if (lane < ppt) {
+                const int y = (page * p.nkv + g) * p.page_size;
+                const uint32_t off = s * KV_BYTES + lane * p.page_size * 128;
+#pragma unroll
+                for (int h = 0; h < NS; ++h)
+                    bw::tma_load_2d(bw::smem_u32(base + off + h * KV_SLICE), tm, full + 8 * s, h * 64, y);
+            }
+        };
+        int page_v = lookup(0), page_k = lookup(1);
+        load(&tmK, k_s, k_full, 0, page_v);
+        for (int i = 0; i < n_tiles; ++i) {
+            const int pk = page_k, pv = page_v;
+            page_v = pk; page_k = lookup(i + 2);
+            if (i + 1 < n_tiles) {   // keys of tile i + 1
+                if (i >= 1 && !__all_sync(0xffffffffu, bw::mbar_wait(k_empty + 8 * ((i + 1) & 1), ((i - 1) >> 1) & 1, &g_status, 15))) break;
+                load(&tmK, k_s, k_full, i + 1, pk);
+            }
+            if (i >= 2 && !__all_sync(0xffffffffu, bw::mbar_wait(v_empty + 8 * (i & 1), ((i - 2) >> 1) & 1, &g_status, 19))) break;
+            load(&tmV, v_s, v_full, i, pv);
+        }
     } else if (warp == 4) {
         if (lane == 0) {
-            const int ppt = BN / p.page_size;   // pages per tile
-            auto load_tile = [&](int i) {
-                const int s = i & 1, t = t_lo + i;
-                bw::mbar_expect_tx(kv_full + 8 * s, 2 * KV_BYTES);
-                for (int pg = 0; pg < ppt; ++pg) {
-                    const int key = t * BN + pg * p.page_size;
-                    int page = key < kv_len ? bt[key / p.page_size] : -1;
-                    if (page < 0) page = 0;      // never read: a resident page keeps the tile finite
-                    const int y = (page * p.nkv + g) * p.page_size;
-                    const uint32_t off = s * KV_BYTES + pg * p.page_size * 128;
-#pragma unroll
-                    for (int h = 0; h < NS; ++h) {
-                        bw::tma_load_2d(bw::smem_u32(k_s + off + h * KV_SLICE), &tmK, kv_full + 8 * s, h * 64, y);
-                        bw::tma_load_2d(bw::smem_u32(v_s + off + h * KV_SLICE), &tmV, kv_full + 8 * s, h * 64, y);
-                    }
-                }
-            };
-            auto issue_qk = [&](int s) {
+            auto issue_qk = [&](int s) {   // keys of stage s -> S buffer s
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
                     const uint64_t da = bw::umma_smem_desc_sw128(bw::smem_u32(q_s + (ks >> 2) * Q_SLICE)) + 2 * (ks & 3);
                     const uint64_t db = bw::umma_smem_desc_sw128(bw::smem_u32(k_s + s * KV_BYTES + (ks >> 2) * KV_SLICE)) + 2 * (ks & 3);
-                    bw::umma_bf16(tmem_S, da, db, IDESC_QK, ks != 0);
+                    bw::umma_bf16(tmem_S + 64 * s, da, db, IDESC_QK, ks != 0);
                 }
-                bw::umma_commit(s_full);
+                bw::umma_commit(s_full + 8 * s);
+                bw::umma_commit(k_empty + 8 * s);
             };
-            auto issue_pv = [&](int s) {
+            auto issue_pv = [&](int s, bool first) {
 #pragma unroll
                 for (int h = 0; h < NS; ++h) {
 #pragma unroll
@@ -142,35 +177,27 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         const uint64_t da = bw::umma_smem_desc_sw128(bw::smem_u32(p_s)) + 2 * kk;
                         const uint64_t db = bw::umma_smem_desc_mn_sw128(bw::smem_u32(v_s + s * KV_BYTES + h * KV_SLICE), KV_SLICE)
                                             + (uint64_t)kk * (2048 >> 4);   // 16 keys = two 8-row groups
-                        bw::umma_bf16(tmem_O + h * 64, da, db, IDESC_PV, kk != 0);
+                        bw::umma_bf16(tmem_O + h * 64, da, db, IDESC_PV, !(first && kk == 0));
                     }
                 }
-                bw::umma_commit(o_full);
-                bw::umma_commit(kv_empty + 8 * s);
+                bw::umma_commit(pv_done);
+                bw::umma_commit(v_empty + 8 * s);
             };
-            // queries: one 3-D box per column slice (channels x the G heads of this kv head x tokens)
-            bw::mbar_expect_tx(q_full, NS * p.G * p.tpt * 128);
-#pragma unroll
-            for (int h = 0; h < NS; ++h)
-                bw::tma_load_3d(bw::smem_u32(q_s + h * Q_SLICE), &tmQ, q_full, h * 64, g * p.G, p.cu_q[r] + tok0);
-            load_tile(0);
-            if (n_tiles > 1) load_tile(1);
-            bool ok = bw::mbar_wait(q_full, 0, &g_status, 11) && bw::mbar_wait(kv_full, 0, &g_status, 12);
+            bool ok = bw::mbar_wait(q_full, 0, &g_status, 11) && bw::mbar_wait(k_full, 0, &g_status, 12);
             if (ok) { bw::tc_fence_after(); issue_qk(0); }
             for (int i = 0; i < n_tiles && ok; ++i) {
                 const int s = i & 1;
-                if (!bw::mbar_wait(p_full, i & 1, &g_status, 13)) break;   // P(i) written, S free again
-                bw::tc_fence_after();
-                issue_pv(s);
                 if (i + 1 < n_tiles) {
-                    if (!bw::mbar_wait(kv_full + 8 * (s ^ 1), ((i + 1) >> 1) & 1, &g_status, 14)) break;
+                    // S of the next tile, while the softmax warps work on this one (its buffer was
+                    // read for the last time before P of tile i - 1 was signalled)
+                    if (!bw::mbar_wait(k_full + 8 * (s ^ 1), ((i + 1) >> 1) & 1, &g_status, 14)) break;
                     bw::tc_fence_after();
                     issue_qk(s ^ 1);
                 }
-                if (i + 2 < n_tiles) {
-                    if (!bw::mbar_wait(kv_empty + 8 * s, (i >> 1) & 1, &g_status, 15)) break;
-                    load_tile(i + 2);
-                }
+                if (!bw::mbar_wait(p_full, i & 1, &g_status, 13)) break;   // P(i) written, O rescaled
+                if (!bw::mbar_wait(v_full + 8 * s, (i >> 1) & 1, &g_status, 20)) break;
+                bw::tc_fence_after();
+                issue_pv(s, i == 0);
             }
         }
     } else {
@@ -180,67 +207,84 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int qpos = q_pos0 + tok;
         const int lo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-        float m = -INFINITY, l = 0.f;
-        float acc[HD];
-#pragma unroll
-        for (int c = 0; c < HD; ++c) acc[c] = 0.f;
+        float m = -INFINITY, l = 0.f;   // m: the reference of the exponents (at most 8 below the row maximum)
         uint8_t* p_row = p_s + row * 128;
+        bool ok = true;
 
         for (int i = 0; i < n_tiles; ++i) {
-            if (!bw::mbar_wait(s_full, i & 1, &g_status, 16)) break;
+            if (!__all_sync(0xffffffffu, bw::mbar_wait(s_full + 8 * (i & 1), (i >> 1) & 1, &g_status, 16))) { ok = false; break; }
             bw::tc_fence_after();
             const int key0 = (t_lo + i) * BN;
             const bool need_mask = !row_ok || (key0 + BN - 1 > q_pos0) || (p.window > 0 && key0 < last_pos - p.window + 1);
-            // pass 1: the row's maximum
+            float sv[BN];
             float mx = -INFINITY;
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
-                bw::tmem_ld_32x32(tmem_S + lane_base + c0, v);
+                bw::tmem_ld_32x32(tmem_S + 64 * (i & 1) + lane_base + c0, v);
                 bw::tmem_ld_wait();
+                if (need_mask) {   // one branch per half tile, not one per key
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    float s = __uint_as_float(v[c]) * p.scale_log2;
-                    if (need_mask) { const int kp = key0 + c0 + c; if (!row_ok || kp > qpos || kp < lo) s = -INFINITY; }
-                    mx = fmaxf(mx, s);
+                    for (int c = 0; c < 32; ++c) {
+                        const int kp = key0 + c0 + c;
+                        const float s = (!row_ok || kp > qpos || kp < lo) ? -INFINITY : __uint_as_float(v[c]) * p.scale_log2;
+                        sv[c0 + c] = s;
+                        mx = fmaxf(mx, s);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const float s = __uint_as_float(v[c]) * p.scale_log2;
+                        sv[c0 + c] = s;
+                        mx = fmaxf(mx, s);
+                    }
                 }
             }
-            const float m_new = fmaxf(m, mx);
-            const float mu = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = fast_exp2(m - mu);
-            m = m_new;
-            // pass 2: probabilities, rounded to bfloat16 into the swizzled P tile
+            // P V of the tile before: P may be overwritten and O read once it is done
+            if (i > 0) {
+                if (!__all_sync(0xffffffffu, bw::mbar_wait(pv_done, (i - 1) & 1, &g_status, 17))) { ok = false; break; }
+                bw::tc_fence_after();
+            }
+            const bool grow = mx > m + 8.f;   // also the first finite maximum of a row (m is -inf until then)
+            float factor = 1.f;
+            if (grow) {
+                if (m != -INFINITY) factor = fast_exp2(m - mx);
+                l *= factor;
+                m = mx;
+            }
+            if (i > 0 && __any_sync(0xffffffffu, grow)) {
+#pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t v[32];
+                    bw::tmem_ld_32x32(tmem_O + lane_base + c0, v);
+                    bw::tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * factor);
+                    bw::tmem_st_32x32(tmem_O + lane_base + c0, v);
+                }
+                bw::tmem_st_wait();
+            }
+            const float mu = m == -INFINITY ? 0.f : m;
+            // probabilities, rounded to bfloat16 into the swizzled P tile
             float sum = 0.f;
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                bw::tmem_ld_32x32(tmem_S + lane_base + c0, v);
-                bw::tmem_ld_wait();
-                uint32_t packed[16];
+            for (int c0 = 0; c0 < BN; c0 += 8) {
+                uint32_t packed[4];
 #pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    float s0 = __uint_as_float(v[c]) * p.scale_log2, s1 = __uint_as_float(v[c + 1]) * p.scale_log2;
-                    if (need_mask) {
-                        const int kp = key0 + c0 + c;
-                        if (!row_ok || kp > qpos || kp < lo) s0 = -INFINITY;
-                        if (!row_ok || kp + 1 > qpos || kp + 1 < lo) s1 = -INFINITY;
-                    }
-                    const float p0 = fast_exp2(s0 - mu), p1 = fast_exp2(s1 - mu);
+                for (int c = 0; c < 8; c += 2) {
+                    const float p0 = fast_exp2(sv[c0 + c] - mu), p1 = fast_exp2(sv[c0 + c + 1] - mu);
                     sum += p0 + p1;
                     packed[c >> 1] = pack_bf16(p0, p1);
                 }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {   // four 16-byte chunks of 8 keys each
-                    const int chunk = (c0 >> 3) + j;
-                    *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) =
-                        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-                }
+                const int chunk = c0 >> 3;   // 16-byte chunk of 8 keys
+                *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            l = l * corr + sum;
+            l += sum;
             // Values of keys that do not exist (past the request's length, or on a page the block
             // table no longer holds) are whatever the stand-in page contained: zero them, since a
             // probability of 0 times a stale NaN would still be NaN.  Rare: the last tile, a window's edge.
             if (key0 + BN > kv_len || (p.window > 0 && key0 < first_key)) {
+                if (!__all_sync(0xffffffffu, bw::mbar_wait(v_full + 8 * (i & 1), (i >> 1) & 1, &g_status, 21))) { ok = false; break; }
                 for (int pg = 0; pg < BN / p.page_size; ++pg) {
                     const int pkey = key0 + pg * p.page_size;
                     int bad_from = p.page_size;   // first row of this page to clear
@@ -258,27 +302,27 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             bw::tc_fence_before();
             __syncwarp();
             if (lane == 0) bw::mbar_arrive(p_full);
-            // fold O_tile = P V into the accumulators
-            if (!bw::mbar_wait(o_full, i & 1, &g_status, 17)) break;
+        }
+        if (ok) ok = __all_sync(0xffffffffu, bw::mbar_wait(pv_done, (n_tiles - 1) & 1, &g_status, 18));
+        if (ok) {
             bw::tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok0 + tok) * p.nh + g * p.G + hg) * HD;
 #pragma unroll
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t v[32];
                 bw::tmem_ld_32x32(tmem_O + lane_base + c0, v);
                 bw::tmem_ld_wait();
+                if (row_ok) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) acc[c0 + c] = fmaf(acc[c0 + c], corr, __uint_as_float(v[c]));
-            }
-            bw::tc_fence_before();
-        }
-        if (row_ok) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok0 + tok) * p.nh + g * p.G + hg) * HD;
-#pragma unroll
-            for (int c = 0; c < HD; c += 8) {
-                *reinterpret_cast<uint4*>(dst + c) =
-                    make_uint4(pack_bf16(acc[c] * inv, acc[c + 1] * inv), pack_bf16(acc[c + 2] * inv, acc[c + 3] * inv),
-                               pack_bf16(acc[c + 4] * inv, acc[c + 5] * inv), pack_bf16(acc[c + 6] * inv, acc[c + 7] * inv));
+                    for (int c = 0; c < 32; c += 8) {
+                        *reinterpret_cast<uint4*>(dst + c0 + c) =
+                            make_uint4(pack_bf16(__uint_as_float(v[c]) * inv, __uint_as_float(v[c + 1]) * inv),
+                                       pack_bf16(__uint_as_float(v[c + 2]) * inv, __uint_as_float(v[c + 3]) * inv),
+                                       pack_bf16(__uint_as_float(v[c + 4]) * inv, __uint_as_float(v[c + 5]) * inv),
+                                       pack_bf16(__uint_as_float(v[c + 6]) * inv, __uint_as_float(v[c + 7]) * inv));
+                    }
+                }
             }
         }
     }
@@ -360,7 +404,7 @@ BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_
     p.work = work; p.max_blocks = max_blocks; p.nh = nh; p.nkv = nkv; p.G = G; p.page_size = page_size;
     p.window = window > 0 ? window : 0; p.tpt = tpt;
     p.scale_log2 = scale * 1.4426950408889634f;
-    bw::launch((attn_tc_kernel), dim3(n_items, nkv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, tq, tk, tv, p);
+    bw::launch((attn_tc_kernel), dim3((unsigned)n_items * nkv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, tq, tk, tv, p);
     BW_LAUNCH_CHECK();
     return 0;
 }
