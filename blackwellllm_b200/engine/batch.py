@@ -11,6 +11,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -108,7 +109,6 @@ class BatchBuilder:
         a_cu, a_qs, a_kv, a_sl = take(R + 1), take(R), take(R), take(R)
         a_lr = take(n_want)
         a_bt = {g: take(R * w) for g, w in widths.items()}
-        import numpy as np
         q_lens = np.fromiter((len(sg[1]) for sg in segments), dtype=np.int32, count=R)
         q_starts = np.fromiter((sg[2] for sg in segments), dtype=np.int32, count=R)
         cu = np.zeros(R + 1, dtype=np.int32)
@@ -138,6 +138,18 @@ class BatchBuilder:
             view[:] = -1
             for r, row in enumerate(rows):
                 view[r, :len(row)] = row
+        return self.finish(host, T, R, n_want, widths, [sg[0] for sg in segments], into)
+
+    def pinned(self, n: int) -> torch.Tensor:
+        """A pinned int32 buffer of at least ``n`` words from the ring (the one :meth:`finish` sends)."""
+        return self._pinned(n)
+
+    def finish(self, host: torch.Tensor, T: int, R: int, n_want: int, widths: Dict[int, int], rids: List[object],
+               into: Optional[torch.Tensor] = None) -> StepBatch:
+        """Sends a packed step (the layout of :meth:`build`: token ids, positions, request of token,
+        cu_q, q_start, kv_len, slot, logit rows, one block table per group) to the device in one
+        copy and returns the views of it."""
+        total = 3 * T + (R + 1) + 3 * R + n_want + sum(R * w for w in widths.values())
         if into is not None:
             if into.numel() != total:
                 raise ValueError(f"static batch buffer holds {into.numel()} words, this batch needs {total}")
@@ -149,6 +161,20 @@ class BatchBuilder:
             ev = self._events[self._slot] or torch.cuda.Event()
             ev.record()
             self._events[self._slot] = ev
+        h = host[:total].numpy()
+        off = 0
+
+        def take(n):
+            nonlocal off
+            a = (off, off + n)
+            off += n
+            return a
+
+        a_tok, a_pos, a_req = take(T), take(T), take(T)
+        a_cu, a_qs, a_kv, a_sl = take(R + 1), take(R), take(R), take(R)
+        a_lr = take(n_want)
+        a_bt = {g: take(R * w) for g, w in widths.items()}
+        cu = h[a_cu[0]:a_cu[1]]
 
         def d(a):
             return dev[a[0]:a[1]]
@@ -157,6 +183,5 @@ class BatchBuilder:
             T=T, R=R, token_ids=d(a_tok), positions=d(a_pos), req_of_token=d(a_req), cu_q=d(a_cu),
             q_start=d(a_qs), kv_len=d(a_kv), state_slot=d(a_sl), logit_rows=d(a_lr),
             block_tables={g: d(a_bt[g]).view(R, widths[g]) for g in widths},
-            h_q_start=[s[2] for s in segments], h_q_len=[len(s[1]) for s in segments],
-            h_kv_len=[s[3] for s in segments], h_slots=[s[4] for s in segments],
-            rids=[s[0] for s in segments])
+            h_q_start=h[a_qs[0]:a_qs[1]].tolist(), h_q_len=(cu[1:] - cu[:-1]).tolist(),
+            h_kv_len=h[a_kv[0]:a_kv[1]].tolist(), h_slots=h[a_sl[0]:a_sl[1]].tolist(), rids=list(rids))

@@ -19,9 +19,11 @@ import os
 from dataclasses import dataclass
 from typing import Dict, List, Mapping, Optional, Sequence
 
+import numpy as np
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import (ERR_BAD_TOKEN, ERR_BAD_WANT, ERR_NO_SLOT, ERR_OUT_OF_PAGES, ERR_TOO_MANY_TOKENS,
+                             ERR_TOO_SMALL, CacheManager, native)
 from ..cache.pages import OutOfPages
 from ..config.registry import load_config, parse_config
 from ..config.specs import ModelConfig
@@ -158,14 +160,64 @@ class Engine:
     # ------------------------------------------------------------------ the step
     def prepare(self, entries: Sequence[StepEntry], min_blocks: int = 0, into=None) -> StepBatch:
         """Checks the entries, reserves pages for all their tokens (all or nothing)
-        and uploads the batch."""
-        V = self.config.vocab_size
+        and uploads the batch.  The checks, the page bookkeeping and the packing of the
+        step's buffer are one call into the C++ host runtime."""
+        cache = self.cache
+        R = len(entries)
+        handles = np.empty(R, dtype=np.int32)
+        n_tok = np.empty(R, dtype=np.int32)
+        n_want = np.empty(R, dtype=np.int32)
         seen = set()
-        T = 0
-        for e in entries:
+        for i, e in enumerate(entries):
             if e.rid in seen:
                 raise EngineError(f"request {e.rid!r} appears twice in one step")
             seen.add(e.rid)
+            handles[i] = cache.handle(e.rid)
+            n_tok[i] = len(e.tokens)
+            n_want[i] = len(e.want)
+        T, W = int(n_tok.sum()), int(n_want.sum())
+        if T == R:
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
+        else:
+            tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T)
+        want = np.fromiter((w for e in entries for w in e.want), dtype=np.int64, count=W)
+        V = self.config.vocab_size
+        if T and (tokens.min() < 0 or tokens.max() >= V):     # also keeps the ids inside int32
+            self._explain(entries, ERR_BAD_TOKEN)
+        if W and (want.min() < 0 or want.max() >= 2 ** 31):
+            self._explain(entries, ERR_BAD_WANT)
+        tokens, want = tokens.astype(np.int32), want.astype(np.int32)
+        G = len(cache.groups)
+        blocks_bound = max(min_blocks, self._graph_width + -(-self.options.max_batch_tokens // cache.page_size) + 1)
+        cap = 3 * T + 4 * R + 1 + W + G * R * blocks_bound
+        meta = np.zeros(4 + max(G, 1), dtype=np.int64)
+        new_slots = np.zeros(max(R, 1), dtype=np.int32)
+        was_new = handles < 0
+        for attempt in range(2):
+            host = self._builder.pinned(cap)
+            total = native().bwh_pack_step(cache._h, R, handles.ctypes.data, n_tok.ctypes.data, tokens.ctypes.data,
+                                           n_want.ctypes.data, want.ctypes.data, V, min_blocks,
+                                           self.options.max_batch_tokens, host.data_ptr(), cap, meta.ctypes.data,
+                                           new_slots.ctypes.data)
+            if total != ERR_TOO_SMALL:
+                break
+            # a request longer than max_context: no table is longer than its group's pool (nothing changed yet)
+            cap = 3 * T + 4 * R + 1 + W + G * R * (max([min_blocks] + [g.num_pages for g in cache.groups]) + 1)
+        if total < 0:
+            self._explain(entries, int(total))
+        k = 0
+        for i in np.nonzero(was_new)[0]:
+            cache.adopt(entries[i].rid, int(handles[i]))
+            cache.zero_state(int(new_slots[k]))
+            k += 1
+        widths = {g: int(meta[4 + g]) for g in range(G)}
+        return self._builder.finish(host, T, R, W, widths, [e.rid for e in entries], into)
+
+    def _explain(self, entries: Sequence[StepEntry], code: int) -> None:
+        """Raises the error that the host runtime's code stands for, with the offending entry named."""
+        V = self.config.vocab_size
+        T = sum(len(e.tokens) for e in entries)
+        for e in entries:
             n = len(e.tokens)
             if n == 0:
                 raise EngineError(f"request {e.rid!r}: a step entry needs at least one token")
@@ -175,35 +227,20 @@ class Engine:
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise EngineError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
-            T += n
-        if T > self.options.max_batch_tokens:
+        if code == ERR_TOO_MANY_TOKENS:
             raise EngineError(f"step of {T} tokens exceeds max_batch_tokens={self.options.max_batch_tokens}")
-        new = [e.rid for e in entries if not self.cache.has(e.rid)]
-        if len(new) > self.cache.slots.num_free:
-            raise OutOfPages(f"{len(new)} new requests but {self.cache.slots.num_free} request slots are free")
-        n_groups = len(self.cache.groups)
-        need = [0] * n_groups
-        ps = self.cache.page_size
-        for e in entries:
-            if self.cache.has(e.rid):
-                pn = self.cache.pages_needed(e.rid, len(e.tokens))
-            else:
-                pn = [-(-len(e.tokens) // ps)] * n_groups
-            need = [a + b for a, b in zip(need, pn)]
-        free = self.cache.free_pages()
-        if any(n > f for n, f in zip(need, free)):
-            raise OutOfPages(f"step needs {need} pages per group, {free} are free")
-        for rid in new:
-            self.cache.add_request(rid)
-        segments, rows, t0 = [], [], 0
-        for e in entries:
-            q_start = self.cache.append(e.rid, len(e.tokens))
-            segments.append((e.rid, [int(t) for t in e.tokens], q_start, q_start + len(e.tokens),
-                             self.cache.slot(e.rid)))
-            rows.extend(t0 + int(w) for w in e.want)
-            t0 += len(e.tokens)
-        block_rows = {g: [self.cache.block_row(e.rid, g) for e in entries] for g in range(n_groups)}
-        return self._builder.build(segments, rows, block_rows, min_blocks=min_blocks, into=into)
+        if code == ERR_NO_SLOT:
+            new = sum(1 for e in entries if not self.cache.has(e.rid))
+            raise OutOfPages(f"{new} new requests but {self.cache.slots.num_free} request slots are free")
+        if code == ERR_OUT_OF_PAGES:
+            ps = self.cache.page_size
+            need = [0] * len(self.cache.groups)
+            for e in entries:
+                pn = self.cache.pages_needed(e.rid, len(e.tokens)) if self.cache.has(e.rid) \
+                    else [-(-len(e.tokens) // ps)] * len(need)
+                need = [a + b for a, b in zip(need, pn)]
+            raise OutOfPages(f"step needs {need} pages per group, {self.cache.free_pages()} are free")
+        raise EngineError(f"the host runtime refused the step (code {code})")
 
     # A decode-only step (one token and one wanted place per request) has the same
     # shapes every time: its kernels are captured once per batch size in a CUDA graph
@@ -268,8 +305,7 @@ class Engine:
                 batch = self.prepare(entries)
                 logits = self.model.forward(batch, self.cache.views)
                 T = batch.T
-        for e in entries:
-            self.cache.release_passed(e.rid)
+        self.cache.release_passed_many([e.rid for e in entries])
         self.steps_run += 1
         self.tokens_run += T
         return logits

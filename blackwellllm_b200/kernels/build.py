@@ -166,3 +166,51 @@ def load_library(name: str, macros: Optional[Mapping[str, object]] = None,
             lib = ctypes.CDLL(path)
             _loaded[key] = lib
         return lib
+
+
+# ------------------------------------------------------------------ host libraries (no GPU code)
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def find_cxx() -> str:
+    for c in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        if c and shutil.which(c):
+            return shutil.which(c)
+    raise BuildError("no C++ compiler found (looked at $CXX, g++, c++, clang++); the host runtime of "
+                     "blackwellllm_b200 cannot be built")
+
+
+def compile_host_library(name: str, verbose: bool = True) -> str:
+    """Builds (if needed) ``csrc/<name>.cpp`` with the host compiler; returns the library's path."""
+    src = os.path.join(CSRC, name + ".cpp")
+    if not os.path.isfile(src):
+        raise BuildError(f"no such source: {src}")
+    out = os.path.join(build_dir(), f"{name}-{_source_hash(src, HOST_FLAGS, {})}.so")
+    if os.path.isfile(out):
+        return out
+    tmp = f"{out}.{os.getpid()}.tmp"
+    cmd = [find_cxx()] + HOST_FLAGS + ["-I", CSRC, "-o", tmp, src]
+    t0 = time.time()
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    if proc.returncode != 0:
+        try:
+            os.remove(tmp)
+        except OSError:
+            pass
+        raise BuildError(f"the host compiler failed for {name} (exit {proc.returncode}):\n"
+                         f"{' '.join(cmd)}\n{proc.stdout.decode(errors='replace')}")
+    os.replace(tmp, out)
+    if verbose:
+        print(f"[blackwellllm_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
+              file=sys.stderr, flush=True)
+    return out
+
+
+def load_host_library(name: str) -> ctypes.CDLL:
+    key = "host|" + name
+    with _lock:
+        lib = _loaded.get(key)
+        if lib is None:
+            lib = ctypes.CDLL(compile_host_library(name))
+            _loaded[key] = lib
+        return lib

@@ -6,7 +6,7 @@ import pytest
 from hypothesis import given, settings, strategies as st
 
 from blackwellllm_b200.cache.manager import CacheManager
-from blackwellllm_b200.cache.pages import OutOfPages, PageAllocator, SlotAllocator
+from blackwellllm_b200.cache.pages import OutOfPages
 from blackwellllm_b200.engine.scheduler import RequestRefused, Scheduler
 from blackwellllm_b200.parts.base import FixedStateRequest, PagedKVRequest
 from blackwellllm_b200.sampling.params import SamplingParams, philox4x32, uniform
@@ -16,27 +16,42 @@ WIN = PagedKVRequest(2, 16, 20)
 
 
 def test_allocator_basics():
-    a = PageAllocator(4)
-    got = a.allocate(3)
-    assert sorted(got) == [0, 1, 2] and a.num_free == 1
-    assert a.try_allocate(2) is None and a.num_free == 1  # never a part of them
+    """Pages through the manager: all or nothing, lowest ids first, the page just freed is used again first."""
+    cm = CacheManager([FULL], page_size=8, num_pages=4, max_requests=2)
+    cm.add_request("a")
+    assert cm.append("a", 24) == 0
+    assert cm.block_table("a", 0) == [0, 1, 2] and cm.free_pages() == [1]
+    cm.add_request("b")
     with pytest.raises(OutOfPages):
-        a.allocate(2)
-    a.free([got[0]])
-    with pytest.raises(ValueError, match="freed twice"):
-        a.free([got[0]])
-    with pytest.raises(ValueError, match="outside"):
-        a.free([9])
-    assert a.allocate(1) == [got[0]]  # LIFO: the page just freed is used again first
+        cm.append("b", 9)                        # needs two pages, one is free
+    assert cm.free_pages() == [1] and cm.length("b") == 0 and cm.block_table("b", 0) == []   # never a part of them
+    cm.truncate("a", 16)                         # gives page 2 back
+    assert cm.free_pages() == [2]
+    assert cm.append("b", 8) == 0
+    assert cm.block_table("b", 0) == [2]         # LIFO: the page just freed is used again first
+    cm.check_invariants()
+    with pytest.raises(ValueError):
+        cm.append("a", 0)
+    with pytest.raises(KeyError):
+        cm.free_request("never added")
+    with pytest.raises(ValueError):
+        CacheManager([FULL], page_size=8, num_pages=0, max_requests=2)
 
 
 def test_slots():
-    s = SlotAllocator(2)
-    a, b = s.try_allocate(), s.try_allocate()
-    assert {a, b} == {0, 1} and s.try_allocate() is None
-    s.free(a)
+    cm = CacheManager([FULL], page_size=8, num_pages=4, max_requests=2)
+    a, b = cm.add_request("a"), cm.add_request("b")
+    assert {a, b} == {0, 1} and cm.slots.num_free == 0
+    with pytest.raises(OutOfPages):
+        cm.add_request("c")
     with pytest.raises(ValueError):
-        s.free(a)
+        cm.add_request("a")                      # already live
+    cm.free_request("a")
+    assert cm.slots.num_free == 1
+    with pytest.raises(KeyError):
+        cm.free_request("a")                     # not twice
+    assert cm.add_request("c") == a              # the slot just freed is used again
+    cm.check_invariants()
 
 
 def test_groups_by_need():
