@@ -298,3 +298,111 @@ def test_philox_stream():
     us = [uniform(7, i) for i in range(1000)]
     assert all(0.0 <= u < 1.0 for u in us) and 0.45 < sum(us) / 1000 < 0.55
     assert uniform(7, 3) == us[3] and uniform(8, 3) != us[3]
+
+
+# ---------------------------------------------------------------------------------------------
+# The host runtime's packed step against the same step put together call by call
+
+def _pack(cm, entries, vocab=1000, min_blocks=0, max_tokens=10 ** 6, cap=1 << 16):
+    import numpy as np
+    from blackwellllm_b200.cache.manager import native
+    R = len(entries)
+    handles = np.array([cm.handle(r) for r, _, _ in entries], dtype=np.int32)
+    n_tok = np.array([len(t) for _, t, _ in entries], dtype=np.int32)
+    n_want = np.array([len(w) for _, _, w in entries], dtype=np.int32)
+    tokens = np.array([x for _, t, _ in entries for x in t], dtype=np.int32)
+    want = np.array([x for _, _, w in entries for x in w], dtype=np.int32)
+    out = np.full(cap, -7, dtype=np.int32)
+    meta = np.zeros(4 + len(cm.groups), dtype=np.int64)
+    new_slots = np.zeros(R, dtype=np.int32)
+    total = native().bwh_pack_step(cm._h, R, handles.ctypes.data, n_tok.ctypes.data, tokens.ctypes.data,
+                                   n_want.ctypes.data, want.ctypes.data, vocab, min_blocks, max_tokens,
+                                   out.ctypes.data, cap, meta.ctypes.data, new_slots.ctypes.data)
+    if total >= 0:
+        for (rid, _, _), h in zip(entries, handles):
+            if not cm.has(rid):
+                cm.adopt(rid, int(h))
+    return int(total), out, meta
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_packed_step_equals_the_step_built_call_by_call(seed):
+    import torch
+    from blackwellllm_b200.cache import manager as M
+    from blackwellllm_b200.engine.batch import BatchBuilder
+    rng = random.Random(seed)
+    pages = rng.randint(12, 30)
+    a = CacheManager([FULL, WIN, FULL], page_size=8, num_pages=[pages, pages], max_requests=4)   # packed
+    b = CacheManager([FULL, WIN, FULL], page_size=8, num_pages=[pages, pages], max_requests=4)   # call by call
+    live, next_id = [], 0
+    for step in range(40):
+        entries = []
+        for rid in list(live):
+            if rng.random() < 0.6:
+                n = rng.choice([1, 1, 1, 2, 5, 13])
+                entries.append((rid, [rng.randrange(1000) for _ in range(n)], sorted(rng.sample(range(n), rng.randint(0, min(n, 2))))))
+        while len(live) + sum(1 for e in entries if e[0] not in live) < 4 and rng.random() < 0.5:
+            n = rng.randint(1, 30)
+            entries.append((f"r{next_id}", [rng.randrange(1000) for _ in range(n)], [n - 1]))
+            next_id += 1
+        if not entries:
+            continue
+        rng.shuffle(entries)
+        min_blocks = rng.choice([0, 0, 7])
+        before = (a.free_pages(), a.slots.num_free, {r: a.length(r) for r in live})
+        total, out, meta = _pack(a, entries, min_blocks=min_blocks)
+        # the same step, call by call, on the twin
+        need = [0, 0]
+        for rid, t, _ in entries:
+            pn = b.pages_needed(rid, len(t)) if b.has(rid) else [-(-len(t) // 8)] * 2
+            need = [x + y for x, y in zip(need, pn)]
+        if any(n > f for n, f in zip(need, b.free_pages())):
+            assert total == M.ERR_OUT_OF_PAGES
+            assert (a.free_pages(), a.slots.num_free, {r: a.length(r) for r in live}) == before   # nothing changed
+            victim = rng.choice(live)                      # make room and go on
+            a.free_request(victim); b.free_request(victim); live.remove(victim)
+            continue
+        assert total > 0
+        segs, rows, t0 = [], [], 0
+        for rid, t, w in entries:
+            if not b.has(rid):
+                b.add_request(rid)
+                live.append(rid)
+            q0 = b.append(rid, len(t))
+            segs.append((rid, t, q0, q0 + len(t), b.slot(rid)))
+            rows += [t0 + x for x in w]
+            t0 += len(t)
+        block_rows = {g: [b.block_table(rid, g) for rid, _, _ in entries] for g in range(2)}
+        ref = BatchBuilder(torch.device("cpu")).build(segs, rows, block_rows, min_blocks=min_blocks)
+        T, R = ref.T, ref.R
+        flat = torch.cat([ref.token_ids, ref.positions, ref.req_of_token, ref.cu_q, ref.q_start, ref.kv_len,
+                          ref.state_slot, ref.logit_rows] + [ref.block_tables[g].reshape(-1) for g in range(2)])
+        assert total == flat.numel() == meta[2] and meta[0] == T and meta[1] == len(rows)
+        assert [int(meta[4]), int(meta[5])] == [ref.block_tables[0].shape[1], ref.block_tables[1].shape[1]]
+        assert out[:total].tolist() == flat.tolist()
+        assert int(out[total]) == -7                       # nothing written past the end
+        for rid, _, _ in entries:
+            assert a.release_passed(rid) == b.release_passed(rid)
+        a.check_invariants(); b.check_invariants()
+        assert a.free_pages() == b.free_pages()
+        for rid in list(live):
+            if rng.random() < 0.15:
+                a.free_request(rid); b.free_request(rid); live.remove(rid)
+
+
+def test_packed_step_refusals_change_nothing():
+    from blackwellllm_b200.cache import manager as M
+    cm = CacheManager([FULL], page_size=8, num_pages=4, max_requests=2)
+    cm.add_request("a")
+    cm.append("a", 5)
+    state = (cm.free_pages(), cm.slots.num_free, cm.length("a"))
+    assert _pack(cm, [("a", [1, 2000], [0])])[0] == M.ERR_BAD_TOKEN
+    assert _pack(cm, [("a", [1, -1], [0])])[0] == M.ERR_BAD_TOKEN
+    assert _pack(cm, [("a", [1, 2], [2])])[0] == M.ERR_BAD_WANT
+    assert _pack(cm, [("a", [1, 2], [0]), ("a", [3], [0])])[0] == M.ERR_TWICE
+    assert _pack(cm, [("a", [1] * 9, [0])], max_tokens=8)[0] == M.ERR_TOO_MANY_TOKENS
+    assert _pack(cm, [("a", [1], [0]), ("n1", [1], [0]), ("n2", [1], [0])])[0] == M.ERR_NO_SLOT
+    assert _pack(cm, [("a", [1] * 20, [0]), ("n1", [1] * 9, [0])])[0] == M.ERR_OUT_OF_PAGES
+    assert _pack(cm, [("a", [1], [0])], cap=5)[0] == M.ERR_TOO_SMALL
+    assert (cm.free_pages(), cm.slots.num_free, cm.length("a")) == state and not cm.has("n1")
+    cm.check_invariants()
