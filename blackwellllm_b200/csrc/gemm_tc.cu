@@ -604,7 +604,10 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const Epilogue& ep, int k
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
-    const int grid = num_work < NUM_SMS ? num_work : NUM_SMS;
+    // the narrow kernel fits twice on an SM: with more items than SMs all of them stream side by side
+    // (decode is bound by bytes in flight, not by CTAs), instead of a second, partly empty round
+    const int slots = BN <= 16 ? 2 * NUM_SMS : NUM_SMS;
+    const int grid = num_work < slots ? num_work : slots;
     bw::launch((gemm_tc_kernel<BN, ROPE>), dim3(grid), dim3(THREADS), smem, s, a, b, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work);
     BW_LAUNCH_CHECK();
     return 0;
