@@ -546,7 +546,9 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         bw::tma_prefetch_desc(&tmK); bw::tma_prefetch_desc(&tmV);
     }
     __syncthreads();
-    BW_PDL_WAIT();
+    // The step's lists (work items, lengths, block tables) were on the device before the step's first
+    // kernel ran; only the queries, and the keys and values of this step's own tokens, come from the
+    // kernels just before this one.  The wait for those kernels therefore comes late (below).
     const int4 w = reinterpret_cast<const int4*>(p.work)[blockIdx.x];
     const int r = w.x, slice = w.y, n_slices = w.z, item = w.w, g = blockIdx.y;
     const int warp = threadIdx.x >> 5;
@@ -595,8 +597,12 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
 
+    // a first tile that holds none of this step's tokens is requested before the wait
+    const bool early = t_lo <= t_hi && t_lo * BN + BN <= q_pos0;
+    if (early && warp == 0) { lookup(t_lo); issue_tile(0); lookup(t_lo + 1); }
+    BW_PDL_WAIT();
     if (t_lo <= t_hi) {
-        if (warp == 0) { lookup(t_lo); issue_tile(0); lookup(t_lo + 1); }
+        if (!early && warp == 0) { lookup(t_lo); issue_tile(0); lookup(t_lo + 1); }
         load_q_rows(p, p.cu_q[r], g, 0, n_rows, q_tile, 16);
         cp_async_commit();
         cp_async_wait<0>();
