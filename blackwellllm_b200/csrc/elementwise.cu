@@ -151,9 +151,10 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
                                    OT* __restrict__ v_pages, int nh, int nkv, int hd,
                                    int page_size, int num_pages, int paired) {
     BW_PDL_TRIGGER();
-    BW_PDL_WAIT();
     // A block takes ROPE_HPB heads of one token; a thread takes one channel of each of them: the
     // loads of the heads are independent and in flight together, the angle is looked up once.
+    // Positions and block tables were on the device before the step's first kernel ran, so the page
+    // is looked up before the wait for the kernels that make qkv and the table.
     const int t = blockIdx.x, h0 = blockIdx.y * ROPE_HPB;
     const int n_heads = nh + 2 * nkv;
     const int pos = positions[t];
@@ -166,6 +167,7 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
         slot = pos % page_size;
         if (page >= num_pages) page = -1;
     }
+    BW_PDL_WAIT();
     for (int c = threadIdx.x; c < hd; c += blockDim.x) {
         float sn = 0.f, cs = 1.f;
         const bool rot_c = c < rotary_dim;
