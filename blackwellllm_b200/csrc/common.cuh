@@ -41,16 +41,23 @@ inline bool pdl_enabled() {
     return v != 0;
 }
 
+// overlap == false: an ordinary launch (the kernel starts when everything before it is complete)
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                          Args&&... args) {
+inline cudaError_t launch_opt(bool overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = (overlap && pdl_enabled()) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+    return launch_opt(true, kernel, grid, block, smem, stream, std::forward<Args>(args)...);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

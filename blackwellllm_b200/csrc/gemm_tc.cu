@@ -20,6 +20,7 @@
 // Roles (192 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps
 // 2..5 epilogue (TMEM lane quarter = warp % 4).  Every wait is bounded; a timeout sets
 // the status word and all roles fall through to the common exit where TMEM is freed.
+#include <cstring>
 #include "tcgen05.cuh"
 
 using bf16 = __nv_bfloat16;
@@ -32,7 +33,7 @@ constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int THREADS = 192;
 constexpr int NUM_SMS = 148;
-constexpr int STAGING_BYTES = 4 * 32 * 33 * 4;          // one 32 x 33 float block per epilogue warp
+constexpr int STAGING_BYTES = 4 * 2 * 4096;   // per epilogue warp: a 32 x 33 float block, or two 32 x 32 boxes for TMA
 constexpr int SMEM_BUDGET = 226 * 1024 - STAGING_BYTES - 2048;
 constexpr int FUSED_REDUCE_MAX_TOKENS = 16;   // split-K sums inside the kernel up to this many tokens
 constexpr int SWIGLU_BLOCK = 16;   // gate/up features are interleaved in blocks of 16 rows of the weight
@@ -60,6 +61,7 @@ struct Epilogue {
     int out_type, bias_type, accumulate, transposed, swiglu;
     int tokens, features, splits;
     int rope_on;
+    int tma_add;          // normal orientation, out += : 32 x 32 boxes go out through the tensor map tmC
     RopeOut rope;
 };
 
@@ -279,7 +281,7 @@ __device__ __forceinline__ void rope_direct(const Epilogue& ep, const uint32_t (
 template <int BN, bool ROPE>
 __global__ void __launch_bounds__(THREADS, BN <= 16 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               Epilogue ep, int kb_total, int kb_per_split, int tiles_a, int tiles_b, int num_work) {
+               const __grid_constant__ CUtensorMap tmC, Epilogue ep, int kb_total, int kb_per_split, int tiles_a, int tiles_b, int num_work) {
     constexpr int STAGES = stages_for<BN>();
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -422,6 +424,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     for (int c = 0; c < CH; ++c) vals[c] = __uint_as_float(v[c]);
                     const int token0 = tile_b * BN + c0;
                     emit<CH, ROPE>(ep, part, vals, token0, min(CH, b_rows - token0), ga, ga < a_rows);
+                } else if (ep.tma_add) {
+                    if constexpr (CH == 32 && !ROPE) {
+                        // out += tile: the lane's row of 32 sums goes to a 128-byte-swizzled box in shared
+                        // memory, the TMA unit adds the box into out (rows and columns past the matrix are
+                        // clipped; columns past this tile's width are sent as zeros).  Two boxes per warp,
+                        // so filling one overlaps the other's way out.
+                        const int chunk = c0 / 32;
+                        uint8_t* box = (uint8_t*)staging + ((warp - 2) * 2 + (chunk & 1)) * 4096;
+                        if (lane == 0) bw::bulk_wait_group_read<1>();   // the box used two chunks ago has been read
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            uint4 q4;
+                            q4.x = c0 + 4 * j + 0 < BN ? v[4 * j + 0] : 0u; q4.y = c0 + 4 * j + 1 < BN ? v[4 * j + 1] : 0u;
+                            q4.z = c0 + 4 * j + 2 < BN ? v[4 * j + 2] : 0u; q4.w = c0 + 4 * j + 3 < BN ? v[4 * j + 3] : 0u;
+                            *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) = q4;
+                        }
+                        bw::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            bw::tma_reduce_add_2d(&tmC, bw::smem_u32(box), tile_b * BN + c0, tile_a * BM + quarter * 32);
+                            bw::bulk_commit_group();
+                        }
+                    }
                 } else if (ROPE && !part) {
                     if constexpr (CH == 32 && ROPE) {
                         const int token = tile_a * BM + quarter * 32 + lane;
@@ -511,6 +537,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         }
     }
+    if (ep.tma_add && warp >= 2 && lane == 0) bw::bulk_wait_group<0>();   // the boxes have left shared memory and landed
     bw::tc_fence_before();
     __syncthreads();
     if (warp == 1) bw::tmem_dealloc(tmem_base, TMEM_COLS);
@@ -593,7 +620,7 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long K, lon
 }
 
 template <int BN, bool ROPE>
-int launch(const CUtensorMap& a, const CUtensorMap& b, const Epilogue& ep, int kb_total, int kb_per_split,
+int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const Epilogue& ep, int kb_total, int kb_per_split,
            int tiles_a, int tiles_b, int num_work, cudaStream_t s) {
     constexpr int STAGES = stages_for<BN>();
     constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + STAGING_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
@@ -608,9 +635,28 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const Epilogue& ep, int k
     // (decode is bound by bytes in flight, not by CTAs), instead of a second, partly empty round
     const int slots = BN <= 16 ? 2 * NUM_SMS : NUM_SMS;
     const int grid = num_work < slots ? num_work : slots;
-    bw::launch((gemm_tc_kernel<BN, ROPE>), dim3(grid), dim3(THREADS), smem, s, a, b, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work);
+    // With more CTAs than SMs the two-per-SM kernel must start on an empty GPU: the block scheduler
+    // then gives every SM one CTA before any gets a second.  Started beside the draining CTAs of the
+    // kernel before, it has been seen to pair CTAs on some SMs while others idle (48 instead of 38 us
+    // for gate/up at batch 8), so this one launch does not overlap its predecessor.
+    const bool overlap = !(BN <= 16 && grid > NUM_SMS);
+    bw::launch_opt(overlap, (gemm_tc_kernel<BN, ROPE>), dim3(grid), dim3(THREADS), smem, s, a, b, c, ep, kb_total,
+                   kb_per_split, tiles_a, tiles_b, num_work);
     BW_LAUNCH_CHECK();
     return 0;
+}
+
+// float32 [rows, cols] with row stride ld (elements), box = 32 x 32, 128-byte swizzle: the epilogue's
+// way out for out += product
+bool make_out_map(CUtensorMap* m, void* base, long long rows, long long cols, long long ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
@@ -710,16 +756,24 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     ep.swiglu = swiglu; ep.tokens = M; ep.features = N; ep.splits = splits;
     ep.rope_on = rope ? 1 : 0;
     if (rope) ep.rope = *rope; else ep.rope = RopeOut{};
+    // out += product with many tokens and no split: the epilogue hands 32 x 32 boxes to the TMA unit
+    CUtensorMap tc;
+    std::memset(&tc, 0, sizeof(tc));
+    ep.tma_add = 0;
+    if (!tr && accumulate && !bias && splits == 1 && !rope && !swiglu && ((uintptr_t)out & 15) == 0 && ldo % 4 == 0) {
+        if (!make_out_map(&tc, out, M, N, ldo)) return BW_ERR_DRIVER;
+        ep.tma_add = 1;
+    }
     const int num_work = tiles_a * tiles_b * splits;
     int rc;
 #define BW_GEMM_LAUNCH(R) switch (bn) { \
-        case 16: rc = launch<16, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
-        case 32: rc = launch<32, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
-        case 64: rc = launch<64, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
-        case 128: rc = launch<128, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
-        case 224: rc = launch<224, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
-        case 240: rc = launch<240, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
-        case 256: rc = launch<256, R>(ta, tb, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 16: rc = launch<16, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 32: rc = launch<32, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 64: rc = launch<64, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 128: rc = launch<128, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 224: rc = launch<224, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 240: rc = launch<240, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
+        case 256: rc = launch<256, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         default: return BW_ERR_BAD_ARG; }
     if (rope) BW_GEMM_LAUNCH(true) else BW_GEMM_LAUNCH(false)
 #undef BW_GEMM_LAUNCH

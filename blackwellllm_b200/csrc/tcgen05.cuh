@@ -65,6 +65,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
 }
 
 // ---------------------------------------------------------------- TMA
+// Adds a box of shared memory (the layout the tensor map describes) into global memory: the
+// read-modify-write happens in the memory system, no thread waits for it.  Completion is tracked
+// by the thread's bulk async-groups.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t smem_src, int x, int y) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+        :: "l"(map), "r"(smem_src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until at most N of the thread's bulk groups still READ their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory");
+}
+// waits until at most N of the thread's bulk groups are not yet complete
+template <int N> __device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" :: "n"(N) : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
 }
