@@ -62,6 +62,7 @@ struct Epilogue {
     int tokens, features, splits;
     int rope_on;
     int tma_add;          // normal orientation, out += : 32 x 32 boxes go out through the tensor map tmC
+    int stream;           // the k-blocks of all tiles, laid end to end, are cut into one equal range per CTA
     RopeOut rope;
 };
 
@@ -277,7 +278,53 @@ __device__ __forceinline__ void rope_direct(const Epilogue& ep, const uint32_t (
     }
 }
 
-// ROPE: the rotary epilogue (a kernel of its own, so that the plain one carries none of its registers)
+// The work items of one CTA, the same sequence in each of its roles.
+//   classic: item w = blockIdx.x + k * gridDim.x is (tile w % tiles, K split w / tiles);
+//   stream:  the k-blocks of all tiles are laid end to end and the CTA owns the range
+//            [c * total / G, (c + 1) * total / G), cut where it crosses a tile.  Every SM then
+//            streams the same number of bytes however the tiles divide among the SMs.  A tile that
+//            two CTAs share is summed like a K split: part = the CTA's rank among them.  (A range
+//            is at least one tile long, the host sees to that, so no tile has more than two parts.)
+struct Item { int tile, kb0, nkb, part, nparts; };
+struct Items {
+    int kb_total, kb_per_split, tiles, num_work, splits, stream, w;
+    long long lo, hi, total;
+    __device__ Items(const Epilogue& ep, int kb_total_, int kb_per_split_, int tiles_, int num_work_)
+        : kb_total(kb_total_), kb_per_split(kb_per_split_), tiles(tiles_), num_work(num_work_), splits(ep.splits),
+          stream(ep.stream), w(blockIdx.x) {
+        total = (long long)tiles * kb_total;
+        lo = (long long)blockIdx.x * total / gridDim.x;
+        hi = (long long)(blockIdx.x + 1) * total / gridDim.x;
+    }
+    __device__ int owner(long long kb) const {   // the CTA whose range holds k-block kb
+        return (int)(((kb + 1) * gridDim.x + total - 1) / total) - 1;
+    }
+    __device__ bool next(Item& it) {
+        if (!stream) {
+            if (w >= num_work) return false;
+            it.tile = w % tiles;
+            it.part = w / tiles;
+            it.nparts = splits;
+            it.kb0 = it.part * kb_per_split;
+            it.nkb = min(kb_total, it.kb0 + kb_per_split) - it.kb0;
+            w += gridDim.x;
+            return true;
+        }
+        if (lo >= hi) return false;
+        it.tile = (int)(lo / kb_total);
+        it.kb0 = (int)(lo - (long long)it.tile * kb_total);
+        it.nkb = (int)min((long long)(kb_total - it.kb0), hi - lo);
+        lo += it.nkb;
+        if (it.nkb == kb_total) { it.part = 0; it.nparts = 1; }
+        else {
+            const int first = owner((long long)it.tile * kb_total), last = owner((long long)(it.tile + 1) * kb_total - 1);
+            it.part = (int)blockIdx.x - first;
+            it.nparts = last - first + 1;
+        }
+        return true;
+    }
+};
+
 template <int BN, bool ROPE>
 __global__ void __launch_bounds__(THREADS, BN <= 16 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -288,7 +335,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // two accumulators; a tile width that is no power of two takes the next one (TMEM is handed out in
     // powers of two)
     constexpr uint32_t ACC_COLS = BN <= 16 ? 16 : BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
-    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
+    // Narrow tiles (few tokens): the four MMAs of a k-block go to four accumulators of their own, which
+    // the epilogue adds up.  One accumulator would chain them, and an MMA of 16 columns is all latency:
+    // measured 0.35 us per k-block and CTA, the same with the weights in L2 as in DRAM.
+    constexpr uint32_t NSUB = BN <= 64 ? 4 : 1;
+    constexpr uint32_t TMEM_COLS = 2 * NSUB * ACC_COLS < 32 ? 32 : 2 * NSUB * ACC_COLS;
     constexpr uint32_t IDESC = bw::umma_idesc_bf16(BM, BN);
 
     extern __shared__ uint8_t smem_raw[];
@@ -329,24 +380,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // for the first stages are requested before the wait for the earlier kernels, whose
             // results (the activations in B) are loaded after it.
             int ahead = 0;
-            if (ep.transposed && blockIdx.x < num_work) {
-                const int w = blockIdx.x;
-                const int tile = w % tiles, split = w / tiles;
-                const int tile_a = tile % tiles_a;
-                const int kb0 = split * kb_per_split;
-                const int nkb = min(kb_total, kb0 + kb_per_split) - kb0;
-                ahead = min(nkb, STAGES);
-                for (int i = 0; i < ahead; ++i) {
-                    bw::mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
-                    bw::tma_load_2d(bw::smem_u32(smem + i * STAGE_BYTES), &tmA, full0 + 8 * i, (kb0 + i) * BK, tile_a * BM);
+            Items items(ep, kb_total, kb_per_split, tiles, num_work);
+            Item im;
+            if (ep.transposed) {
+                Items peek = items;
+                if (peek.next(im)) {
+                    const int tile_a = im.tile % tiles_a;
+                    ahead = min(im.nkb, STAGES);
+                    for (int i = 0; i < ahead; ++i) {
+                        bw::mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                        bw::tma_load_2d(bw::smem_u32(smem + i * STAGE_BYTES), &tmA, full0 + 8 * i, (im.kb0 + i) * BK, tile_a * BM);
+                    }
                 }
             }
             BW_PDL_WAIT();
-            for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-                const int tile = w % tiles, split = w / tiles;
-                const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;
-                const int kb0 = split * kb_per_split;
-                const int nkb = min(kb_total, kb0 + kb_per_split) - kb0;
+            while (ok && items.next(im)) {
+                const int tile_a = im.tile % tiles_a, tile_b = im.tile / tiles_a;
+                const int kb0 = im.kb0, nkb = im.nkb;
                 for (int i = 0; i < nkb; ++i, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -366,14 +416,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
             uint32_t it = 0, n = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++n) {
-                const int split = w / tiles;
-                const int kb0 = split * kb_per_split;
-                const int nkb = min(kb_total, kb0 + kb_per_split) - kb0;
+            Items items(ep, kb_total, kb_per_split, tiles, num_work);
+            Item im;
+            for (; ok && items.next(im); ++n) {
+                const int nkb = im.nkb;
                 const uint32_t acc = n & 1, accph = (n >> 1) & 1;
                 if (!bw::mbar_wait(tempty0 + 8 * acc, accph ^ 1, &g_status, 4)) break;   // epilogue drained it
                 bw::tc_fence_after();
-                const uint32_t tmem_acc = tmem_base + acc * ACC_COLS;
+                const uint32_t tmem_acc = tmem_base + acc * NSUB * ACC_COLS;
                 for (int i = 0; i < nkb; ++i, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -385,7 +435,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // advance 32 bytes (2 units of 16 B) along K inside the swizzle row
-                        bw::umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, IDESC, (i | k) != 0);
+                        if constexpr (NSUB == 4) bw::umma_bf16(tmem_acc + k * ACC_COLS, da + 2 * k, db + 2 * k, IDESC, i != 0);
+                        else bw::umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, IDESC, (i | k) != 0);
                     }
                     bw::umma_commit(empty0 + 8 * s);   // the stage is free once these MMAs are done
                 }
@@ -401,22 +452,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const size_t plane = (size_t)ep.tokens * ep.features;
         constexpr int CH = BN < 32 ? 16 : 32;
         uint32_t n = 0;
-        for (int w = blockIdx.x; w < num_work; w += gridDim.x, ++n) {
-            const int tile = w % tiles, split = w / tiles;
+        Items items(ep, kb_total, kb_per_split, tiles, num_work);
+        Item im;
+        for (; items.next(im); ++n) {
+            const int tile = im.tile, split = im.part, nparts = im.nparts;
             const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;
             const uint32_t acc = n & 1, accph = (n >> 1) & 1;
             if (!bw::mbar_wait(tfull0 + 8 * acc, accph, &g_status, 3)) break;
             bw::tc_fence_after();
-            const uint32_t lane_addr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t lane_addr = tmem_base + acc * NSUB * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             const int ga = tile_a * BM + quarter * 32 + lane;   // this lane's row of A
-            float* part = ep.partial ? ep.partial + (size_t)split * plane : nullptr;
+            float* part = (ep.partial && nparts > 1) ? ep.partial + (size_t)split * plane : nullptr;
             int rope_kv = -1;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += CH) {
                 uint32_t v[CH];
                 if constexpr (CH == 32) bw::tmem_ld_32x32(lane_addr + c0, v);
                 else bw::tmem_ld_32x16(lane_addr + c0, v);
-                bw::tmem_ld_wait();
+                if constexpr (NSUB == 4) {   // (k-step 0 + 1) + (2 + 3), the same order everywhere
+                    uint32_t v1[CH], v2[CH], v3[CH];
+                    if constexpr (CH == 32) {
+                        bw::tmem_ld_32x32(lane_addr + ACC_COLS + c0, v1); bw::tmem_ld_32x32(lane_addr + 2 * ACC_COLS + c0, v2);
+                        bw::tmem_ld_32x32(lane_addr + 3 * ACC_COLS + c0, v3);
+                    } else {
+                        bw::tmem_ld_32x16(lane_addr + ACC_COLS + c0, v1); bw::tmem_ld_32x16(lane_addr + 2 * ACC_COLS + c0, v2);
+                        bw::tmem_ld_32x16(lane_addr + 3 * ACC_COLS + c0, v3);
+                    }
+                    bw::tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < CH; ++c)
+                        v[c] = __float_as_uint((__uint_as_float(v[c]) + __uint_as_float(v1[c])) +
+                                               (__uint_as_float(v2[c]) + __uint_as_float(v3[c])));
+                } else {
+                    bw::tmem_ld_wait();
+                }
                 if (ep.transposed) {
                     // lanes hold 32 consecutive features, the columns are consecutive tokens: coalesced as it is
                     float vals[CH];
@@ -487,7 +556,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 int last = 0;
                 if (lane == 0) {
                     __threadfence();
-                    last = atomicAdd(&ep.counters[tile * 4 + quarter], 1) == ep.splits - 1;
+                    last = atomicAdd(&ep.counters[tile * 4 + quarter], 1) == nparts - 1;
                 }
                 last = __shfl_sync(0xffffffffu, last, 0);
                 if (last) {
@@ -503,7 +572,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             RopeCtx<8> cx;
                             if constexpr (ROPE) rope_prefetch<8>(ep, cx, token0, nv, ga, ga < a_rows);
                             if (ga < a_rows)
-                                for (int s = 0; s < ep.splits; ++s) {
+                                for (int s = 0; s < nparts; ++s) {
                                     const float* src = ep.partial + (size_t)s * plane + (size_t)token0 * ep.features + ga;
 #pragma unroll
                                     for (int c = 0; c < 8; ++c)
@@ -522,7 +591,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                 for (int c = 0; c < 8; ++c) vals[c] = 0.f;
                                 const int nv = min(8, r_end - token0);
                                 if (feature < b_rows && c0 + lane < BN)
-                                    for (int s = 0; s < ep.splits; ++s) {
+                                    for (int s = 0; s < nparts; ++s) {
                                         const float* src = ep.partial + (size_t)s * plane + (size_t)token0 * ep.features + feature;
 #pragma unroll
                                         for (int c = 0; c < 8; ++c)
@@ -631,17 +700,9 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, con
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
-    // the narrow kernel fits twice on an SM: with more items than SMs all of them stream side by side
-    // (decode is bound by bytes in flight, not by CTAs), instead of a second, partly empty round
-    const int slots = BN <= 16 ? 2 * NUM_SMS : NUM_SMS;
-    const int grid = num_work < slots ? num_work : slots;
-    // With more CTAs than SMs the two-per-SM kernel must start on an empty GPU: the block scheduler
-    // then gives every SM one CTA before any gets a second.  Started beside the draining CTAs of the
-    // kernel before, it has been seen to pair CTAs on some SMs while others idle (48 instead of 38 us
-    // for gate/up at batch 8), so this one launch does not overlap its predecessor.
-    const bool overlap = !(BN <= 16 && grid > NUM_SMS);
-    bw::launch_opt(overlap, (gemm_tc_kernel<BN, ROPE>), dim3(grid), dim3(THREADS), smem, s, a, b, c, ep, kb_total,
-                   kb_per_split, tiles_a, tiles_b, num_work);
+    const int grid = num_work < NUM_SMS ? num_work : NUM_SMS;
+    bw::launch((gemm_tc_kernel<BN, ROPE>), dim3(grid), dim3(THREADS), smem, s, a, b, c, ep, kb_total, kb_per_split,
+               tiles_a, tiles_b, num_work);
     BW_LAUNCH_CHECK();
     return 0;
 }
@@ -750,11 +811,21 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     Epilogue ep;
     // few tokens: the last warp of each tile sums the splits inside the kernel; more: a second kernel
     const bool fused_reduce = M <= FUSED_REDUCE_MAX_TOKENS;
+    // Few tokens and more tiles than SMs, not a multiple of them (gate/up, the head): whole tiles leave
+    // the last round partly empty, and the SMs that still work cannot draw the whole bandwidth (a CTA
+    // of this kernel streams about 40 GB/s).  The k-blocks are dealt out in equal ranges instead:
+    // gate/up at batch 8 takes 43 us instead of 47.5.  (Two CTAs per SM on whole tiles took 38 us when
+    // the block scheduler spread them and 48 us when it paired them on some SMs and left others idle.)
+    const long long n_tiles = (long long)tiles_a * tiles_b;
+    const bool stream_k = tr && fused_reduce && can_split && force_splits <= 0 && splits == 1 && n_tiles > NUM_SMS &&
+                          n_tiles % NUM_SMS != 0 && 2LL * M * N <= workspace_elems && n_tiles * 4 <= n_counters;
+    if (stream_k) splits = 2;   // at most two CTAs share a tile: two planes of partial sums
     ep.out = out; ep.partial = splits > 1 ? workspace : nullptr; ep.counters = fused_reduce ? counters : nullptr;
     ep.bias = bias; ep.ldo = ldo;
     ep.out_type = out_type; ep.bias_type = bias_type; ep.accumulate = accumulate; ep.transposed = tr;
     ep.swiglu = swiglu; ep.tokens = M; ep.features = N; ep.splits = splits;
     ep.rope_on = rope ? 1 : 0;
+    ep.stream = stream_k ? 1 : 0;
     if (rope) ep.rope = *rope; else ep.rope = RopeOut{};
     // out += product with many tokens and no split: the epilogue hands 32 x 32 boxes to the TMA unit
     CUtensorMap tc;
@@ -764,7 +835,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
         if (!make_out_map(&tc, out, M, N, ldo)) return BW_ERR_DRIVER;
         ep.tma_add = 1;
     }
-    const int num_work = tiles_a * tiles_b * splits;
+    const int num_work = stream_k ? NUM_SMS : tiles_a * tiles_b * splits;
     int rc;
 #define BW_GEMM_LAUNCH(R) switch (bn) { \
         case 16: rc = launch<16, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \

@@ -27,7 +27,8 @@ def rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 300, 176), (8, 4096, 4096), (17, 136, 80), (64, 1000, 2048),
                                    (100, 6144, 1024), (256, 384, 96), (257, 512, 256), (300, 260, 200),
                                    (1000, 1111, 520), (2048, 1024, 4096),
-                                   (2048, 4096, 64), (2048, 6144 + 48, 64)])   # tiles 240 wide, the last one of a row cut
+                                   (2048, 4096, 64), (2048, 6144 + 48, 64),     # tiles 240 wide, the last one of a row cut
+                                   (3, 19000, 200), (16, 25000, 136), (1, 128 * 149, 64 * 149)])   # few tokens, more tiles than SMs: k-blocks dealt out in ranges
 @pytest.mark.parametrize("mode", ["plain", "bias_f32out", "accumulate"])
 def test_gemm_tc(ops, M, N, K, mode):
     x = rand(M, K, dtype=torch.bfloat16, seed=1).to(DEV)
