@@ -33,8 +33,11 @@ constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int THREADS = 192;
 constexpr int NUM_SMS = 148;
-constexpr int STAGING_BYTES = 4 * 2 * 4096;   // per epilogue warp: a 32 x 33 float block, or two 32 x 32 boxes for TMA
-constexpr int SMEM_BUDGET = 226 * 1024 - STAGING_BYTES - 2048;
+// Epilogue staging, per epilogue warp a 32 x 33 float block or two 32 x 32 boxes for TMA.  Only the normal
+// orientation uses it, and that has tiles of 128 columns or more: the narrow kernels do without, which
+// keeps two of them on an SM.
+template <int BN> __host__ __device__ constexpr int staging_bytes() { return BN >= 128 ? 4 * 2 * 4096 : 0; }
+constexpr int SMEM_BUDGET = 226 * 1024 - staging_bytes<256>() - 2048;
 constexpr int FUSED_REDUCE_MAX_TOKENS = 16;   // split-K sums inside the kernel up to this many tokens
 constexpr int SWIGLU_BLOCK = 16;   // gate/up features are interleaved in blocks of 16 rows of the weight
 
@@ -345,7 +348,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     float* staging = (float*)(smem + STAGES * STAGE_BYTES);
-    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES + STAGING_BYTES);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES + staging_bytes<BN>());
     // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
 
@@ -692,7 +695,7 @@ template <int BN, bool ROPE>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const Epilogue& ep, int kb_total, int kb_per_split,
            int tiles_a, int tiles_b, int num_work, cudaStream_t s) {
     constexpr int STAGES = stages_for<BN>();
-    constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + STAGING_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+    constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + staging_bytes<BN>() + (2 * STAGES + 4) * 8 + 16 + 1024;
     static_assert(smem <= 227 * 1024, "shared memory budget");
     static bool attr_done = false;
     if (!attr_done) {
@@ -791,6 +794,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     const bool can_split = workspace && counters;
     int tr, bn;
     int splits = bw_gemm_tc_plan(M, N, K, swiglu, can_split ? workspace_elems : 0, can_split ? n_counters : 0, &tr, &bn);
+    if (!tr && bn < 128) return BW_ERR_BAD_ARG;   // only tiles of 128 columns or more have the normal orientation's staging
     const int kb_total = ceil_div(K, BK);
     const long long a_rows = tr ? N : M, b_rows = tr ? M : N;
     const int tiles_a = ceil_div(a_rows, BM), tiles_b = ceil_div(b_rows, bn);
