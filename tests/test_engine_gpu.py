@@ -208,3 +208,37 @@ def test_no_cpu_path_and_bad_tokens(folders):
     with pytest.raises(OutOfPages):
         eng.step([StepEntry("a", [1] * 65, [])])
     assert not eng.has_request("a") and eng.cache.free_pages() == [4]   # nothing was changed
+
+
+def test_command_line_one_shot_and_gen_protocol(folders, capsys, monkeypatch):
+    """The command line on a model folder: `--prompt-ids` prints the greedy continuation, and the
+    GEN line protocol of `--serve` (src/main.cpp's `GEN <bytes> <max_new> <max_in> <temp> <top_p>`
+    followed by the payload) answers with RESULT / TEXT / END; a bad request does not end the loop."""
+    import io
+    from blackwellllm_b200 import cli
+    folder = folders[("llama", "float32")]
+    raw, _, _ = tiny.CONFIGS["llama"]
+    W = load_plain_weights(folder)
+    prompt = [5, 17, 3, 200, 41, 7, 7, 9]
+    want = plain_greedy(raw, W, prompt, 6)
+    rc = cli.main(["-m", folder, "--dtype", "float32", "--ctx", "128", "--temperature", "0", "--max-new-tokens", "6",
+                   "--prompt-ids", ",".join(map(str, prompt)), "--stats"])
+    cap = capsys.readouterr()
+    assert rc == 0 and [int(t) for t in cap.out.strip().splitlines()[0].split()] == want
+    assert "[stats] prompt=8 new=6" in cap.err
+
+    payload = " ".join(map(str, prompt)).encode()
+    script = b"GEN %d 6 0 0.0 1.0 0\n" % len(payload) + payload + b"\nNONSENSE\n" + \
+             b"GEN %d 4 0 0.0 1.0 0\n" % len(payload) + payload + b"\nQUIT\n"
+
+    class Stdin:
+        buffer = io.BytesIO(script)
+    monkeypatch.setattr("sys.stdin", Stdin)
+    rc = cli.main(["-m", folder, "--dtype", "float32", "--ctx", "128", "--serve"])
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert rc == 0
+    results = [ln for ln in lines if ln.startswith("<<<RESULT")]
+    texts = [ln for ln in lines if ln.startswith("TEXT ")]
+    assert len(results) == 2 and "prompt_tokens=8 gen_tokens=6" in results[0] and "gen_tokens=4" in results[1]
+    assert [int(t) for t in texts[0][5:].split()] == want and [int(t) for t in texts[1][5:].split()] == want[:4]
+    assert any(ln.startswith("<<<ERROR") for ln in lines) and lines.count("<<<END>>>") == 2
