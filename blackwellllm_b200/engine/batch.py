@@ -144,12 +144,9 @@ class BatchBuilder:
         """A pinned int32 buffer of at least ``n`` words from the ring (the one :meth:`finish` sends)."""
         return self._pinned(n)
 
-    def finish(self, host: torch.Tensor, T: int, R: int, n_want: int, widths: Dict[int, int], rids: List[object],
-               into: Optional[torch.Tensor] = None) -> StepBatch:
-        """Sends a packed step (the layout of :meth:`build`: token ids, positions, request of token,
-        cu_q, q_start, kv_len, slot, logit rows, one block table per group) to the device in one
-        copy and returns the views of it."""
-        total = 3 * T + (R + 1) + 3 * R + n_want + sum(R * w for w in widths.values())
+    def send(self, host: torch.Tensor, total: int, into: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Copies the first ``total`` words of the pinned buffer to the device (into ``into``, a buffer of
+        exactly that size at a fixed address, or a new tensor) and marks the ring slot busy until then."""
         if into is not None:
             if into.numel() != total:
                 raise ValueError(f"static batch buffer holds {into.numel()} words, this batch needs {total}")
@@ -161,6 +158,15 @@ class BatchBuilder:
             ev = self._events[self._slot] or torch.cuda.Event()
             ev.record()
             self._events[self._slot] = ev
+        return dev
+
+    def finish(self, host: torch.Tensor, T: int, R: int, n_want: int, widths: Dict[int, int], rids: List[object],
+               into: Optional[torch.Tensor] = None) -> StepBatch:
+        """Sends a packed step (the layout of :meth:`build`: token ids, positions, request of token,
+        cu_q, q_start, kv_len, slot, logit rows, one block table per group) to the device in one
+        copy and returns the views of it."""
+        total = 3 * T + (R + 1) + 3 * R + n_want + sum(R * w for w in widths.values())
+        dev = self.send(host, total, into)
         h = host[:total].numpy()
         off = 0
 

@@ -158,7 +158,8 @@ class Engine:
         return self.cache.has(rid)
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: Sequence[StepEntry], min_blocks: int = 0, into=None) -> StepBatch:
+    def prepare(self, entries: Sequence[StepEntry], min_blocks: int = 0, into=None,
+                replay_width: Optional[int] = None) -> Optional[StepBatch]:
         """Checks the entries, reserves pages for all their tokens (all or nothing)
         and uploads the batch.  The checks, the page bookkeeping and the packing of the
         step's buffer are one call into the C++ host runtime."""
@@ -211,6 +212,12 @@ class Engine:
             cache.zero_state(int(new_slots[k]))
             k += 1
         widths = {g: int(meta[4 + g]) for g in range(G)}
+        if replay_width is not None:
+            # a graph replay: the captured kernels read the buffer at its fixed address, no views needed
+            if any(w != replay_width for w in widths.values()):
+                raise EngineError("a request outgrew max_context: its block table no longer fits the graph")
+            self._builder.send(host, int(total), into)
+            return None
         return self._builder.finish(host, T, R, W, widths, [e.rid for e in entries], into)
 
     def _explain(self, entries: Sequence[StepEntry], code: int) -> None:
@@ -266,22 +273,25 @@ class Engine:
             slot = {"buf": torch.zeros(total, dtype=torch.int32, device=self.device), "graph": None,
                     "logits": None, "kernels": 0}
             self._graphs[R] = slot
+        if slot["graph"] is not None:
+            self.prepare(entries, min_blocks=width, into=slot["buf"], replay_width=width)
+            slot["graph"].replay()
+            return slot["logits"]
         batch = self.prepare(entries, min_blocks=width, into=slot["buf"])
         if any(t.shape[1] != width for t in batch.block_tables.values()):
             raise EngineError("a request outgrew max_context: its block table no longer fits the graph")
         batch.static_bound = width * self.cache.page_size
-        if slot["graph"] is None:
-            from ..kernels import ops
-            self.model.forward(batch, self.cache.views)           # warm-up: builds kernels, scratch
-            torch.cuda.synchronize(self.device)
-            batch.extras.clear()   # what depends on this step's values is recomputed inside the graph
-            graph = torch.cuda.CUDAGraph()
-            before = ops.launches
-            with torch.cuda.graph(graph):
-                slot["logits"] = self.model.forward(batch, self.cache.views)
-            slot["kernels"] = ops.launches - before
-            slot["graph"] = graph
-            slot["batch"] = batch   # keeps the per-step tensors that the captured kernels read alive
+        from ..kernels import ops
+        self.model.forward(batch, self.cache.views)           # warm-up: builds kernels, scratch
+        torch.cuda.synchronize(self.device)
+        batch.extras.clear()   # what depends on this step's values is recomputed inside the graph
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launches
+        with torch.cuda.graph(graph):
+            slot["logits"] = self.model.forward(batch, self.cache.views)
+        slot["kernels"] = ops.launches - before
+        slot["graph"] = graph
+        slot["batch"] = batch   # keeps the per-step tensors that the captured kernels read alive
         slot["graph"].replay()
         return slot["logits"]
 
