@@ -155,6 +155,13 @@ __device__ __forceinline__ void rope_finish(const Epilogue& ep, const RopeCtx<G>
     }
 }
 
+// stages of the pair kernel: a stage holds 128 rows of x and BN / 2 rows of w
+template <int BN> __host__ __device__ constexpr int pair_stages() {
+    constexpr int per = A_BYTES + (BN / 2) * BK * 2;
+    constexpr int s = SMEM_BUDGET / per;
+    return s > 8 ? 8 : s;
+}
+
 // The lane holds the finished sums vals[0..N) of ONE feature for N consecutive tokens (token0 + c);
 // the 32 lanes of the warp hold 32 consecutive features.  nvalid (the same in all lanes) of the
 // tokens exist.  When the result is added to `out`, all old values are fetched before the first
@@ -281,6 +288,28 @@ __device__ __forceinline__ void rope_direct(const Epilogue& ep, const uint32_t (
     }
 }
 
+// SwiGLU epilogue in the normal orientation: the thread holds 32 consecutive features f0 .. f0 + 31 of
+// ONE token, f0 a multiple of 32: 16 gate sums, then the 16 up sums of the same output features.
+// It writes silu(gate) * up for those 16 features as 32 contiguous bytes.
+__device__ __forceinline__ void swiglu_direct(const Epilogue& ep, const uint32_t (&v)[32], int token, int f0) {
+    float y[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float g = __uint_as_float(v[i]), u = __uint_as_float(v[16 + i]);
+        y[i] = __fdividef(g, 1.f + __expf(-g)) * u;
+    }
+    bf16* dst = (bf16*)ep.out + (size_t)token * ep.ldo + (f0 / (2 * SWIGLU_BLOCK)) * SWIGLU_BLOCK;
+    if ((ep.ldo & 7) == 0 && ((uintptr_t)ep.out & 15) == 0) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(bw::pack_bf16x2(y[0], y[1]), bw::pack_bf16x2(y[2], y[3]),
+                                                    bw::pack_bf16x2(y[4], y[5]), bw::pack_bf16x2(y[6], y[7]));
+        *reinterpret_cast<uint4*>(dst + 8) = make_uint4(bw::pack_bf16x2(y[8], y[9]), bw::pack_bf16x2(y[10], y[11]),
+                                                        bw::pack_bf16x2(y[12], y[13]), bw::pack_bf16x2(y[14], y[15]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[i] = __float2bfloat16_rn(y[i]);
+    }
+}
+
 // The work items of one CTA, the same sequence in each of its roles.
 //   classic: item w = blockIdx.x + k * gridDim.x is (tile w % tiles, K split w / tiles);
 //   stream:  the k-blocks of all tiles are laid end to end and the CTA owns the range
@@ -290,11 +319,13 @@ __device__ __forceinline__ void rope_direct(const Epilogue& ep, const uint32_t (
 //            is at least one tile long, the host sees to that, so no tile has more than two parts.)
 struct Item { int tile, kb0, nkb, part, nparts; };
 struct Items {
-    int kb_total, kb_per_split, tiles, num_work, splits, stream, w;
+    int kb_total, kb_per_split, tiles, num_work, splits, stream, w, stride;
     long long lo, hi, total;
-    __device__ Items(const Epilogue& ep, int kb_total_, int kb_per_split_, int tiles_, int num_work_)
+    // first, stride: the CTA's place among the CTAs (or CTA pairs) that share the items; default: the grid
+    __device__ Items(const Epilogue& ep, int kb_total_, int kb_per_split_, int tiles_, int num_work_, int first = -1,
+                     int stride_ = 0)
         : kb_total(kb_total_), kb_per_split(kb_per_split_), tiles(tiles_), num_work(num_work_), splits(ep.splits),
-          stream(ep.stream), w(blockIdx.x) {
+          stream(ep.stream), w(first < 0 ? (int)blockIdx.x : first), stride(stride_ > 0 ? stride_ : (int)gridDim.x) {
         total = (long long)tiles * kb_total;
         lo = (long long)blockIdx.x * total / gridDim.x;
         hi = (long long)(blockIdx.x + 1) * total / gridDim.x;
@@ -310,7 +341,7 @@ struct Items {
             it.nparts = splits;
             it.kb0 = it.part * kb_per_split;
             it.nkb = min(kb_total, it.kb0 + kb_per_split) - it.kb0;
-            w += gridDim.x;
+            w += stride;
             return true;
         }
         if (lo >= hi) return false;
@@ -520,6 +551,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             bw::bulk_commit_group();
                         }
                     }
+                } else if (ep.swiglu && !part) {
+                    if constexpr (CH == 32 && !ROPE) {
+                        const int token = tile_a * BM + quarter * 32 + lane;
+                        if (token < a_rows && tile_b * BN + c0 < b_rows) swiglu_direct(ep, v, token, tile_b * BN + c0);
+                    }
                 } else if (ROPE && !part) {
                     if constexpr (CH == 32 && ROPE) {
                         const int token = tile_a * BM + quarter * 32 + lane;
@@ -615,6 +651,179 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 1) bw::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// The same product for many tokens on CTA PAIRS (cta_group::2): a cluster of two CTAs takes a tile of
+// 256 tokens x BN features.  Each CTA loads its 128 rows of x and HALF of the BN weight rows (so a
+// k-block costs it 16 + BN / 8 KB instead of 16 + BN / 4: less traffic from L2 per flop, and room
+// for more stages), the leader CTA's MMA thread issues one M = 256 instruction that reads both
+// CTAs' shared memory and writes each CTA's 128 accumulator rows into its own TMEM, and each CTA
+// runs the epilogue of its own rows.  Normal orientation only, no K split.
+//   full[s]   on the leader: both CTAs' loads of stage s count their bytes there;
+//   empty[s]  on each CTA: the leader's commit reaches both;
+//   tfull[a]  on each CTA (the leader's commit reaches both); tempty[a] on the leader: the four
+//             epilogue warps of BOTH CTAs arrive there.
+template <int BN, bool ROPE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, Epilogue ep, int kb_total, int tiles_a, int tiles_b, int num_work) {
+    constexpr int BH = BN / 2;                       // weight rows this CTA loads
+    constexpr int B_BYTES = BH * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int STAGES = pair_stages<BN>();
+    constexpr uint32_t TMEM_COLS = 512;              // two accumulators of up to 256 columns
+    constexpr uint32_t IDESC = bw::umma_idesc_bf16(2 * BM, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    float* staging = (float*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES + staging_bytes<BN>());
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+
+    BW_PDL_TRIGGER();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = bw::cluster_ctarank();     // 0: the leader
+    const uint32_t full0 = bw::smem_u32(bars), empty0 = bw::smem_u32(bars + STAGES);
+    const uint32_t tfull0 = bw::smem_u32(bars + 2 * STAGES), tempty0 = bw::smem_u32(bars + 2 * STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { bw::mbar_init(full0 + 8 * s, 1); bw::mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { bw::mbar_init(tfull0 + 8 * a, 1); bw::mbar_init(tempty0 + 8 * a, 8); }
+        bw::fence_barrier_init();
+        bw::tma_prefetch_desc(&tmA);
+        bw::tma_prefetch_desc(&tmB);
+        tmem_slot[1] = (uint32_t)g_status;
+    }
+    if (warp == 1) bw::tmem_alloc_pair(bw::smem_u32(tmem_slot), TMEM_COLS);
+    bw::tc_fence_before();
+    __syncthreads();
+    bw::cluster_sync();                              // both CTAs' barriers exist before anyone arrives remotely
+    bw::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const bool dead = tmem_slot[1] != 0;
+    const int tiles = tiles_a * tiles_b;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    if (dead) {
+        // fall through to the exit
+    } else if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            Items items(ep, kb_total, kb_total, tiles, num_work, pair, n_pairs);
+            Item im;
+            BW_PDL_WAIT();
+            while (ok && items.next(im)) {
+                const int tile_a = im.tile % tiles_a, tile_b = im.tile / tiles_a;
+                for (int i = 0; i < im.nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!bw::mbar_wait(empty0 + 8 * s, ph ^ 1, &g_status, 31)) { ok = false; break; }
+                    const uint32_t a_dst = bw::smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t lead_full = bw::pair_leader_addr(full0 + 8 * s);
+                    if (rank == 0) bw::mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);   // the bytes of both CTAs
+                    bw::tma_load_2d_pair(a_dst, &tmA, lead_full, i * BK, tile_a * 2 * BM + (int)rank * BM);
+                    bw::tma_load_2d_pair(a_dst + A_BYTES, &tmB, lead_full, i * BK, tile_b * BN + (int)rank * BH);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            uint32_t it = 0, n = 0;
+            bool ok = true;
+            Items items(ep, kb_total, kb_total, tiles, num_work, pair, n_pairs);
+            Item im;
+            for (; ok && items.next(im); ++n) {
+                const uint32_t acc = n & 1, accph = (n >> 1) & 1;
+                if (!bw::mbar_wait_cluster(tempty0 + 8 * acc, accph ^ 1, &g_status, 34)) break;   // both epilogues drained it
+                bw::tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + acc * 256;
+                for (int i = 0; i < im.nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!bw::mbar_wait_cluster(full0 + 8 * s, ph, &g_status, 32)) { ok = false; break; }
+                    bw::tc_fence_after();
+                    const uint32_t a_addr = bw::smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t da = bw::umma_smem_desc_sw128(a_addr);
+                    const uint64_t db = bw::umma_smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        bw::umma_bf16_pair(tmem_acc, da + 2 * k, db + 2 * k, IDESC, (i | k) != 0);
+                    bw::umma_commit_pair(empty0 + 8 * s, 3);   // the stage is free in both CTAs
+                }
+                bw::umma_commit_pair(tfull0 + 8 * acc, 3);     // both CTAs' rows of the accumulator are complete
+            }
+        }
+    } else {
+        BW_PDL_WAIT();
+        const int quarter = warp & 3;
+        float* stage = staging + (warp - 2) * (32 * 33);
+        const int a_rows = ep.tokens, b_rows = ep.features;
+        uint32_t n = 0;
+        Items items(ep, kb_total, kb_total, tiles, num_work, pair, n_pairs);
+        Item im;
+        for (; items.next(im); ++n) {
+            const int tile_a = im.tile % tiles_a, tile_b = im.tile / tiles_a;
+            const uint32_t acc = n & 1, accph = (n >> 1) & 1;
+            if (!bw::mbar_wait_cluster(tfull0 + 8 * acc, accph, &g_status, 33)) break;
+            bw::tc_fence_after();
+            const uint32_t lane_addr = tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16);
+            const int row0 = tile_a * 2 * BM + (int)rank * BM + quarter * 32;   // first token of this warp
+            int rope_kv = -1;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                bw::tmem_ld_32x32(lane_addr + c0, v);
+                bw::tmem_ld_wait();
+                if (ep.tma_add) {
+                    if constexpr (!ROPE) {
+                        const int chunk = c0 / 32;
+                        uint8_t* box = (uint8_t*)staging + ((warp - 2) * 2 + (chunk & 1)) * 4096;
+                        if (lane == 0) bw::bulk_wait_group_read<1>();
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                                make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        bw::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            bw::tma_reduce_add_2d(&tmC, bw::smem_u32(box), tile_b * BN + c0, row0);
+                            bw::bulk_commit_group();
+                        }
+                    }
+                } else if (ROPE) {
+                    if constexpr (ROPE) {
+                        const int token = row0 + lane;
+                        if (c0 == 0) rope_kv = (token < a_rows && ep.rope.kv_slot) ? __ldg(ep.rope.kv_slot + token) : -1;
+                        if (token < a_rows && tile_b * BN + c0 < b_rows)
+                            rope_direct(ep, v, token, tile_b * BN + c0, min(32, BN - c0), rope_kv);
+                    }
+                } else if (ep.swiglu) {
+                    if (row0 + lane < a_rows && tile_b * BN + c0 < b_rows) swiglu_direct(ep, v, row0 + lane, tile_b * BN + c0);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) stage[lane * 33 + c] = __uint_as_float(v[c]);
+                    __syncwarp();
+                    const int feature = tile_b * BN + c0 + lane;
+                    float vals[32];
+#pragma unroll
+                    for (int r = 0; r < 32; ++r) vals[r] = stage[r * 33 + lane];
+                    __syncwarp();
+                    if (tile_b * BN + c0 < b_rows)
+                        emit<32, false>(ep, nullptr, vals, row0, min(32, a_rows - row0), feature, feature < b_rows);
+                }
+            }
+            bw::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) bw::mbar_arrive_cluster(bw::pair_leader_addr(tempty0 + 8 * acc));
+        }
+        if (ep.tma_add && lane == 0) bw::bulk_wait_group<0>();
+    }
+    bw::tc_fence_before();
+    __syncthreads();
+    bw::cluster_sync();   // nobody leaves while the other CTA may still arrive on its barriers or read its tiles
+    if (warp == 1) bw::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
 // Split-K with many tokens: out = epilogue(sum over splits of partial), one thread per (token,
 // feature), splits added in order.  SwiGLU: one thread per (token, output feature) reads its gate
 // and up sums from the interleaved layout.
@@ -706,6 +915,26 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, con
     const int grid = num_work < NUM_SMS ? num_work : NUM_SMS;
     bw::launch((gemm_tc_kernel<BN, ROPE>), dim3(grid), dim3(THREADS), smem, s, a, b, c, ep, kb_total, kb_per_split,
                tiles_a, tiles_b, num_work);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+template <int BN, bool ROPE>
+int launch_pair(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const Epilogue& ep, int kb_total,
+                int tiles_a, int tiles_b, cudaStream_t s) {
+    constexpr int STAGES = pair_stages<BN>();
+    constexpr int smem = STAGES * (A_BYTES + (BN / 2) * BK * 2) + staging_bytes<BN>() + (2 * STAGES + 4) * 8 + 16 + 1024;
+    static_assert(smem <= 227 * 1024, "shared memory budget");
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    const int num_work = tiles_a * tiles_b;
+    const int pairs = num_work < NUM_SMS / 2 ? num_work : NUM_SMS / 2;
+    bw::launch_pairs((gemm_pair_kernel<BN, ROPE>), dim3(2 * pairs), dim3(THREADS), smem, s, a, b, c, ep, kb_total, tiles_a,
+                     tiles_b, num_work);
     BW_LAUNCH_CHECK();
     return 0;
 }
@@ -850,6 +1079,19 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
         case 240: rc = launch<240, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         case 256: rc = launch<256, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         default: return BW_ERR_BAD_ARG; }
+    // many tokens, no K split: CTA pairs on tiles of 256 tokens (BW_GEMM_PAIR=0 keeps single CTAs)
+    static const bool pairs_on = []{ const char* e = getenv("BW_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    if (pairs_on && !tr && splits == 1 && M >= 512 && (bn == 256 || bn == 224 || bn == 240)) {
+        const int pbn = bn == 240 ? 256 : bn;      // pairs come 256 or 224 columns wide
+        CUtensorMap tb2;
+        if (!make_map(&tb2, b_ptr, b_rows, K, b_ld, pbn / 2)) return BW_ERR_DRIVER;
+        const int pa = ceil_div(M, 2 * BM), pb = ceil_div(N, pbn);
+        if (pbn == 256) rc = rope ? launch_pair<256, true>(ta, tb2, tc, ep, kb_total, pa, pb, s)
+                                  : launch_pair<256, false>(ta, tb2, tc, ep, kb_total, pa, pb, s);
+        else rc = rope ? launch_pair<224, true>(ta, tb2, tc, ep, kb_total, pa, pb, s)
+                       : launch_pair<224, false>(ta, tb2, tc, ep, kb_total, pa, pb, s);
+        return rc;
+    }
     if (rope) BW_GEMM_LAUNCH(true) else BW_GEMM_LAUNCH(false)
 #undef BW_GEMM_LAUNCH
     if (rc) return rc;
