@@ -780,9 +780,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         if (lane == 0) bw::bulk_wait_group_read<1>();
                         __syncwarp();
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
+                        for (int j = 0; j < 8; ++j) {   // columns past this tile's width go out as zeros
+                            const bool in = c0 + 4 * j < BN;   // BN is a multiple of 16: whole groups of four
                             *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                                make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                                in ? make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]) : make_uint4(0u, 0u, 0u, 0u);
+                        }
                         bw::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
@@ -809,7 +811,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     for (int r = 0; r < 32; ++r) vals[r] = stage[r * 33 + lane];
                     __syncwarp();
                     if (tile_b * BN + c0 < b_rows)
-                        emit<32, false>(ep, nullptr, vals, row0, min(32, a_rows - row0), feature, feature < b_rows);
+                        emit<32, false>(ep, nullptr, vals, row0, min(32, a_rows - row0), feature,
+                                        feature < b_rows && c0 + lane < BN);
                 }
             }
             bw::tc_fence_before();
@@ -1081,16 +1084,23 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
         default: return BW_ERR_BAD_ARG; }
     // many tokens, no K split: CTA pairs on tiles of 256 tokens (BW_GEMM_PAIR=0 keeps single CTAs)
     static const bool pairs_on = []{ const char* e = getenv("BW_GEMM_PAIR"); return !(e && e[0] == '0'); }();
-    if (pairs_on && !tr && splits == 1 && M >= 512 && (bn == 256 || bn == 224 || bn == 240)) {
-        const int pbn = bn == 240 ? 256 : bn;      // pairs come 256 or 224 columns wide
+    if (pairs_on && !tr && splits == 1 && M >= 512) {
+        // the width whose rounds over the 74 pairs cost least
+        const int pa = ceil_div(M, 2 * BM);
+        const int widths[2] = {256, 224};   // (240 works but was measured no faster than 256)
+        int pbn = 256; double best_cost = 0.0;
+        for (int i = 0; i < 2; ++i) {
+            const long long t = (long long)pa * ceil_div(N, widths[i]);
+            const double cost = (double)ceil_div(t, NUM_SMS / 2) * widths[i];
+            if (i == 0 || cost < best_cost * 0.995) { best_cost = cost; pbn = widths[i]; }
+        }
         CUtensorMap tb2;
         if (!make_map(&tb2, b_ptr, b_rows, K, b_ld, pbn / 2)) return BW_ERR_DRIVER;
-        const int pa = ceil_div(M, 2 * BM), pb = ceil_div(N, pbn);
-        if (pbn == 256) rc = rope ? launch_pair<256, true>(ta, tb2, tc, ep, kb_total, pa, pb, s)
-                                  : launch_pair<256, false>(ta, tb2, tc, ep, kb_total, pa, pb, s);
-        else rc = rope ? launch_pair<224, true>(ta, tb2, tc, ep, kb_total, pa, pb, s)
-                       : launch_pair<224, false>(ta, tb2, tc, ep, kb_total, pa, pb, s);
-        return rc;
+        const int pb = ceil_div(N, pbn);
+#define BW_PAIR_LAUNCH(W) (rope ? launch_pair<W, true>(ta, tb2, tc, ep, kb_total, pa, pb, s) \
+                                : launch_pair<W, false>(ta, tb2, tc, ep, kb_total, pa, pb, s))
+        return pbn == 256 ? BW_PAIR_LAUNCH(256) : BW_PAIR_LAUNCH(224);
+#undef BW_PAIR_LAUNCH
     }
     if (rope) BW_GEMM_LAUNCH(true) else BW_GEMM_LAUNCH(false)
 #undef BW_GEMM_LAUNCH
