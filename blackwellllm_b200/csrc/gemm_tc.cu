@@ -17,6 +17,10 @@
 // (the residual stream), or SwiGLU over interleaved gate/up features -> bfloat16, or rotary
 // position encoding of a fused q/k/v projection with the keys and values written to their pages.
 //
+// With 512 tokens or more and no K split the product runs on CTA PAIRS instead
+// (gemm_pair_kernel, cta_group::2): two CTAs of a cluster share a tile of 256 tokens, each loads
+// half of the weight tile, and the leader's MMAs read both CTAs' shared memory.
+//
 // Roles (192 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps
 // 2..5 epilogue (TMEM lane quarter = warp % 4).  Every wait is bounded; a timeout sets
 // the status word and all roles fall through to the common exit where TMEM is freed.

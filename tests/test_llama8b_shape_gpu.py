@@ -102,3 +102,36 @@ def test_rope_scaling_at_far_positions():
     for t, p in enumerate(positions):
         got = kp[p // 16, :, p % 16].double().cpu()
         assert float((got - k_ref[t]).abs().max()) < 1e-5
+
+
+MID = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 320, "num_attention_heads": 5,
+       "num_key_value_heads": 1, "head_dim": 64, "intermediate_size": 736, "num_hidden_layers": 2, "vocab_size": 1000,
+       "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_more_than_512_tokens(dtype):
+    """Steps wide enough for the products to run on CTA pairs (rotary and cache append, SwiGLU and
+    the residual sum in their epilogues; q/k/v bias): a prompt of 700 tokens whole, then in portions of
+    530 + 170 beside another request, against the plain implementation at every position."""
+    from blackwellllm_b200 import Engine, StepEntry
+    from blackwellllm_b200.weights.random_init import model_param_specs, random_tensors
+    W = random_tensors(model_param_specs(MID), seed=21, std=0.05, bias_std=0.3,
+                       dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+    ids = tiny.prompt(700, MID["vocab_size"], 31)
+    other = tiny.prompt(60, MID["vocab_size"], 32)
+    with torch.no_grad():
+        ref = plain_logits(MID, W, ids, dtype=torch.float64)
+        ref_o = plain_logits(MID, W, other, dtype=torch.float64)
+    eng = Engine.from_tensors(MID, W, dtype=dtype, page_size=16, max_tokens=1600, max_requests=3, max_batch_tokens=1024)
+    tol, scale = tiny.TOL[dtype], float(ref.abs().max())
+    out = eng.step([StepEntry("w", ids, list(range(700)))]).double().cpu()
+    assert float((out - ref).abs().max()) / scale <= tol
+    out = eng.step([StepEntry("p", ids[:530], list(range(530))), StepEntry("o", other[:30], list(range(30)))]).double().cpu()
+    assert float((out[:530] - ref[:530]).abs().max()) / scale <= tol
+    assert float((out[530:] - ref_o[:30]).abs().max()) / scale <= tol
+    out = eng.step([StepEntry("o", other[30:], list(range(30))), StepEntry("p", ids[530:], list(range(170)))]).double().cpu()
+    assert float((out[:30] - ref_o[30:]).abs().max()) / scale <= tol
+    assert float((out[30:] - ref[530:]).abs().max()) / scale <= tol
+    from blackwellllm_b200.kernels import ops
+    assert ops.gemm_tc_status() == 0 and ops.attention_tc_status() == 0
