@@ -158,7 +158,19 @@ class Scheduler:
         self.waiting.appendleft(req)
 
     def plan(self) -> StepPlan:
+        """The next step.  If nothing can run although requests are running (every one of them is
+        in its prompt and needs a page, and none is free), the most recently admitted one is
+        preempted and the step is planned again: the oldest request always gets to finish."""
         preempted: List[Request] = []
+        while True:
+            entries = self._plan_once(preempted)
+            if entries or not self.running:
+                return StepPlan(entries, preempted)
+            victim = max(self.running, key=lambda r: r.admitted_at)
+            self._preempt(victim)
+            preempted.append(victim)
+
+    def _plan_once(self, preempted: List[Request]) -> List[PlannedEntry]:
         n_groups = len(self.cache.groups)
         # 1. decodes, preempting the most recent admissions until their pages exist
         while True:
@@ -210,7 +222,7 @@ class Scheduler:
             self.running.append(r)
             entries.append(PlannedEntry(r, r.tokens[:n], n == r.remaining))
             budget -= n
-        return StepPlan(entries, preempted)
+        return entries
 
     # ------------------------------------------------------------------ after the step
     def commit(self, plan: StepPlan, sampled: Dict[int, int]) -> List[Request]:

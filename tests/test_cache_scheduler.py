@@ -3,7 +3,7 @@ manager runs without tensors, and a fake step stands in for the model)."""
 import random
 
 import pytest
-from hypothesis import given, settings, strategies as st
+from hypothesis import example, given, settings, strategies as st
 
 from blackwellllm_b200.cache.manager import CacheManager
 from blackwellllm_b200.cache.pages import OutOfPages
@@ -276,6 +276,7 @@ def test_admission_waits_for_slots_and_pages():
 
 @settings(max_examples=25, deadline=None)
 @given(st.integers(0, 10_000))
+@example(512)   # every running request in its prompt, each needing a page, none free: one must yield
 def test_scheduler_random_loads_always_finish_right(seed):
     rng = random.Random(seed)
     cm = CacheManager([FULL, WIN], page_size=8, num_pages=[rng.randint(8, 20)] * 2, max_requests=rng.randint(1, 4))
