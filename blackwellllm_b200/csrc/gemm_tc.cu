@@ -73,19 +73,6 @@ struct Epilogue {
     RopeOut rope;
 };
 
-// RMSNorm folded into the product's token operand (few tokens, transposed orientation): the kernel
-// reads the float32 residual rows itself, normalises them (y = x * rsqrt(mean(x^2) + eps) * gain,
-// 32-bit arithmetic, rounded to bfloat16 as the norm kernel would) and keeps them in shared memory
-// for all its k-blocks, so no norm kernel and no launch boundary stand before the product.
-struct NormIn {
-    const float* x;       // [tokens, K] float32, row stride ldx
-    const void* gain;     // [K]
-    long long ldx;
-    int gain_type;
-    float eps;
-};
-constexpr int NORM_KB_MAX = 64;   // k-blocks of the resident operand: K <= 4096
-
 __device__ __forceinline__ float bias_at(const Epilogue& ep, int feature) {
     if (!ep.bias) return 0.f;
     return ep.bias_type == BW_F32 ? ((const float*)ep.bias)[feature] : __bfloat162float(((const bf16*)ep.bias)[feature]);
@@ -376,16 +363,13 @@ struct Items {
     }
 };
 
-// ROPE: the rotary epilogue (a kernel of its own, so that the plain one carries none of its registers).
-// NORMB: the token operand is made in the kernel from the residual rows (see NormIn), not loaded.
-template <int BN, bool ROPE, bool NORMB = false>
-__global__ void __launch_bounds__(THREADS, (BN <= 16 && !NORMB) ? 2 : 1)
+template <int BN, bool ROPE>
+__global__ void __launch_bounds__(THREADS, BN <= 16 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, Epilogue ep, NormIn nin, int kb_total, int kb_per_split, int tiles_a, int tiles_b, int num_work) {
-    constexpr int STAGES = NORMB ? 6 : stages_for<BN>();
+               const __grid_constant__ CUtensorMap tmC, Epilogue ep, int kb_total, int kb_per_split, int tiles_a, int tiles_b, int num_work) {
+    constexpr int STAGES = stages_for<BN>();
     constexpr int B_BYTES = BN * BK * 2;
-    constexpr int STAGE_BYTES = NORMB ? A_BYTES : A_BYTES + B_BYTES;
-    constexpr int BRES_BYTES = NORMB ? NORM_KB_MAX * B_BYTES : 0;   // the resident token operand
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     // two accumulators; a tile width that is no power of two takes the next one (TMEM is handed out in
     // powers of two)
     constexpr uint32_t ACC_COLS = BN <= 16 ? 16 : BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
@@ -399,24 +383,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     float* staging = (float*)(smem + STAGES * STAGE_BYTES);
-    uint8_t* bres = smem + STAGES * STAGE_BYTES + staging_bytes<BN>();
-    uint64_t* bars = (uint64_t*)(bres + BRES_BYTES);
-    // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], b_ready
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 5);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES + staging_bytes<BN>());
+    // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
 
     BW_PDL_TRIGGER();   // the next kernel in the stream may start launching
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = bw::smem_u32(bars), empty0 = bw::smem_u32(bars + STAGES);
     const uint32_t tfull0 = bw::smem_u32(bars + 2 * STAGES), tempty0 = bw::smem_u32(bars + 2 * STAGES + 2);
-    const uint32_t bready = bw::smem_u32(bars + 2 * STAGES + 4);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { bw::mbar_init(full0 + 8 * s, 1); bw::mbar_init(empty0 + 8 * s, 1); }
         for (int a = 0; a < 2; ++a) { bw::mbar_init(tfull0 + 8 * a, 1); bw::mbar_init(tempty0 + 8 * a, 4); }
-        bw::mbar_init(bready, 4);
         bw::fence_barrier_init();
         bw::tma_prefetch_desc(&tmA);
-        if constexpr (!NORMB) bw::tma_prefetch_desc(&tmB);
+        bw::tma_prefetch_desc(&tmB);
         tmem_slot[1] = (uint32_t)g_status;   // an earlier timeout: later launches do no work
     }
     if (warp == 1) bw::tmem_alloc(bw::smem_u32(tmem_slot), TMEM_COLS);
@@ -459,13 +440,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t ph = (it / STAGES) & 1;
                     const uint32_t a_dst = bw::smem_u32(smem + s * STAGE_BYTES);
                     if ((int)it < ahead) {   // A of this stage is already on its way
-                        if constexpr (!NORMB) bw::tma_load_2d(a_dst + A_BYTES, &tmB, full0 + 8 * s, (kb0 + i) * BK, tile_b * BN);
+                        bw::tma_load_2d(a_dst + A_BYTES, &tmB, full0 + 8 * s, (kb0 + i) * BK, tile_b * BN);
                         continue;
                     }
                     if (!bw::mbar_wait(empty0 + 8 * s, ph ^ 1, &g_status, 1)) { ok = false; break; }
                     bw::mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                     bw::tma_load_2d(a_dst, &tmA, full0 + 8 * s, (kb0 + i) * BK, tile_a * BM);
-                    if constexpr (!NORMB) bw::tma_load_2d(a_dst + A_BYTES, &tmB, full0 + 8 * s, (kb0 + i) * BK, tile_b * BN);
+                    bw::tma_load_2d(a_dst + A_BYTES, &tmB, full0 + 8 * s, (kb0 + i) * BK, tile_b * BN);
                 }
             }
         }
@@ -475,7 +456,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool ok = true;
             Items items(ep, kb_total, kb_per_split, tiles, num_work);
             Item im;
-            if constexpr (NORMB) ok = bw::mbar_wait(bready, 0, &g_status, 5);   // the token operand is in shared memory
             for (; ok && items.next(im); ++n) {
                 const int nkb = im.nkb;
                 const uint32_t acc = n & 1, accph = (n >> 1) & 1;
@@ -489,7 +469,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     bw::tc_fence_after();
                     const uint32_t a_addr = bw::smem_u32(smem + s * STAGE_BYTES);
                     const uint64_t da = bw::umma_smem_desc_sw128(a_addr);
-                    const uint64_t db = bw::umma_smem_desc_sw128(NORMB ? bw::smem_u32(bres) + (im.kb0 + i) * B_BYTES : a_addr + A_BYTES);
+                    const uint64_t db = bw::umma_smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // advance 32 bytes (2 units of 16 B) along K inside the swizzle row
@@ -504,47 +484,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else {
         BW_PDL_WAIT();   // the outputs, the split-K scratch and its counters belong to earlier kernels until here
         const int quarter = warp & 3;              // TMEM lanes 32 * quarter .. + 31
-        if constexpr (NORMB) {
-            // The token operand, made here: warp q normalises tokens q, q + 4, ... (a lane takes every
-            // 32nd group of four channels: sum of squares, warp sum, then the scaled row as bfloat16 into
-            // the 128-byte-swizzled k-block tiles the MMA reads); rows of tokens that do not exist are
-            // zero.  The weight tiles stream in meanwhile.
-            const int K = kb_total * BK;           // the host sends only K that are multiples of 64
-            for (int t = warp - 2; t < BN; t += 4) {
-                uint8_t* rowp = bres + (t >> 3) * 1024 + (t & 7) * 128;
-                if (t >= ep.tokens) {
-                    for (int c = lane * 4; c < K; c += 128)
-                        *reinterpret_cast<uint2*>(rowp + (c >> 6) * B_BYTES + ((((c & 63) >> 3) ^ (t & 7)) << 4) + ((c & 4) << 1)) = make_uint2(0u, 0u);
-                    continue;
-                }
-                const float* xr = nin.x + (size_t)t * nin.ldx;
-                float ss = 0.f;
-                for (int c = lane * 4; c < K; c += 128) {
-                    const float4 v4 = *reinterpret_cast<const float4*>(xr + c);
-                    ss = fmaf(v4.x, v4.x, ss); ss = fmaf(v4.y, v4.y, ss); ss = fmaf(v4.z, v4.z, ss); ss = fmaf(v4.w, v4.w, ss);
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                const float r = rsqrtf(ss / (float)K + nin.eps);
-                for (int c = lane * 4; c < K; c += 128) {
-                    const float4 v4 = *reinterpret_cast<const float4*>(xr + c);
-                    float4 g4;
-                    if (nin.gain_type == BW_F32) g4 = *reinterpret_cast<const float4*>((const float*)nin.gain + c);
-                    else {
-                        const uint2 raw = *reinterpret_cast<const uint2*>((const bf16*)nin.gain + c);
-                        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-                        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-                        g4 = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
-                    }
-                    const uint2 packed = make_uint2(bw::pack_bf16x2(v4.x * r * g4.x, v4.y * r * g4.y),
-                                                    bw::pack_bf16x2(v4.z * r * g4.z, v4.w * r * g4.w));
-                    *reinterpret_cast<uint2*>(rowp + (c >> 6) * B_BYTES + ((((c & 63) >> 3) ^ (t & 7)) << 4) + ((c & 4) << 1)) = packed;
-                }
-            }
-            bw::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) bw::mbar_arrive(bready);
-        }
         float* stage = staging + (warp - 2) * (32 * 33);
         const int a_rows = ep.transposed ? ep.features : ep.tokens;
         const int b_rows = ep.transposed ? ep.tokens : ep.features;
@@ -968,21 +907,20 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long K, lon
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, bool ROPE, bool NORMB = false>
+template <int BN, bool ROPE>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const Epilogue& ep, int kb_total, int kb_per_split,
-           int tiles_a, int tiles_b, int num_work, cudaStream_t s, const NormIn& nin = NormIn{}) {
-    constexpr int STAGES = NORMB ? 6 : stages_for<BN>();
-    constexpr int smem = NORMB ? STAGES * A_BYTES + NORM_KB_MAX * BN * BK * 2 + (2 * STAGES + 5) * 8 + 16 + 1024
-                               : STAGES * (A_BYTES + BN * BK * 2) + staging_bytes<BN>() + (2 * STAGES + 5) * 8 + 16 + 1024;
+           int tiles_a, int tiles_b, int num_work, cudaStream_t s) {
+    constexpr int STAGES = stages_for<BN>();
+    constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + staging_bytes<BN>() + (2 * STAGES + 4) * 8 + 16 + 1024;
     static_assert(smem <= 227 * 1024, "shared memory budget");
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, ROPE, NORMB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
     const int grid = num_work < NUM_SMS ? num_work : NUM_SMS;
-    bw::launch((gemm_tc_kernel<BN, ROPE, NORMB>), dim3(grid), dim3(THREADS), smem, s, a, b, c, ep, nin, kb_total, kb_per_split,
+    bw::launch((gemm_tc_kernel<BN, ROPE>), dim3(grid), dim3(THREADS), smem, s, a, b, c, ep, kb_total, kb_per_split,
                tiles_a, tiles_b, num_work);
     BW_LAUNCH_CHECK();
     return 0;
@@ -1080,13 +1018,8 @@ BW_EXPORT int bw_gemm_tc_plan(int M, int N, int K, int swiglu, long long workspa
 static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_type, void* out, int out_type,
                        int M, int N, int K, long long ldx, long long ldo, int accumulate, int swiglu,
                        float* workspace, long long workspace_elems, int* counters, long long n_counters,
-                       int force_splits, const RopeOut* rope, void* stream, const NormIn* nin = nullptr) {
+                       int force_splits, const RopeOut* rope, void* stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (nin) {   // x is the float32 residual: the kernel normalises it itself (few tokens, K a multiple of 64 up to 4096)
-        if (M > 16 || K % BK != 0 || K > NORM_KB_MAX * BK || rope || ((uintptr_t)w & 15) != 0 ||
-            ((uintptr_t)nin->x & 15) != 0 || nin->ldx % 4 != 0 || ((uintptr_t)nin->gain & 15) != 0)
-            return BW_ERR_UNSUPPORTED;
-    } else
     if (!bw_gemm_tc_supported(x, w, K, ldx)) return BW_ERR_UNSUPPORTED;
     if (accumulate && out_type != BW_F32) return BW_ERR_BAD_ARG;
     if (swiglu && (N % (2 * SWIGLU_BLOCK) != 0 || out_type != BW_BF16 || accumulate || bias || ldo < N / 2))
@@ -1113,8 +1046,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     CUtensorMap ta, tb;
     const void* a_ptr = tr ? w : x; const void* b_ptr = tr ? x : w;
     const long long a_ld = tr ? K : ldx, b_ld = tr ? ldx : K;
-    std::memset(&tb, 0, sizeof(tb));
-    if (!make_map(&ta, a_ptr, a_rows, K, a_ld, BM) || (!nin && !make_map(&tb, b_ptr, b_rows, K, b_ld, bn))) return BW_ERR_DRIVER;
+    if (!make_map(&ta, a_ptr, a_rows, K, a_ld, BM) || !make_map(&tb, b_ptr, b_rows, K, b_ld, bn)) return BW_ERR_DRIVER;
 
     Epilogue ep;
     // few tokens: the last warp of each tile sums the splits inside the kernel; more: a second kernel
@@ -1154,11 +1086,6 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
         case 240: rc = launch<240, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         case 256: rc = launch<256, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         default: return BW_ERR_BAD_ARG; }
-    if (nin) {
-        if (!tr || bn != 16) return BW_ERR_UNSUPPORTED;
-        rc = launch<16, false, true>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s, *nin);
-        return rc;
-    }
     // many tokens, no K split: CTA pairs on tiles of 256 tokens (BW_GEMM_PAIR=0 keeps single CTAs)
     static const bool pairs_on = []{ const char* e = getenv("BW_GEMM_PAIR"); return !(e && e[0] == '0'); }();
     if (pairs_on && !tr && splits == 1 && M >= 512) {
@@ -1220,19 +1147,6 @@ BW_EXPORT int bw_gemm_tc_rope(const void* x, const void* w, const void* bias, in
     ro.nh = nh; ro.nkv = nkv; ro.hd = hd; ro.rd = rd; ro.page_size = page_size;
     return run_gemm_tc(x, w, bias, bias_type, nullptr, BW_BF16, M, (nh + 2 * nkv) * hd, K, ldx, 0, 0, 0, workspace,
                        workspace_elems, counters, n_counters, force_splits, &ro, stream);
-}
-
-// RMSNorm and product in one kernel, for up to 16 tokens: out (=|+=) rmsnorm(x) . w^T (+ bias), x the float32
-// residual rows [M, K] (row stride ldx), gain [K] (float32 or bf16), K a multiple of 64 up to 4096;
-// the other arguments as in bw_gemm_tc (swiglu as there).
-BW_EXPORT int bw_gemm_tc_normed(const float* x, const void* gain, int gain_type, float eps, const void* w, const void* bias,
-                                int bias_type, void* out, int out_type, int M, int N, int K, long long ldx, long long ldo,
-                                int accumulate, int swiglu, float* workspace, long long workspace_elems, int* counters,
-                                long long n_counters, int force_splits, void* stream) {
-    NormIn nin;
-    nin.x = x; nin.gain = gain; nin.ldx = ldx; nin.gain_type = gain_type; nin.eps = eps;
-    return run_gemm_tc(x, w, bias, bias_type, out, out_type, M, N, K, K, ldo, accumulate, swiglu, workspace,
-                       workspace_elems, counters, n_counters, force_splits, nullptr, stream, &nin);
 }
 
 // Reads and clears the status word (synchronises the device).  0: no wait ever gave up.

@@ -374,61 +374,6 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
     return out
 
 
-NORMED_MAX_TOKENS = 16     # gemm_tc_normed: tokens a step may have
-NORMED_MAX_K = 4096        # ... and the width of the rows it normalises (a multiple of 64)
-_GEMM_TC_NORMED_ARGS = [c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                        c_ll, c_ll, c_int, c_int, c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p]
-
-
-def gemm_tc_normed_supports(residual: torch.Tensor, gain: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether :func:`gemm_tc_normed` takes this: up to 16 float32 rows of a width that is a multiple of
-    64 up to 4096, a bfloat16 weight, 16-byte aligned."""
-    M, K = residual.shape
-    return (residual.dtype == torch.float32 and residual.is_cuda and residual.stride(1) == 1 and residual.stride(0) % 4 == 0
-            and M <= NORMED_MAX_TOKENS and K % 64 == 0 and K <= NORMED_MAX_K and w.dtype == torch.bfloat16
-            and w.is_contiguous() and w.shape[1] == K and gain.numel() == K and gain.is_contiguous()
-            and gain.dtype in (torch.float32, torch.bfloat16)
-            and residual.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and gain.data_ptr() % 16 == 0)
-
-
-def gemm_tc_normed(residual: torch.Tensor, gain: torch.Tensor, eps: float, w: torch.Tensor,
-                   bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                   out_dtype: Optional[torch.dtype] = None, accumulate: bool = False, swiglu: bool = False,
-                   force_splits: int = 0) -> torch.Tensor:
-    """``out (=|+=) rmsnorm(residual; gain, eps) @ w.T (+ bias)`` in ONE kernel for a few tokens: the
-    product's CTAs normalise the float32 rows themselves (rounded to bfloat16 as :func:`rmsnorm`
-    does) while the weight tiles stream in.  The other arguments as in :func:`gemm_tc`."""
-    _dev(residual, "residual", torch.float32, contiguous=False); _dev(w, "w", torch.bfloat16); _dev(gain, "gain")
-    if not gemm_tc_normed_supports(residual, gain, w):
-        raise KernelError("gemm_tc_normed: up to 16 float32 rows, K a multiple of 64 up to 4096, bfloat16 weight, "
-                          "16-byte aligned")
-    M, K = residual.shape
-    N = w.shape[0]
-    n_out = N
-    if swiglu:
-        if N % (2 * SWIGLU_BLOCK) or bias is not None or accumulate:
-            raise KernelError("gemm_tc_normed: the SwiGLU epilogue needs N = 2 I with I a multiple of 16, no bias, no accumulate")
-        n_out, out_dtype = N // 2, torch.bfloat16
-    if out is None:
-        if accumulate:
-            raise KernelError("gemm: accumulate needs an output tensor")
-        out = torch.empty((M, n_out), dtype=out_dtype or torch.bfloat16, device=residual.device)
-    _dev(out, "out", contiguous=False)
-    if out.shape != (M, n_out) or out.stride(1) != 1:
-        raise KernelError("gemm: out must be [M, N] with contiguous rows")
-    if bias is not None:
-        _dev(bias, "bias")
-        if bias.numel() != N:
-            raise KernelError("gemm: bias must have N entries")
-    ws, counters = _workspace(residual.device)
-    fn = _fn("gemm_tc", "bw_gemm_tc_normed", _GEMM_TC_NORMED_ARGS, tag=f"normed{M}x{N}x{K}" if _timings is not None else None)
-    _check(fn(_ptr(residual), _ptr(gain), _code(gain, "gain"), float(eps), _ptr(w), _ptr(bias),
-              _code(bias, "bias") if bias is not None else 0, _ptr(out), _code(out, "out"), M, N, K, residual.stride(0),
-              out.stride(0), int(accumulate), int(swiglu), _ptr(ws), ws.numel(), _ptr(counters), counters.numel(),
-              int(force_splits), _stream()), "gemm_tc_normed")
-    return out
-
-
 def rotary_row_order(nh: int, nkv: int, hd: int, rotary_dim: int) -> torch.Tensor:
     """Row order of a fused q/k/v weight for :func:`gemm_tc_rope`: in every q and k head rows 2j
     and 2j + 1 are channels j and j + rotary_dim / 2; the other rows and the v heads stay."""

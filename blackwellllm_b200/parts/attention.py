@@ -16,13 +16,11 @@ from typing import Dict, List
 import torch
 
 from ..kernels import ops
-from .base import (BuildContext, Mixer, PagedKVRequest, ParamSpec, as_tensor, build_position, register_mixer)
+from .base import (BuildContext, Mixer, PagedKVRequest, ParamSpec, build_position, register_mixer)
 from .linear import Linear
 
 
 class GQAAttention(Mixer):
-    takes_normed = True
-
     def __init__(self, spec, hidden_size: int, ctx: BuildContext):
         self.nh, self.nkv, self.hd = int(spec.num_heads), int(spec.num_kv_heads), int(spec.head_dim)
         if self.nh % self.nkv:
@@ -65,7 +63,7 @@ class GQAAttention(Mixer):
 
     def forward(self, x, residual, batch, cache, owns_cache: bool = True) -> None:
         if self.project is not None:
-            q = self.project(x if getattr(self.project, "takes_normed", False) else as_tensor(x), batch, cache, owns_cache)
+            q = self.project(x, batch, cache, owns_cache)
         else:
             qkv = self.qkv(x, out_dtype=torch.float32)
             q = self.position.rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, append=owns_cache)

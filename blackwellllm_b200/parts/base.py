@@ -84,31 +84,6 @@ class Norm(Part):
         raise NotImplementedError
 
 
-class Normed:
-    """The input of a mixer or feed-forward that has not been normalised yet: the residual stream and
-    the norm that is to be applied to it.  A part that sets ``takes_normed = True`` receives this
-    instead of a tensor and may hand it to a kernel that normalises on the fly
-    (:meth:`rms` tells what an RMSNorm would do); :meth:`tensor` runs the norm as a kernel of its own."""
-
-    def __init__(self, norm: "Norm", residual: torch.Tensor):
-        self.norm, self.residual = norm, residual
-        self._value: Optional[torch.Tensor] = None
-
-    def tensor(self) -> torch.Tensor:
-        if self._value is None:
-            self._value = self.norm.forward(self.residual)
-        return self._value
-
-    def rms(self):
-        """(gain, eps) if the norm is an RMS norm over the whole row, else None."""
-        f = getattr(self.norm, "rms_parameters", None)
-        return f() if f is not None else None
-
-
-def as_tensor(x) -> torch.Tensor:
-    return x.tensor() if isinstance(x, Normed) else x
-
-
 class PositionEncoding(Part):
     def rotate_append(self, qkv, batch, cache, nh: int, nkv: int, hd: int, append: bool = True) -> torch.Tensor:
         """qkv [T, (nh + 2 nkv) * hd] float32 -> encoded queries [T, nh * hd]; encoded keys and raw
@@ -118,14 +93,12 @@ class PositionEncoding(Part):
     def fuse_projection(self, weight: torch.Tensor, bias: Optional[torch.Tensor], nh: int, nkv: int, hd: int):
         """Optional: an encoding that can run inside the q/k/v projection returns a callable
         ``project(x, batch, cache, append) -> queries`` that replaces projection plus
-        :meth:`rotate_append` (``x``: the normalised input; a callable with an attribute
-        ``takes_normed = True`` gets the :class:`Normed` instead) (it may keep its own copy of ``weight`` and ``bias`` in another
+        :meth:`rotate_append` (it may keep its own copy of ``weight`` and ``bias`` in another
         row order).  None: the mixer projects and calls :meth:`rotate_append`."""
         return None
 
 
 class Mixer(Part):
-    takes_normed = False   # True: forward() gets a Normed (see above) instead of the normalised tensor
     graph_safe = True  # False: forward() does host work between kernels; decode steps then run uncaptured
 
     def cache_request(self):
@@ -136,8 +109,6 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    takes_normed = False
-
     def forward(self, x, residual, batch) -> None:
         raise NotImplementedError
 

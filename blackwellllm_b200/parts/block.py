@@ -10,7 +10,7 @@ from typing import Dict, List
 
 import torch
 
-from .base import (Block, BuildContext, Normed, ParamSpec, build_ffn, build_mixer, build_norm,
+from .base import (Block, BuildContext, ParamSpec, build_ffn, build_mixer, build_norm,
                    register_block)
 
 
@@ -44,12 +44,11 @@ class PreNormBlock(Block):
             part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
 
     def forward(self, residual, batch, cache, owns_cache: bool = True) -> None:
-        # a part that takes a Normed decides itself whether the norm runs as a kernel of its own
-        x = Normed(self.mixer_norm, residual)
-        self.mixer.forward(x if self.mixer.takes_normed else x.tensor(), residual, batch, cache, owns_cache)
+        x = self.mixer_norm.forward(residual)
+        self.mixer.forward(x, residual, batch, cache, owns_cache)
         if self.ffn is not None:
-            x = Normed(self.ffn_norm, residual)
-            self.ffn.forward(x if self.ffn.takes_normed else x.tensor(), residual, batch)
+            x = self.ffn_norm.forward(residual)
+            self.ffn.forward(x, residual, batch)
 
 
 register_block("prenorm", PreNormBlock)

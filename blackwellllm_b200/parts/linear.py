@@ -13,7 +13,6 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from .base import Normed
 
 
 class Linear:
@@ -26,15 +25,8 @@ class Linear:
 
     def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None, accumulate: bool = False) -> torch.Tensor:
-        """``out (=|+=) x @ W.T (+ bias)``.  ``accumulate`` adds into ``out`` (float32).  ``x`` may be a
-        :class:`Normed`: with few tokens the norm then runs inside the product's kernel."""
+        """``out (=|+=) x @ W.T (+ bias)``.  ``accumulate`` adds into ``out`` (float32)."""
         w = self.weight
-        if isinstance(x, Normed):
-            rms = x.rms()
-            if rms is not None and w.dtype == torch.bfloat16 and ops.gemm_tc_normed_supports(x.residual, rms[0], w):
-                return ops.gemm_tc_normed(x.residual, rms[0], rms[1], w, self.bias, out=out, out_dtype=out_dtype,
-                                          accumulate=accumulate)
-            x = x.tensor()
         if x.dtype != w.dtype:
             raise ops.KernelError(f"Linear: input is {x.dtype}, weight is {w.dtype}")
         if w.dtype == torch.bfloat16 and ops.gemm_tc_supports(x, w):

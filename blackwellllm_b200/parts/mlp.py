@@ -15,13 +15,11 @@ from typing import Dict, List
 import torch
 
 from ..kernels import ops
-from .base import BuildContext, FeedForward, Normed, ParamSpec, as_tensor, register_ffn
+from .base import BuildContext, FeedForward, ParamSpec, register_ffn
 from .linear import Linear
 
 
 class SwiGLU(FeedForward):
-    takes_normed = True
-
     def __init__(self, spec, hidden_size: int, ctx: BuildContext):
         self.intermediate_size = int(spec.intermediate_size)
         self.hidden_size = hidden_size
@@ -47,11 +45,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, residual, batch) -> None:
         if self.fused:
-            rms = x.rms() if isinstance(x, Normed) else None
-            if rms is not None and ops.gemm_tc_normed_supports(x.residual, rms[0], self.gate_up.weight):
-                a = ops.gemm_tc_normed(x.residual, rms[0], rms[1], self.gate_up.weight, swiglu=True)
-            else:
-                a = ops.gemm_tc(as_tensor(x), self.gate_up.weight, swiglu=True)
+            a = ops.gemm_tc(x, self.gate_up.weight, swiglu=True)
         else:
             a = ops.swiglu(self.gate_up(x))
         self.down(a, out=residual, accumulate=True)

@@ -28,11 +28,6 @@ class RMSNorm(Norm):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].contiguous()
 
-    def rms_parameters(self):
-        """What a kernel that normalises on the fly needs: (gain, eps); the output is rounded to the
-        compute dtype as here."""
-        return self.weight, self.eps
-
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, self.ctx.dtype, rows=rows)
 

@@ -17,8 +17,7 @@ import math
 import torch
 
 from ..kernels import ops
-from .base import BuildContext, PositionEncoding, as_tensor, register_position
-from .linear import Linear
+from .base import BuildContext, PositionEncoding, register_position
 
 
 def rotary_inv_freq(theta: float, rotary_dim: int, scaling=None) -> torch.Tensor:
@@ -69,17 +68,14 @@ class RotaryEncoding(PositionEncoding):
         w = weight.index_select(0, order).contiguous()
         b = bias.index_select(0, order).contiguous() if bias is not None else None
 
-        lin = Linear(w, b)
-
         def project(x, batch, cache, append=True):
             if batch.T <= ops.GEMM_FUSED_REDUCE_MAX_TOKENS:
                 # few tokens: the product sums its K splits in its last warps, and the rotation on
                 # top of that was measured slower than a kernel of its own on the paired layout
-                qkv = lin(x, out_dtype=torch.float32)       # x may still carry its norm: run inside the product
+                qkv = ops.gemm_tc(x, w, b, out_dtype=torch.float32)
                 return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
                                        self.inv_freq, self.rotary_dim, cache.k_pages, cache.v_pages, nh, nkv, hd,
                                        append=append, table=self._table(batch), paired=True)
-            x = as_tensor(x)
             slots = None
             if append:   # where the step's tokens go in this cache group: the same for all its layers
                 key = ("kv_slots", cache.group)
@@ -90,7 +86,6 @@ class RotaryEncoding(PositionEncoding):
                     batch.extras[key] = slots
             return ops.gemm_tc_rope(x, w, b, self._table(batch), slots, cache.k_pages, cache.v_pages, nh, nkv, hd,
                                     self.rotary_dim)
-        project.takes_normed = True   # x may be a Normed: with few tokens its norm runs inside the product
         return project
 
 
