@@ -156,12 +156,13 @@ def main():
         torch.cuda.synchronize()
         pre_ms.append(s.elapsed_time(e))
         eng.end_request("prefill")
-    prefill_ms = min(pre_ms[1:]) if pre_ms else float("nan")
+    prefill_ms = min(pre_ms[1:]) if pre_ms else None
     nh, hd = cfg["num_attention_heads"], cfg["head_dim"]
     prefill_flops = 2.0 * T * args.layers * per_layer + 2.0 * V * cfg["hidden_size"] \
         + args.layers * 4.0 * nh * hd * T * (T + 1) / 2
-    prefill = {"value": T / (prefill_ms / 1e3), "tokens": T, "ms": prefill_ms,
-               "frac": prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+    prefill = {"value": None, "tokens": T, "ms": None, "frac": None} if prefill_ms is None else \
+        {"value": T / (prefill_ms / 1e3), "tokens": T, "ms": prefill_ms,
+         "frac": prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
 
     # ---------------- decode at context C: caches of B requests filled with random keys and values
     def fill_cache(B):
