@@ -1088,16 +1088,21 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
         default: return BW_ERR_BAD_ARG; }
     // many tokens, no K split: CTA pairs on tiles of 256 tokens (BW_GEMM_PAIR=0 keeps single CTAs)
     static const bool pairs_on = []{ const char* e = getenv("BW_GEMM_PAIR"); return !(e && e[0] == '0'); }();
-    if (pairs_on && !tr && splits == 1 && M >= 512) {
-        // the width whose rounds over the 74 pairs cost least
-        const int pa = ceil_div(M, 2 * BM);
+    // pairs or single CTAs: whichever needs less time for its rounds of tiles.  A round of pair tiles
+    // (256 tokens x W features on two CTAs) costs W / 1.18 (pairs were measured 15-20 % faster per
+    // flop), a round of single tiles W (W / 0.9 at 128 columns).
+    int pbn = 256; double pair_cost = 0.0;
+    const int pa = ceil_div(M, 2 * BM);
+    {
         const int widths[2] = {256, 224};   // (240 works but was measured no faster than 256)
-        int pbn = 256; double best_cost = 0.0;
         for (int i = 0; i < 2; ++i) {
             const long long t = (long long)pa * ceil_div(N, widths[i]);
-            const double cost = (double)ceil_div(t, NUM_SMS / 2) * widths[i];
-            if (i == 0 || cost < best_cost * 0.995) { best_cost = cost; pbn = widths[i]; }
+            const double cost = (double)ceil_div(t, NUM_SMS / 2) * widths[i] / 1.18;
+            if (i == 0 || cost < pair_cost * 0.995) { pair_cost = cost; pbn = widths[i]; }
         }
+    }
+    const double single_cost = (double)ceil_div((long long)tiles_a * tiles_b, NUM_SMS) * bn * (bn == 128 ? 1.0 / 0.9 : 1.0);
+    if (pairs_on && !tr && splits == 1 && M > 256 && pair_cost <= single_cost) {
         CUtensorMap tb2;
         if (!make_map(&tb2, b_ptr, b_rows, K, b_ld, pbn / 2)) return BW_ERR_DRIVER;
         const int pb = ceil_div(N, pbn);
