@@ -288,10 +288,6 @@ class CacheManager:
         native().bwh_free_pages(self._h, self._scratch)
         return list(self._scratch[:len(self.groups)])
 
-    def held_pages(self) -> List[int]:
-        return [sum(1 for rid in self._handles for p in self.block_table(rid, gi) if p >= 0)
-                for gi in range(len(self.groups))]
-
     def check_invariants(self) -> None:
         """No page lost and none held twice: per group, pages held by requests plus
         free pages are exactly the pool; every slot is either free or a live request's."""

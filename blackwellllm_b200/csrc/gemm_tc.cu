@@ -46,6 +46,7 @@ constexpr int FUSED_REDUCE_MAX_TOKENS = 16;   // split-K sums inside the kernel 
 constexpr int SWIGLU_BLOCK = 16;   // gate/up features are interleaved in blocks of 16 rows of the weight
 
 __device__ int g_status = 0;  // 0 ok; else the code of the first wait that gave up
+int g_pair_mode = -1;         // see bw_gemm_tc_pair_mode
 
 // Rotary epilogue of a fused q/k/v projection: features are (q heads, k heads, v heads) x hd.  In
 // the rotated heads the weight rows are ordered so that features 2j and 2j + 1 are channel j and
@@ -1086,8 +1087,9 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
         case 240: rc = launch<240, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         case 256: rc = launch<256, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         default: return BW_ERR_BAD_ARG; }
-    // many tokens, no K split: CTA pairs on tiles of 256 tokens (BW_GEMM_PAIR=0 keeps single CTAs)
-    static const bool pairs_on = []{ const char* e = getenv("BW_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    // many tokens, no K split: CTA pairs on tiles of 256 tokens (mode 0: never; 1: when their rounds of
+    // tiles take less time; 2: whenever they can; from BW_GEMM_PAIR or bw_gemm_tc_pair_mode)
+    if (g_pair_mode < 0) { const char* e = getenv("BW_GEMM_PAIR"); g_pair_mode = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1; }
     // pairs or single CTAs: whichever needs less time for its rounds of tiles.  A round of pair tiles
     // (256 tokens x W features on two CTAs) costs W / 1.18 (pairs were measured 15-20 % faster per
     // flop), a round of single tiles W (W / 0.9 at 128 columns).
@@ -1102,7 +1104,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
         }
     }
     const double single_cost = (double)ceil_div((long long)tiles_a * tiles_b, NUM_SMS) * bn * (bn == 128 ? 1.0 / 0.9 : 1.0);
-    if (pairs_on && !tr && splits == 1 && M > 256 && pair_cost <= single_cost) {
+    if (g_pair_mode > 0 && !tr && splits == 1 && M > 256 && (g_pair_mode == 2 || pair_cost <= single_cost)) {
         CUtensorMap tb2;
         if (!make_map(&tb2, b_ptr, b_rows, K, b_ld, pbn / 2)) return BW_ERR_DRIVER;
         const int pb = ceil_div(N, pbn);
@@ -1152,6 +1154,14 @@ BW_EXPORT int bw_gemm_tc_rope(const void* x, const void* w, const void* bias, in
     ro.nh = nh; ro.nkv = nkv; ro.hd = hd; ro.rd = rd; ro.page_size = page_size;
     return run_gemm_tc(x, w, bias, bias_type, nullptr, BW_BF16, M, (nh + 2 * nkv) * hd, K, ldx, 0, 0, 0, workspace,
                        workspace_elems, counters, n_counters, force_splits, &ro, stream);
+}
+
+// When products of more than 256 tokens run on CTA pairs: 0 never, 1 when the estimate says they are
+// faster (the default), 2 whenever the product allows it (tests).  Returns the mode before.
+BW_EXPORT int bw_gemm_tc_pair_mode(int mode) {
+    const int old = g_pair_mode;
+    if (mode >= 0 && mode <= 2) g_pair_mode = mode;
+    return old;
 }
 
 // Reads and clears the status word (synchronises the device).  0: no wait ever gave up.

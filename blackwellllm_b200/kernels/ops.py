@@ -433,6 +433,13 @@ def gemm_tc_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     return q_out
 
 
+def gemm_pair_mode(mode: int) -> int:
+    """When products of more than 256 tokens run on CTA pairs: 0 never, 1 when estimated faster (the
+    default), 2 whenever possible.  Returns the mode before (-1: not set yet, i.e. the default)."""
+    fn = _fn("gemm_tc", "bw_gemm_tc_pair_mode", [c_int])
+    return fn(int(mode))
+
+
 def gemm_tc_status() -> int:
     """0 if no bounded wait in the tensor-core kernels ever gave up (synchronises the device)."""
     lib = load_library("gemm_tc")

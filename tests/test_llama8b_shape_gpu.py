@@ -109,11 +109,22 @@ MID = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_siz
        "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_steps_of_more_than_512_tokens(dtype):
+@pytest.mark.parametrize("dtype,pairs", [("float32", 1), ("bfloat16", 1), ("bfloat16", 2)])
+def test_steps_of_more_than_512_tokens(dtype, pairs):
     """Steps wide enough for the products to run on CTA pairs (rotary and cache append, SwiGLU and
     the residual sum in their epilogues; q/k/v bias): a prompt of 700 tokens whole, then in portions of
     530 + 170 beside another request, against the plain implementation at every position."""
+    from blackwellllm_b200 import Engine, StepEntry
+    from blackwellllm_b200.kernels import ops
+    from blackwellllm_b200.weights.random_init import model_param_specs, random_tensors
+    before = ops.gemm_pair_mode(pairs)      # 2: every product that can runs on CTA pairs, whatever the estimate says
+    try:
+        _steps_of_more_than_512_tokens(dtype)
+    finally:
+        ops.gemm_pair_mode(before if before >= 0 else 1)
+
+
+def _steps_of_more_than_512_tokens(dtype):
     from blackwellllm_b200 import Engine, StepEntry
     from blackwellllm_b200.weights.random_init import model_param_specs, random_tensors
     W = random_tensors(model_param_specs(MID), seed=21, std=0.05, bias_std=0.3,
