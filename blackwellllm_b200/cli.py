@@ -53,6 +53,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--temperature", type=float, default=0.6)
     ap.add_argument("--top-p", type=float, default=0.9)
     ap.add_argument("--max-new-tokens", type=int, default=1024)
+    ap.add_argument("--repetition-penalty", type=float, default=1.0,
+                    help="> 1 makes tokens already generated less likely (with --prompt-ids; default off)")
     ap.add_argument("--prompt-ids", default=None, help="comma-separated token ids: generate once and exit")
     ap.add_argument("--stats", action="store_true", help="print timing and scheduler counters")
     return ap
@@ -219,7 +221,8 @@ def main(argv=None) -> int:
         ids = parse_ids(args.prompt_ids)
         t0 = time.perf_counter()
         res = engine.generate(ids, SamplingParams(temperature=args.temperature, top_p=args.top_p,
-                                                  max_new_tokens=args.max_new_tokens))[0]
+                                                  max_new_tokens=args.max_new_tokens,
+                                                  repetition_penalty=args.repetition_penalty))[0]
         dt = time.perf_counter() - t0
         print(" ".join(str(t) for t in res.token_ids))
         if args.stats:

@@ -6,6 +6,9 @@
 //    tokens tied with the last one kept are kept too); then the inverse CDF over
 //    the kept tokens IN INDEX ORDER at the uniform number u[r] given by the host.
 //    The draw therefore depends on (logits row, u) only, not on the batch.
+//
+// Beside it: the repetition penalty on a row's logits before the choice, and the log
+// probability of a given token (the reference's src/kernels/sampling.cu:85-118 and 213-247).
 #include "common.cuh"
 
 namespace {
@@ -126,7 +129,71 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     if (threadIdx.x == 0) out[r] = chosen;
 }
 
+// Repetition penalty in place, one block per row: every DISTINCT id of the row's history
+// ids[begin[r] .. begin[r+1]) has its logit divided by penalty[r] when positive and multiplied
+// by it when not, once however often the id occurs (only an id's first occurrence acts).
+// penalty <= 1 and ids outside [0, V) do nothing.
+__global__ void repetition_penalty_kernel(float* __restrict__ logits, const int* __restrict__ ids,
+                                          const int* __restrict__ begin, const float* __restrict__ penalty,
+                                          int V, size_t ld) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    const int r = blockIdx.x;
+    const float pen = penalty[r];
+    if (!(pen > 1.f)) return;
+    const int* mine = ids + begin[r];
+    const int n = begin[r + 1] - begin[r];
+    float* row = logits + (size_t)r * ld;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int id = mine[i];
+        if (id < 0 || id >= V) continue;
+        bool first = true;
+        for (int j = 0; j < i && first; ++j) first = mine[j] != id;
+        if (!first) continue;
+        const float v = row[id];
+        row[id] = v > 0.f ? v / pen : v * pen;
+    }
+}
+
+// log softmax(row)[target[r]] per row, float32: (x_t - max) - log(sum exp(x - max)).
+__global__ void __launch_bounds__(THREADS)
+log_prob_kernel(const float* __restrict__ logits, const int* __restrict__ target, float* __restrict__ out,
+                int V, size_t ld) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    __shared__ float sf[32];
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    float mx = -INFINITY;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) mx = fmaxf(mx, row[c]);
+    mx = bw::block_max(mx, sf);
+    float s = 0.f;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) s += expf(row[c] - mx);
+    s = bw::block_sum(s, sf);
+    if (threadIdx.x == 0) out[r] = (row[target[r]] - mx) - logf(s);
+}
+
 }  // namespace
+
+BW_EXPORT int bw_repetition_penalty(float* logits, const int* ids, const int* begin, const float* penalty,
+                                    int R, int V, long long ld, void* stream) {
+    if (R <= 0) return 0;
+    if (V <= 0 || ld < V || !ids || !begin || !penalty) return BW_ERR_BAD_ARG;
+    bw::launch((repetition_penalty_kernel), dim3(R), dim3(256), 0, (cudaStream_t)stream, logits, ids, begin, penalty,
+               V, (size_t)ld);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+// target[r] must lie in [0, V): the caller checks it on the host.
+BW_EXPORT int bw_log_prob(const float* logits, const int* target, float* out, int R, int V, long long ld,
+                          void* stream) {
+    if (R <= 0) return 0;
+    if (V <= 0 || ld < V || !target || !out) return BW_ERR_BAD_ARG;
+    bw::launch((log_prob_kernel), dim3(R), dim3(THREADS), 0, (cudaStream_t)stream, logits, target, out, V, (size_t)ld);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
 
 // temperature, top_p: per row (may be null: greedy / no nucleus); u: per row uniform in [0,1).
 BW_EXPORT int bw_sample(const float* logits, const float* temperature, const float* top_p, const float* u,

@@ -6,18 +6,21 @@ them: ``InferenceConfig(max_context_length, max_batch_size, temperature, top_p)`
 position-addressed ``forward(token_id, pos, ...)`` that returns the next sampled
 token, ``prefill(token_ids, start_pos, ...)`` that consumes a prompt and samples
 only after its last token, ``forward_batch`` (one token each of distinct
-sequences, greedy), ``rewind`` and ``release_sequence``.  Beyond the reference,
+sequences, greedy), ``forward_eval`` and ``last_token_probability`` (log
+probability of a given next token), ``rewind`` and ``release_sequence``.  Beyond the reference,
 ``generate`` runs many requests with continuous batching through the scheduler.
 
 Token ids in, token ids out: the engine holds no tokenizer.
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 from typing import Dict, List, Mapping, Optional, Sequence, Union
 
 import torch
 
+from ..kernels import ops
 from ..sampling.params import SamplingParams, uniform
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
@@ -87,6 +90,7 @@ class BlackwellEngine:
         self.chunk = chunk
         self.max_batch_tokens = max_batch_tokens
         self._draws: Dict[int, int] = {}
+        self._last_logits: Dict[int, torch.Tensor] = {}   # rows of the LAST step's logits, by sequence
         self.scheduler = self._new_scheduler()
 
     def _new_scheduler(self) -> Scheduler:
@@ -147,7 +151,35 @@ class BlackwellEngine:
             last = at + n == len(ids)
             logits = self.engine.step([StepEntry(rid, ids[at:at + n], [n - 1] if last else [])])
             at += n
+        self._last_logits = {seq_id: logits[0]}
         return self._pick(logits, [seq_id], temperature, top_p)[0]
+
+    def forward_eval(self, token_id: int, pos: int, target_token_id: int, seq_id: int = 0) -> float:
+        """Feeds ``token_id`` at ``pos`` and returns ln P(target_token_id) of the next token,
+        for perplexity (the reference's forward_eval_status, src/core/engine.cpp:1557-1570)."""
+        self._check_token(target_token_id)
+        self._reconcile(seq_id, pos)
+        logits = self.engine.step([StepEntry(self._seq(seq_id), [token_id], [0])])
+        self._last_logits = {seq_id: logits[0]}
+        return self._log_prob(logits[:1], target_token_id)
+
+    def last_token_probability(self, token_id: int, seq_id: int = 0) -> float:
+        """P(token_id) under the logits that the last forward, prefill, forward_batch or
+        forward_eval left for the sequence, without a model step; 0 for an id outside the
+        vocabulary or a sequence that was not in that last call (the reference reads its one
+        logits buffer as the last step left it, src/core/engine.cpp:1618-1630)."""
+        row = self._last_logits.get(seq_id)
+        if row is None or not 0 <= token_id < self.vocab_size:
+            return 0.0
+        return min(1.0, max(0.0, math.exp(self._log_prob(row[None, :], token_id))))
+
+    def _check_token(self, token_id: int) -> None:
+        if not 0 <= token_id < self.vocab_size:
+            raise EngineError(f"token id {token_id} is outside the vocabulary of {self.vocab_size}")
+
+    def _log_prob(self, logits: torch.Tensor, token_id: int) -> float:
+        target = torch.tensor([token_id], dtype=torch.int32, device=logits.device)
+        return float(ops.log_prob(logits, target).item())
 
     def forward_batch(self, requests: Sequence[DecodeRequest]) -> List[int]:
         """One token each of distinct sequences, greedy (src/core/engine.cpp:1576-1616)."""
@@ -159,6 +191,7 @@ class BlackwellEngine:
         for r in requests:
             self._reconcile(r.seq_id, r.pos)
         logits = self.engine.step([StepEntry(self._seq(r.seq_id), [r.token_id], [0]) for r in requests])
+        self._last_logits = {s: logits[i] for i, s in enumerate(seqs)}
         return self._pick(logits, seqs, 0.0, 1.0)
 
     def rewind(self, seq_id: int, pos: int) -> None:
@@ -172,6 +205,7 @@ class BlackwellEngine:
         if self.engine.cache.has(rid):
             self.engine.cache.free_request(rid)
         self._draws.pop(seq_id, None)
+        self._last_logits.pop(seq_id, None)
 
     def reset_state(self, seq_id: int = 0) -> None:
         """Forgets the sequence (cache and any fixed-size state)."""
@@ -190,12 +224,13 @@ class BlackwellEngine:
             return []
         entries = [StepEntry(e.request.rid, e.tokens, [len(e.tokens) - 1] if e.samples else [])
                    for e in plan.entries]
+        self._last_logits = {}
         logits = self.engine.step(entries)
         samplers = [e.request for e in plan.entries if e.samples]
         sampled: Dict[int, int] = {}
         if samplers:
             toks = self.sampler.sample(logits, [r.params for r in samplers], [r.seed for r in samplers],
-                                       [len(r.generated) for r in samplers])
+                                       [len(r.generated) for r in samplers], [r.generated for r in samplers])
             sampled = {r.rid: t for r, t in zip(samplers, toks)}
         done = self.scheduler.commit(plan, sampled)
         return [GenerationResult(r.rid, r.prompt, r.generated, r.finish_reason, r.preemptions) for r in done]

@@ -293,6 +293,41 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Opt
     return out
 
 
+def repetition_penalty(logits: torch.Tensor, ids: torch.Tensor, begin: torch.Tensor, penalty: torch.Tensor) -> torch.Tensor:
+    """In place on ``logits`` [R, V]: each distinct id of row r's history ``ids[begin[r]:begin[r+1]]``
+    has its logit divided by ``penalty[r]`` when positive, multiplied when not; penalty <= 1 is off."""
+    _dev(logits, "logits", torch.float32, contiguous=False)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("repetition_penalty: logits must be [R, V] with contiguous rows")
+    R, V = logits.shape
+    _dev(ids, "ids", torch.int32)
+    _dev(begin, "begin", torch.int32)
+    _dev(penalty, "penalty", torch.float32)
+    if begin.numel() != R + 1 or penalty.numel() != R:
+        raise KernelError("repetition_penalty: begin needs R + 1 entries and penalty R")
+    fn = _fn("sampling", "bw_repetition_penalty",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p])
+    _check(fn(_ptr(logits), _ptr(ids), _ptr(begin), _ptr(penalty), R, V, logits.stride(0), _stream()),
+           "repetition_penalty")
+    return logits
+
+
+def log_prob(logits: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+    """log softmax(logits[r])[target[r]] for each row, float32 [R].  ``target`` int32 in [0, V)
+    (checked by the caller on the host)."""
+    _dev(logits, "logits", torch.float32, contiguous=False)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("log_prob: logits must be [R, V] with contiguous rows")
+    R, V = logits.shape
+    _dev(target, "target", torch.int32)
+    if target.numel() != R:
+        raise KernelError("log_prob: one target per row")
+    out = torch.empty((R,), dtype=torch.float32, device=logits.device)
+    fn = _fn("sampling", "bw_log_prob", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p])
+    _check(fn(_ptr(logits), _ptr(target), _ptr(out), R, V, logits.stride(0), _stream()), "log_prob")
+    return out
+
+
 # ------------------------------------------------------------------ dispatch
 
 _GEMM_TC_ARGS = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int,

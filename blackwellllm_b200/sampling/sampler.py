@@ -1,13 +1,15 @@
 """Chooses one token per logits row on the device.
 
-Per row: greedy, or temperature softmax with an optional nucleus and an inverse
-CDF draw at a uniform number that the host takes from the request's own Philox
-stream (``sampling.params.uniform(seed, draw_index)``).  One small upload of
-(temperature, top_p, u) per step, one kernel, one read-back of the tokens.
+Per row: an optional repetition penalty on the tokens the request has emitted, then
+greedy, or temperature softmax with an optional nucleus and an inverse CDF draw at a
+uniform number that the host takes from the request's own Philox stream
+(``sampling.params.uniform(seed, draw_index)``).  One small upload of (temperature,
+top_p, u) per step (and one of the penalized ids where a request asks for the
+penalty), one or two kernels, one read-back of the tokens.
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -20,15 +22,42 @@ class Sampler:
         self.device = device
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-               draw_index: Sequence[int]) -> List[int]:
+               draw_index: Sequence[int], generated: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
         """``logits`` [R, V] float32 on the device; row r uses params[r] and the
-        ``draw_index[r]``-th number of the stream of ``seeds[r]``."""
-        return self.sample_async(logits, params, seeds, draw_index).tolist()
+        ``draw_index[r]``-th number of the stream of ``seeds[r]``.  ``generated[r]``: what
+        request r has emitted so far, for its repetition penalty (the logits are changed
+        in place then)."""
+        return self.sample_async(logits, params, seeds, draw_index, generated).tolist()
 
-    def sample_async(self, logits, params, seeds, draw_index) -> torch.Tensor:
+    def penalize(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                 generated: Sequence[Sequence[int]]) -> None:
+        """The repetition penalty of every row that asks for it, in place."""
+        R = logits.shape[0]
+        if len(generated) != R:
+            raise ValueError("one history per logits row")
+        acts = [list(p.penalized(g)) for p, g in zip(params, generated)]
+        total = sum(len(a) for a in acts)
+        if total == 0:
+            return
+        host = torch.empty((total + R + 1,), dtype=torch.int32, pin_memory=True)
+        pen = torch.empty((R,), dtype=torch.float32, pin_memory=True)
+        at = 0
+        for r, a in enumerate(acts):
+            host[total + r] = at
+            if a:
+                host[at:at + len(a)] = torch.tensor(a, dtype=torch.int32)
+            at += len(a)
+            pen[r] = params[r].repetition_penalty if a else 1.0
+        host[total + R] = at
+        dev = host.to(self.device, non_blocking=True)
+        ops.repetition_penalty(logits, dev[:total], dev[total:], pen.to(self.device, non_blocking=True))
+
+    def sample_async(self, logits, params, seeds, draw_index, generated=None) -> torch.Tensor:
         R = logits.shape[0]
         if R != len(params):
             raise ValueError("one SamplingParams per logits row")
+        if generated is not None:
+            self.penalize(logits, params, generated)
         if all(p.greedy for p in params):
             return ops.sample(logits, None, None, None)
         host = torch.empty((3, R), dtype=torch.float32, pin_memory=True)

@@ -32,3 +32,22 @@ def plain_sample(logits: torch.Tensor, temperature: float, top_p: float, u: floa
     lo = float(cdf[idx] - kept[idx])
     margin = min(goal - lo, float(cdf[idx]) - goal) / mass
     return idx, margin
+
+
+def plain_repetition_penalty(logits: torch.Tensor, ids, penalty: float) -> torch.Tensor:
+    """src/kernels/sampling.cuh:10-29: every DISTINCT id among ``ids`` has its logit divided
+    by the penalty when positive and multiplied by it otherwise, once; ids outside the
+    vocabulary are skipped; a penalty <= 1 does nothing."""
+    out = logits.clone()
+    if penalty <= 1.0:
+        return out
+    for t in set(int(i) for i in ids):
+        if 0 <= t < out.numel():
+            out[t] = out[t] / penalty if float(out[t]) > 0 else out[t] * penalty   # in the logits' own precision
+    return out
+
+
+def plain_log_prob(logits: torch.Tensor, target: int) -> float:
+    """src/kernels/sampling.cu:213-247: (x_t - max) - log(sum exp(x - max)), here in double."""
+    lg = logits.double()
+    return float(lg[target] - lg.max() - torch.log(torch.exp(lg - lg.max()).sum()))

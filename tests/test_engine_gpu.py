@@ -2,12 +2,14 @@
 greedy generation, long decoding, the first tokens of a sequence, sampling with
 temperature and nucleus against the CPU twin, the position-addressed calls, and
 what happens when pages run out."""
+import math
+
 import pytest
 import torch
 
 import tiny
 from plain_model import load_plain_weights, plain_greedy, plain_logits
-from plain_sampling import plain_sample
+from plain_sampling import plain_log_prob, plain_repetition_penalty, plain_sample
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -137,6 +139,76 @@ def test_temperature_generation_is_seeded_and_independent_of_the_batch(folders):
     alone = make(folder, "float32", page_size=page, seed=2)
     solo = alone.generate([prompts[0]], sp)[0]          # request number 0 again, with no company
     assert solo.token_ids == res[0].token_ids
+
+
+def test_repetition_penalty_and_log_prob_kernels_match_the_cpu_twins():
+    from blackwellllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(3)
+    R, V = 5, 1003
+    base = torch.randn(R, V + 5, generator=g) * 4
+    logits = base.to(DEV)[:, :V]                       # rows with a stride that is not their width
+    hist = [[10, 20, 10, 10, 999, 20], [], [7] * 300 + [8, 9], [-1, V, V + 3, 5], list(range(0, V, 3))]
+    pens = [1.15, 1.5, 2.0, 1.3, 1.0]                  # the last row: penalty off
+    flat = [t for h in hist for t in h]
+    begin = [0]
+    for h in hist:
+        begin.append(begin[-1] + len(h))
+    out = ops.repetition_penalty(logits, torch.tensor(flat, dtype=torch.int32, device=DEV),
+                                 torch.tensor(begin, dtype=torch.int32, device=DEV),
+                                 torch.tensor(pens, dtype=torch.float32, device=DEV)).cpu()
+    for r in range(R):
+        want = plain_repetition_penalty(base[r, :V], hist[r], pens[r])
+        assert torch.equal(out[r], want), r
+    assert torch.equal(logits.cpu(), out)              # in place
+    targets = [0, V - 1, 500, 7, 123]
+    lp = ops.log_prob(logits, torch.tensor(targets, dtype=torch.int32, device=DEV)).cpu()
+    for r in range(R):
+        assert abs(float(lp[r]) - plain_log_prob(out[r], targets[r])) < 1e-4, r
+
+
+def test_generation_with_a_repetition_penalty_follows_the_plain_rule(folders):
+    """Greedy with a strong penalty over a window of 3: every token is the argmax of the plain
+    logits after the plain penalty on the last three generated tokens."""
+    from blackwellllm_b200 import SamplingParams
+    raw, _, page = tiny.CONFIGS["llama"]
+    folder = folders[("llama", "float32")]
+    W = load_plain_weights(folder)
+    llm = make(folder, "float32", page_size=page)
+    prompts = [tiny.prompt(n, raw["vocab_size"], 30 + n) for n in (5, 17)]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=10, repetition_penalty=50.0, repetition_window=3,
+                        ignore_eos=True)
+    res = llm.generate(prompts, sp)
+    for p, r in zip(prompts, res):
+        seq, gen = list(p), []
+        for t in r.token_ids:
+            lg = plain_repetition_penalty(plain_logits(raw, W, seq)[-1].float(), gen[-3:], 50.0)
+            top2 = torch.topk(lg, 2).values
+            if float(top2[0] - top2[1]) > 1e-4:
+                assert t == int(lg.argmax())
+            seq.append(t); gen.append(t)
+
+
+def test_forward_eval_and_last_token_probability(folders):
+    from blackwellllm_b200 import EngineError
+    raw, _, page = tiny.CONFIGS["qwen"]
+    folder = folders[("qwen", "float32")]
+    W = load_plain_weights(folder)
+    llm = make(folder, "float32", page_size=page)
+    ids = tiny.prompt(12, raw["vocab_size"], 4)
+    ref = plain_logits(raw, W, ids)
+    total = 0.0
+    for i in range(len(ids) - 1):                       # the perplexity loop of the reference's evaluation
+        lp = llm.forward_eval(ids[i], i, ids[i + 1])
+        assert abs(lp - plain_log_prob(ref[i], ids[i + 1])) < 1e-4
+        total += lp
+    assert total < 0
+    prob = llm.last_token_probability(ids[5])
+    assert abs(prob - math.exp(plain_log_prob(ref[len(ids) - 2], ids[5]))) < 1e-5
+    assert llm.last_token_probability(raw["vocab_size"]) == 0.0 and llm.last_token_probability(3, seq_id=9) == 0.0
+    with pytest.raises(EngineError, match="vocabulary"):
+        llm.forward_eval(ids[0], 0, raw["vocab_size"])
+    nxt = llm.prefill(ids, 0, 0.0, 1.0)                  # rewinds to 0 and leaves the last position's logits
+    assert abs(llm.last_token_probability(nxt) - math.exp(plain_log_prob(ref[-1], nxt))) < 1e-5
 
 
 def test_position_addressed_calls(folders):

@@ -7,7 +7,7 @@ import torch
 import tiny
 from plain_model import (plain_attention, plain_config, plain_greedy, plain_inv_freq, plain_logits, plain_rmsnorm,
                          plain_rope, plain_swiglu)
-from plain_sampling import plain_sample
+from plain_sampling import plain_log_prob, plain_repetition_penalty, plain_sample
 
 
 def test_config_defaults():
@@ -88,3 +88,16 @@ def test_plain_sampler():
     assert [plain_sample(lg, 1.0, 1.0, u)[0] for u in (0.05, 0.5, 0.95)] == [0, 1, 2]
     assert [plain_sample(lg, 1.0, 0.7, u)[0] for u in (0.05, 0.5, 0.95)] == [1, 1, 2]   # nucleus {1, 2}
     assert plain_sample(lg, 1.0, 0.5, 0.9)[0] == 1                                       # nucleus {1}
+
+
+def test_plain_repetition_penalty_and_log_prob():
+    # the reference's own test vectors (tests/validation/test_sampling.cpp:83-140): 4 -> 4 / 1.15, -4 -> -4 * 1.15,
+    # an id that occurs many times is penalized once, ids outside the vocabulary and a penalty <= 1 do nothing
+    lg = torch.zeros(32)
+    lg[10], lg[20] = 4.0, -4.0
+    out = plain_repetition_penalty(lg, [10, 20, 10, 10, -1, 99], 1.15)
+    assert float(out[10]) == float(torch.tensor(4.0) / 1.15) and float(out[20]) == float(torch.tensor(-4.0) * 1.15)
+    assert float(out.abs().sum()) == float(out[10].abs() + out[20].abs())
+    assert torch.equal(plain_repetition_penalty(lg, [10, 20], 1.0), lg)
+    probs = torch.tensor([0.1, 0.6, 0.3])
+    assert abs(plain_log_prob(probs.log() + 3.0, 1) - float(torch.log(torch.tensor(0.6)))) < 1e-6
