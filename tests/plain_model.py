@@ -29,7 +29,9 @@ def plain_config(raw: dict) -> dict:
     src/core/config.cpp:126-131 (required sizes), 144-145 (head_dim default),
     157 (rms_norm_eps default 1e-6), 158 (tie default false), 188 (rope_theta
     default 10000), 226-227 (qkv bias default: model_type == "qwen2"),
-    263-273 (llama3 rope scaling keys and their defaults).
+    263-273 (llama3 rope scaling keys and their defaults), 194-201 (the rotated
+    span: head_dim x partial_rotary_factor, default 1, rounded down to even;
+    the whole head if that leaves 0 or more than the head).
     """
     c = {
         "H": raw["hidden_size"], "nh": raw["num_attention_heads"],
@@ -41,6 +43,8 @@ def plain_config(raw: dict) -> dict:
     c["theta"] = raw.get("rope_theta", 10000.0)
     c["bias"] = raw.get("attention_bias", raw.get("model_type") == "qwen2")
     c["tie"] = raw.get("tie_word_embeddings", False)
+    rd = int(float(c["hd"]) * float(raw.get("partial_rotary_factor", 1.0)))
+    c["rd"] = (rd if 0 < rd <= c["hd"] else c["hd"]) & ~1
     rs = raw.get("rope_scaling")
     c["scaling"] = None
     if rs is not None and rs.get("rope_type", rs.get("type")) == "llama3":
@@ -172,7 +176,7 @@ def plain_logits(raw_config: dict, weights: Dict[str, torch.Tensor], ids: Sequen
     W = {k: v.to(dtype) for k, v in weights.items()}
     x = plain_embedding(W["model.embed_tokens.weight"], ids)
     positions = torch.arange(len(ids))
-    inv_freq = plain_inv_freq(c["hd"], c["theta"], c["scaling"])
+    inv_freq = plain_inv_freq(c["hd"], c["theta"], c["scaling"], c["rd"])
     for i in range(c["L"]):
         x = plain_layer(x, positions, W, i, c, inv_freq)
     x = plain_rmsnorm(x, W["model.norm.weight"], c["eps"])

@@ -71,7 +71,7 @@ def test_logits_prefix_property_and_greedy():
     """Causality of the whole model: logits of a prefix equal the first rows of the
     logits of the longer sequence."""
     from blackwellllm_b200.weights.random_init import model_param_specs, random_tensors
-    for name in ("llama", "qwen", "llama3"):
+    for name in ("llama", "qwen", "llama3", "partial"):
         raw, kw, _ = tiny.CONFIGS[name]
         W = random_tensors(model_param_specs(raw), kw["seed"], kw["std"], kw["bias_std"], dtype=torch.float32)
         ids = tiny.prompt(23, raw["vocab_size"], 1)
@@ -80,6 +80,10 @@ def test_logits_prefix_property_and_greedy():
         assert torch.allclose(plain_logits(raw, W, ids[:9]), full[:9], atol=1e-12)
         nxt = plain_greedy(raw, W, ids, 2)
         assert nxt[0] == int(full[-1].argmax())
+        if "partial_rotary_factor" in raw:   # the rotated span matters, and a factor of 1 is the default
+            whole = {k: v for k, v in raw.items() if k != "partial_rotary_factor"}
+            assert float((plain_logits(whole, W, ids) - full).abs().max()) > 1e-3 * float(full.abs().max())
+            assert torch.equal(plain_logits(dict(whole, partial_rotary_factor=1.0), W, ids), plain_logits(whole, W, ids))
 
 
 def test_plain_sampler():

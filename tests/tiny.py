@@ -1,6 +1,7 @@
 """Tiny configurations of the architecture for the tests.  They differ in every
 size and option: heads and groups, sizes that are no power of two, layers,
-vocabulary, the norms' eps, rope base and scaling, bias, tied head."""
+vocabulary, the norms' eps, rope base and scaling, the rotated span of a head,
+bias, tied head."""
 import os
 import tempfile
 
@@ -32,11 +33,20 @@ TINY_LLAMA3 = {
                      "high_freq_factor": 4.0, "original_max_position_embeddings": 32},
     "max_position_embeddings": 1024,
 }
+# half of each head rotated (partial_rotary_factor, src/core/config.cpp:194-201); six heads in three groups
+TINY_PARTIAL = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 72, "num_attention_heads": 6, "num_key_value_heads": 3, "head_dim": 48,
+    "intermediate_size": 200, "num_hidden_layers": 2, "vocab_size": 500,
+    "rope_theta": 20000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "partial_rotary_factor": 0.5, "max_position_embeddings": 2048,
+}
 
 CONFIGS = {
     "llama": (TINY_LLAMA, dict(seed=0, std=0.02, bias_std=None), 16),
     "qwen": (TINY_QWEN, dict(seed=1, std=0.05, bias_std=0.1), 8),
     "llama3": (TINY_LLAMA3, dict(seed=7, std=0.04, bias_std=None), 16),
+    "partial": (TINY_PARTIAL, dict(seed=11, std=0.05, bias_std=None), 32),
 }
 
 
