@@ -29,7 +29,18 @@ LLAMA_8B = {
                      "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
     "max_position_embeddings": 131072,
 }
-FULL_LAYERS = 32
+# the other two big shapes: for --shape, not for the default run
+QWEN25_7B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4, "head_dim": 128,
+    "intermediate_size": 18944, "num_hidden_layers": 28, "vocab_size": 152064,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 131072,
+}
+QWEN25_14B = dict(QWEN25_7B, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                  intermediate_size=13824, num_hidden_layers=48)
+SHAPES = {"llama-3.1-8b": ("Llama-3.1-8B", LLAMA_8B, 3), "qwen2.5-7b": ("Qwen2.5-7B", QWEN25_7B, 4),
+          "qwen2.5-14b": ("Qwen2.5-14B", QWEN25_14B, 5)}
 
 
 def peaks():
@@ -101,7 +112,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES),
+                    help="layer sizes (default: the Llama-3.1-8B shape of the headline number)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (for profiling)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--points", default="1,64", help="other decode batch sizes to report")
     ap.add_argument("--no-graphs", action="store_true")
@@ -123,7 +136,11 @@ def main():
     from blackwellllm_b200 import BlackwellEngine, DecodeRequest, InferenceConfig, StepEntry
     from blackwellllm_b200.kernels import ops
 
-    cfg = dict(LLAMA_8B, num_hidden_layers=args.layers)
+    shape_name, shape_cfg, weight_seed = SHAPES[args.shape]
+    full_layers = shape_cfg["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = full_layers
+    cfg = dict(shape_cfg, num_hidden_layers=args.layers)
     pk = peaks()
     page = 16
     sizes = sorted({args.batch, *[int(x) for x in args.points.split(",") if x]})
@@ -131,7 +148,7 @@ def main():
     room = args.context + args.warmup + args.steps * 2 + 64
     num_pages = max_b * -(-room // page) + -(-args.prefill_tokens // page) + 8
     llm = BlackwellEngine(None, InferenceConfig(max_context_length=room + 64, max_batch_size=max_b + 1),
-                          config=cfg, random_seed=3, random_std=0.02, dtype="bfloat16", page_size=page,
+                          config=cfg, random_seed=weight_seed, random_std=0.02, dtype="bfloat16", page_size=page,
                           num_pages=num_pages, max_batch_tokens=max(args.prefill_tokens, max_b), seed=0,
                           cuda_graphs=not args.no_graphs)
     eng = llm.engine
@@ -232,14 +249,15 @@ def main():
     achieved = bytes_step / (ms_step / 1e3) / 1e9
     blocks_w = -(-(args.context + 1) // page)
     out = {
-        "metric": "decode tok/s at batch 8, context 8192 (Llama-3.1-8B shape, bf16)",
+        "metric": f"decode tok/s at batch {B}, context {args.context} ({shape_name} shape, bf16)",
         "value": B / (ms_step / 1e3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "Llama-3.1-8B shape, random weights N(0,0.02) seed 3", "global_batch": B,
+        "config": {"model": f"{shape_name} shape, random weights N(0,0.02) seed {weight_seed}", "global_batch": B,
                    "seq_len": args.context, "parallelism": "single GPU", "layers": args.layers,
-                   "layers_full": FULL_LAYERS, "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128,
-                   "intermediate": 14336, "vocab": V, "page_size": page, "kv_dtype": "bf16",
+                   "layers_full": full_layers, "hidden": cfg["hidden_size"], "heads": nh,
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": hd,
+                   "intermediate": cfg["intermediate_size"], "vocab": V, "page_size": page, "kv_dtype": "bf16",
                    "kv_fill": "random keys/values at context-1 tokens", "l2": "inputs larger than L2",
                    "cuda_graphs": not args.no_graphs, "peaks": pk["source"]},
         "e2e": {"value": B / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
