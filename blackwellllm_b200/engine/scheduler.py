@@ -58,6 +58,15 @@ class Request:
     def remaining(self) -> int:
         return len(self.prompt) + len(self.generated) - self.num_computed
 
+    def span(self, start: int, n: int) -> List[int]:
+        """tokens[start:start + n] without joining the two lists."""
+        p = len(self.prompt)
+        if start >= p:
+            return self.generated[start - p:start - p + n]
+        if start + n <= p:
+            return self.prompt[start:start + n]
+        return self.prompt[start:] + self.generated[:start + n - p]
+
 
 @dataclass
 class PlannedEntry:
@@ -188,11 +197,12 @@ class Scheduler:
         entries: List[PlannedEntry] = []
         free = [f - n for f, n in zip(self.cache.free_pages(), need)]
         for r in decodes[:budget]:
-            entries.append(PlannedEntry(r, [r.tokens[-1]], True))
+            entries.append(PlannedEntry(r, r.span(r.num_computed, 1), True))
         budget -= len(entries)
+        decoding = {r.rid for r in decodes}
         # 2. prompt portions of running requests
         for r in self.running:
-            if r in decodes or budget <= 0:
+            if r.rid in decoding or budget <= 0:
                 continue
             n = min(r.remaining, budget, self.chunk or r.remaining)
             n = self._fit(r, n, free)
@@ -200,8 +210,7 @@ class Scheduler:
                 continue
             pn = self._pages_for(r, n)
             free = [f - p for f, p in zip(free, pn)]
-            toks = r.tokens[r.num_computed:r.num_computed + n]
-            entries.append(PlannedEntry(r, toks, n == r.remaining))
+            entries.append(PlannedEntry(r, r.span(r.num_computed, n), n == r.remaining))
             budget -= n
         # 3. admissions (a request preempted in this step waits for the next one)
         while (self.waiting and budget > 0 and len(self.running) < self.max_running
@@ -220,7 +229,7 @@ class Scheduler:
             self._admissions += 1
             self.stats.admitted += 1
             self.running.append(r)
-            entries.append(PlannedEntry(r, r.tokens[:n], n == r.remaining))
+            entries.append(PlannedEntry(r, r.span(0, n), n == r.remaining))
             budget -= n
         return entries
 
