@@ -8,13 +8,17 @@
 //     block table, the K and V tiles into 128-byte-swizzled shared memory (2 stages);
 //   * S = Q K^T: tcgen05.mma (M 128, N 64) into one of two TMEM buffers, so that S of the next tile
 //     is computed while the softmax warps work on this one;
-//   * four softmax warps, one thread per row (no shuffles): tcgen05.ld of the row of S, scale,
-//     mask, running maximum and sum in float32, P rounded to bfloat16 into swizzled shared memory;
-//   * O += P V: tcgen05.mma with V as an MN-major operand (keys are its K dimension), accumulated
-//     in TMEM over all tiles.  The exponent's reference m follows the row maximum lazily: only
-//     when the maximum has grown by more than 8 (a factor 256) since m was set does the warp
-//     rescale its rows of O in TMEM (tcgen05.ld, multiply, tcgen05.st); P stays below 2^8, the
-//     sums are float32, and O / l at the end is the same quotient.
+//   * four softmax warps, one thread per row (no shuffles), in two passes over the row of S with
+//     tcgen05.ld (32 keys at a time: the kernel stays within 128 registers): the maximum, then
+//     the probabilities 2^(s * scale - m) with running sum in float32, rounded to bfloat16 and
+//     written back with tcgen05.st over the first 32 columns of the S buffer they came from;
+//   * O += P V: tcgen05.mma with P read from tensor memory and V as an MN-major shared-memory
+//     operand (keys are its K dimension), accumulated in TMEM over all tiles.  P has the two
+//     buffers of S, so the softmax warps never wait for the P V of the tile before.  The
+//     exponent's reference m follows the row maximum lazily: only when the maximum has grown by
+//     more than 8 (a factor 256) since m was set does the warp wait for that P V and rescale its
+//     rows of O in TMEM (tcgen05.ld, multiply, tcgen05.st); P stays below 2^8, the sums are
+//     float32, and O / l at the end is the same quotient.
 // Warp 4 issues the MMAs, warp 5 the TMA loads.  Keys past the request's length are never loaded
 // (a resident page stands in, so the tile holds finite numbers) and are masked by position.
 // Every wait is bounded and sets a status word.
@@ -34,8 +38,8 @@ constexpr int NS = HD / 64;            // 128-byte column slices of a row
 constexpr int BM = 128, BN = 64, STAGES = 2;
 constexpr int THREADS = 192;
 constexpr int Q_SLICE = BM * 128, KV_SLICE = BN * 128;   // bytes of one column slice of a tile
-constexpr int Q_BYTES = NS * Q_SLICE, KV_BYTES = NS * KV_SLICE, P_BYTES = BM * 128;
-constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES + 16 * 8 + 16;   // 2 CTAs per SM at head size 128
+constexpr int Q_BYTES = NS * Q_SLICE, KV_BYTES = NS * KV_SLICE;
+constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + 16 * 8 + 16;   // 2 CTAs per SM at head size 128
 constexpr uint32_t TMEM_COLS = (128 + HD) <= 256 ? 256 : 512;   // S (two buffers of 64 columns), then O
 constexpr uint32_t IDESC_QK = bw::umma_idesc_bf16(BM, BN, false);
 constexpr uint32_t IDESC_PV = bw::umma_idesc_bf16(BM, 64, true);
@@ -61,7 +65,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(THREADS, HD <= 128 ? 2 : 1)
+// Two CTAs share an SM up to head size 128.  The bound is written for 256 threads, which caps the
+// registers at 128 a thread: the six warps of a CTA lie unevenly on the SM's four register files
+// (2, 2, 1, 1), and only with at most 128 registers does a new CTA fit beside a running one in
+// whichever way its warps fall; with more, it started only once the SM was empty.
+__global__ void __launch_bounds__(HD <= 128 ? 256 : THREADS, HD <= 128 ? 2 : 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, Params p) {
     BW_PDL_TRIGGER();
@@ -69,13 +77,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     uint8_t* q_s = smem;
     uint8_t* k_s = q_s + Q_BYTES;                 // [STAGES][KV_BYTES]
     uint8_t* v_s = k_s + STAGES * KV_BYTES;
-    uint8_t* p_s = v_s + STAGES * KV_BYTES;
-    uint64_t* bars = (uint64_t*)(p_s + P_BYTES);
-    // 0 q_full, 1..2 k_full, 3..4 v_full, 5..6 k_empty, 7..8 v_empty, 9..10 s_full, 11 p_full, 12 pv_done
+    uint64_t* bars = (uint64_t*)(v_s + STAGES * KV_BYTES);
+    // 0 q_full, 1..2 k_full, 3..4 v_full, 5..6 k_empty, 7..8 v_empty, 9..10 s_full, 11..12 p_full, 13..14 pv_done:
+    // one of each pair per S buffer, so that a wait by parity is never more than one phase behind
     uint32_t* tmem_slot = (uint32_t*)(bars + 16);
     const uint32_t bar0 = bw::smem_u32(bars);
     const uint32_t q_full = bar0, k_full = bar0 + 8, v_full = bar0 + 24, k_empty = bar0 + 40, v_empty = bar0 + 56,
-                   s_full = bar0 + 72, p_full = bar0 + 88, pv_done = bar0 + 96;
+                   s_full = bar0 + 72, p_full = bar0 + 88, pv_done = bar0 + 104;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -83,8 +91,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int s = 0; s < STAGES; ++s) {
             bw::mbar_init(k_full + 8 * s, 1); bw::mbar_init(v_full + 8 * s, 1); bw::mbar_init(k_empty + 8 * s, 1);
             bw::mbar_init(v_empty + 8 * s, 1); bw::mbar_init(s_full + 8 * s, 1);
+            bw::mbar_init(p_full + 8 * s, 4); bw::mbar_init(pv_done + 8 * s, 1);
         }
-        bw::mbar_init(p_full, 4); bw::mbar_init(pv_done, 1);
         bw::fence_barrier_init();
         bw::tma_prefetch_desc(&tmQ); bw::tma_prefetch_desc(&tmK); bw::tma_prefetch_desc(&tmV);
         tmem_slot[1] = (uint32_t)g_status;
@@ -169,18 +177,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 bw::umma_commit(s_full + 8 * s);
                 bw::umma_commit(k_empty + 8 * s);
             };
-            auto issue_pv = [&](int s, bool first) {
+            auto issue_pv = [&](int s, bool first) {   // P in the first 32 columns of S buffer s, values of stage s
 #pragma unroll
                 for (int h = 0; h < NS; ++h) {
 #pragma unroll
                     for (int kk = 0; kk < BN / 16; ++kk) {
-                        const uint64_t da = bw::umma_smem_desc_sw128(bw::smem_u32(p_s)) + 2 * kk;
                         const uint64_t db = bw::umma_smem_desc_mn_sw128(bw::smem_u32(v_s + s * KV_BYTES + h * KV_SLICE), KV_SLICE)
                                             + (uint64_t)kk * (2048 >> 4);   // 16 keys = two 8-row groups
-                        bw::umma_bf16(tmem_O + h * 64, da, db, IDESC_PV, !(first && kk == 0));
+                        bw::umma_bf16_ts(tmem_O + h * 64, tmem_S + 64 * s + 8 * kk, db, IDESC_PV, !(first && kk == 0));
                     }
                 }
-                bw::umma_commit(pv_done);
+                bw::umma_commit(pv_done + 8 * s);
                 bw::umma_commit(v_empty + 8 * s);
             };
             bool ok = bw::mbar_wait(q_full, 0, &g_status, 11) && bw::mbar_wait(k_full, 0, &g_status, 12);
@@ -188,13 +195,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int i = 0; i < n_tiles && ok; ++i) {
                 const int s = i & 1;
                 if (i + 1 < n_tiles) {
-                    // S of the next tile, while the softmax warps work on this one (its buffer was
-                    // read for the last time before P of tile i - 1 was signalled)
+                    // S of the next tile, while the softmax warps work on this one.  Its buffer holds
+                    // P of tile i - 1: the P V issued before reads it first (MMAs run in issue order)
                     if (!bw::mbar_wait(k_full + 8 * (s ^ 1), ((i + 1) >> 1) & 1, &g_status, 14)) break;
                     bw::tc_fence_after();
                     issue_qk(s ^ 1);
                 }
-                if (!bw::mbar_wait(p_full, i & 1, &g_status, 13)) break;   // P(i) written, O rescaled
+                if (!bw::mbar_wait(p_full + 8 * s, (i >> 1) & 1, &g_status, 13)) break;   // P(i) written, O rescaled
                 if (!bw::mbar_wait(v_full + 8 * s, (i >> 1) & 1, &g_status, 20)) break;
                 bw::tc_fence_after();
                 issue_pv(s, i == 0);
@@ -208,7 +215,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int lo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         float m = -INFINITY, l = 0.f;   // m: the reference of the exponents (at most 8 below the row maximum)
-        uint8_t* p_row = p_s + row * 128;
         bool ok = true;
 
         for (int i = 0; i < n_tiles; ++i) {
@@ -216,35 +222,28 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             bw::tc_fence_after();
             const int key0 = (t_lo + i) * BN;
             const bool need_mask = !row_ok || (key0 + BN - 1 > q_pos0) || (p.window > 0 && key0 < last_pos - p.window + 1);
-            float sv[BN];
-            float mx = -INFINITY;
+            // Two passes over the row of S in tensor memory, 32 keys at a time, so that the kernel stays
+            // within 128 registers (see the launch bounds).  First the maximum of the unscaled scores
+            // (scale > 0, so the maximum commutes with it; masked keys count as -inf).
+            const uint32_t s_row = tmem_S + 64 * (i & 1) + lane_base;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int h = 0; h < 2; ++h) {
                 uint32_t v[32];
-                bw::tmem_ld_32x32(tmem_S + 64 * (i & 1) + lane_base + c0, v);
+                bw::tmem_ld_32x32(s_row + 32 * h, v);
                 bw::tmem_ld_wait();
                 if (need_mask) {   // one branch per half tile, not one per key
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
-                        const int kp = key0 + c0 + c;
-                        const float s = (!row_ok || kp > qpos || kp < lo) ? -INFINITY : __uint_as_float(v[c]) * p.scale_log2;
-                        sv[c0 + c] = s;
-                        mx = fmaxf(mx, s);
+                        const int kp = key0 + 32 * h + c;
+                        mx4[c & 3] = fmaxf(mx4[c & 3], (!row_ok || kp > qpos || kp < lo) ? -INFINITY : __uint_as_float(v[c]));
                     }
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const float s = __uint_as_float(v[c]) * p.scale_log2;
-                        sv[c0 + c] = s;
-                        mx = fmaxf(mx, s);
-                    }
+                    for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(v[c]));
                 }
             }
-            // P V of the tile before: P may be overwritten and O read once it is done
-            if (i > 0) {
-                if (!__all_sync(0xffffffffu, bw::mbar_wait(pv_done, (i - 1) & 1, &g_status, 17))) { ok = false; break; }
-                bw::tc_fence_after();
-            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             const bool grow = mx > m + 8.f;   // also the first finite maximum of a row (m is -inf until then)
             float factor = 1.f;
             if (grow) {
@@ -253,6 +252,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 m = mx;
             }
             if (i > 0 && __any_sync(0xffffffffu, grow)) {
+                // O may be read once the P V of the tile before is done (the P V of tile i - 3, the one
+                // before on that barrier, is: S of this tile was computed after the P V of tile i - 2)
+                if (!__all_sync(0xffffffffu, bw::mbar_wait(pv_done + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, &g_status, 17))) { ok = false; break; }
+                bw::tc_fence_after();
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     uint32_t v[32];
@@ -265,21 +268,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 bw::tmem_st_wait();
             }
             const float mu = m == -INFINITY ? 0.f : m;
-            // probabilities, rounded to bfloat16 into the swizzled P tile
-            float sum = 0.f;
+            // Then the probabilities 2^(s * scale - mu), rounded to bfloat16, over the row of S they came
+            // from: 32 scores (columns 32 h ..) become 16 columns (16 h ..), which have been read by then.
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 8) {
-                uint32_t packed[4];
+            for (int h = 0; h < 2; ++h) {
+                uint32_t v[32];
+                bw::tmem_ld_32x32(s_row + 32 * h, v);
+                bw::tmem_ld_wait();
+                if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < 8; c += 2) {
-                    const float p0 = fast_exp2(sv[c0 + c] - mu), p1 = fast_exp2(sv[c0 + c + 1] - mu);
-                    sum += p0 + p1;
+                    for (int c = 0; c < 32; ++c) {
+                        const int kp = key0 + 32 * h + c;
+                        if (!row_ok || kp > qpos || kp < lo) v[c] = 0xff800000u;   // -inf
+                    }
+                }
+                uint32_t packed[16];
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(v[c]), p.scale_log2, -mu));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), p.scale_log2, -mu));
+                    sum4[(c >> 1) & 3] += p0 + p1;
                     packed[c >> 1] = pack_bf16(p0, p1);
                 }
-                const int chunk = c0 >> 3;   // 16-byte chunk of 8 keys
-                *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                bw::tmem_st_32x16(s_row + 16 * h, packed);
             }
-            l += sum;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             // Values of keys that do not exist (past the request's length, or on a page the block
             // table no longer holds) are whatever the stand-in page contained: zero them, since a
             // probability of 0 times a stale NaN would still be NaN.  Rare: the last tile, a window's edge.
@@ -297,13 +311,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         *reinterpret_cast<uint4*>(vbase + (rem >> 3) * KV_SLICE + rk * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
                     }
                 }
+                bw::fence_proxy_async_smem();
             }
-            bw::fence_proxy_async_smem();
+            bw::tmem_st_wait();
             bw::tc_fence_before();
             __syncwarp();
-            if (lane == 0) bw::mbar_arrive(p_full);
+            if (lane == 0) bw::mbar_arrive(p_full + 8 * (i & 1));
         }
-        if (ok) ok = __all_sync(0xffffffffu, bw::mbar_wait(pv_done, (n_tiles - 1) & 1, &g_status, 18));
+        if (ok) ok = __all_sync(0xffffffffu, bw::mbar_wait(pv_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, &g_status, 18));
         if (ok) {
             bw::tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -377,7 +392,7 @@ BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_
                               const int* work, int n_items, int T, int nh, int nkv, int page_size, int num_pages,
                               int window, float scale, void* stream) {
     if (n_items <= 0) return 0;
-    if (!bw_attention_tc_supported(nh, nkv, page_size)) return BW_ERR_UNSUPPORTED;
+    if (!bw_attention_tc_supported(nh, nkv, page_size) || !(scale > 0.f)) return BW_ERR_UNSUPPORTED;
     if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) != 0) return BW_ERR_UNSUPPORTED;
     const int G = nh / nkv, tpt = BM / G;
     CUtensorMap tq, tk, tv;
@@ -408,6 +423,7 @@ BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_
     BW_LAUNCH_CHECK();
     return 0;
 }
+
 
 BW_EXPORT int bw_attention_tc_status() {
     int v = 0, zero = 0;
