@@ -236,12 +236,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         const int kp = key0 + 32 * h + c;
-                        mx4[c & 3] = fmaxf(mx4[c & 3], (!row_ok || kp > qpos || kp < lo) ? -INFINITY : __uint_as_float(v[c]));
+                        if (!row_ok || kp > qpos || kp < lo) v[c] = 0xff800000u;   // -inf
                     }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(v[c]));
                 }
+#pragma unroll
+                for (int c = 0; c < 32; c += 2)   // max(m, a, b): one three-input instruction where the hardware has it
+                    mx4[(c >> 1) & 3] = fmaxf(mx4[(c >> 1) & 3], fmaxf(__uint_as_float(v[c]), __uint_as_float(v[c + 1])));
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             const bool grow = mx > m + 8.f;   // also the first finite maximum of a row (m is -inf until then)
