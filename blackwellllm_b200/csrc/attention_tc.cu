@@ -8,10 +8,10 @@
 //     block table, the K and V tiles into 128-byte-swizzled shared memory (2 stages);
 //   * S = Q K^T: tcgen05.mma (M 128, N 64) into one of two TMEM buffers, so that S of the next tile
 //     is computed while the softmax warps work on this one;
-//   * four softmax warps, one thread per row (no shuffles), in two passes over the row of S with
-//     tcgen05.ld (32 keys at a time: the kernel stays within 128 registers): the maximum, then
-//     the probabilities 2^(s * scale - m) with running sum in float32, rounded to bfloat16 and
-//     written back with tcgen05.st over the first 32 columns of the S buffer they came from;
+//   * four softmax warps, one thread per row (no shuffles): tcgen05.ld of the row of S, mask,
+//     maximum, then the probabilities 2^(s * scale - m) with running sum in float32, rounded to
+//     bfloat16 pairs in the registers of the scores already used (the kernel stays within 128
+//     registers) and written back with tcgen05.st over the first 32 columns of the S buffer;
 //   * O += P V: tcgen05.mma with P read from tensor memory and V as an MN-major shared-memory
 //     operand (keys are its K dimension), accumulated in TMEM over all tiles.  P has the two
 //     buffers of S, so the softmax warps never wait for the P V of the tile before.  The
@@ -222,27 +222,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             bw::tc_fence_after();
             const int key0 = (t_lo + i) * BN;
             const bool need_mask = !row_ok || (key0 + BN - 1 > q_pos0) || (p.window > 0 && key0 < last_pos - p.window + 1);
-            // Two passes over the row of S in tensor memory, 32 keys at a time, so that the kernel stays
-            // within 128 registers (see the launch bounds).  First the maximum of the unscaled scores
-            // (scale > 0, so the maximum commutes with it; masked keys count as -inf).
+            // The row of S, unscaled (scale > 0, so the maximum commutes with it; masked keys become -inf).
+            // It stays in these 64 registers; the packed probabilities take the place of the first 32
+            // as they are made, so that the kernel stays within 128 registers (see the launch bounds).
             const uint32_t s_row = tmem_S + 64 * (i & 1) + lane_base;
+            uint32_t v[BN];
+            bw::tmem_ld_32x32(s_row, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+            bw::tmem_ld_32x32(s_row + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            bw::tmem_ld_wait();
+            if (need_mask) {   // one branch per tile, not one per key
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const int kp = key0 + c;
+                    if (!row_ok || kp > qpos || kp < lo) v[c] = 0xff800000u;   // -inf
+                }
+            }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t v[32];
-                bw::tmem_ld_32x32(s_row + 32 * h, v);
-                bw::tmem_ld_wait();
-                if (need_mask) {   // one branch per half tile, not one per key
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int kp = key0 + 32 * h + c;
-                        if (!row_ok || kp > qpos || kp < lo) v[c] = 0xff800000u;   // -inf
-                    }
-                }
-#pragma unroll
-                for (int c = 0; c < 32; c += 2)   // max(m, a, b): one three-input instruction where the hardware has it
-                    mx4[(c >> 1) & 3] = fmaxf(mx4[(c >> 1) & 3], fmaxf(__uint_as_float(v[c]), __uint_as_float(v[c + 1])));
-            }
+            for (int c = 0; c < BN; c += 2)   // max(m, a, b): one three-input instruction where the hardware has it
+                mx4[(c >> 1) & 3] = fmaxf(mx4[(c >> 1) & 3], fmaxf(__uint_as_float(v[c]), __uint_as_float(v[c + 1])));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             const bool grow = mx > m + 8.f;   // also the first finite maximum of a row (m is -inf until then)
             float factor = 1.f;
@@ -256,43 +254,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 // before on that barrier, is: S of this tile was computed after the P V of tile i - 2)
                 if (!__all_sync(0xffffffffu, bw::mbar_wait(pv_done + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, &g_status, 17))) { ok = false; break; }
                 bw::tc_fence_after();
-#pragma unroll
-                for (int c0 = 0; c0 < HD; c0 += 32) {
-                    uint32_t v[32];
-                    bw::tmem_ld_32x32(tmem_O + lane_base + c0, v);
+#pragma unroll 1
+                for (int c0 = 0; c0 < HD; c0 += 16) {   // rare: a rolled loop of small pieces, few registers
+                    uint32_t o[16];
+                    bw::tmem_ld_32x16(tmem_O + lane_base + c0, o);
                     bw::tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * factor);
-                    bw::tmem_st_32x32(tmem_O + lane_base + c0, v);
+                    for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+                    bw::tmem_st_32x16(tmem_O + lane_base + c0, o);
                 }
                 bw::tmem_st_wait();
             }
             const float mu = m == -INFINITY ? 0.f : m;
-            // Then the probabilities 2^(s * scale - mu), rounded to bfloat16, over the row of S they came
-            // from: 32 scores (columns 32 h ..) become 16 columns (16 h ..), which have been read by then.
+            // The probabilities 2^(s * scale - mu), rounded to bfloat16 pairs: pair c / 2 goes where score
+            // c / 2 was (already used), and the 32 pairs over the first 32 columns of the row of S.
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t v[32];
-                bw::tmem_ld_32x32(s_row + 32 * h, v);
-                bw::tmem_ld_wait();
-                if (need_mask) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int kp = key0 + 32 * h + c;
-                        if (!row_ok || kp > qpos || kp < lo) v[c] = 0xff800000u;   // -inf
-                    }
-                }
-                uint32_t packed[16];
-#pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(v[c]), p.scale_log2, -mu));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), p.scale_log2, -mu));
-                    sum4[(c >> 1) & 3] += p0 + p1;
-                    packed[c >> 1] = pack_bf16(p0, p1);
-                }
-                bw::tmem_st_32x16(s_row + 16 * h, packed);
+            for (int c = 0; c < BN; c += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(v[c]), p.scale_log2, -mu));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), p.scale_log2, -mu));
+                sum4[(c >> 1) & 3] += p0 + p1;
+                v[c >> 1] = pack_bf16(p0, p1);
             }
+            bw::tmem_st_32x32(s_row, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             // Values of keys that do not exist (past the request's length, or on a page the block
             // table no longer holds) are whatever the stand-in page contained: zero them, since a
