@@ -21,11 +21,11 @@ from typing import Dict, List, Mapping, Optional, Sequence, Union
 import torch
 
 from ..kernels import ops
-from ..sampling.params import SamplingParams, uniform
+from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
 from .engine import Engine, EngineError, EngineOptions
-from .scheduler import Request, Scheduler
+from .scheduler import Scheduler
 
 
 @dataclass
