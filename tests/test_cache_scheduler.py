@@ -301,6 +301,38 @@ def test_philox_stream():
     assert uniform(7, 3) == us[3] and uniform(8, 3) != us[3]
 
 
+def test_sampling_params_checks_and_penalty_window():
+    with pytest.raises(ValueError):
+        SamplingParams(temperature=-0.1)
+    with pytest.raises(ValueError):
+        SamplingParams(top_p=0.0)
+    with pytest.raises(ValueError):
+        SamplingParams(max_new_tokens=0)
+    with pytest.raises(ValueError):
+        SamplingParams(repetition_penalty=0.0)
+    with pytest.raises(ValueError):
+        SamplingParams(repetition_window=-1)
+    assert SamplingParams(temperature=0.0).greedy and SamplingParams(temperature=9e-6).greedy
+    assert not SamplingParams(temperature=0.1).greedy
+    gen = list(range(100))
+    assert SamplingParams().penalized(gen) == ()                                   # off by default
+    assert SamplingParams(repetition_penalty=1.0).penalized(gen) == ()             # <= 1 is off
+    assert list(SamplingParams(repetition_penalty=1.2).penalized(gen)) == gen[-64:]
+    assert list(SamplingParams(repetition_penalty=1.2, repetition_window=3).penalized(gen)) == [97, 98, 99]
+    assert list(SamplingParams(repetition_penalty=1.2, repetition_window=0).penalized(gen)) == gen
+    assert SamplingParams(repetition_penalty=1.2).penalized([]) == ()
+
+
+def test_request_span_is_a_slice_of_prompt_plus_generated():
+    from blackwellllm_b200.engine.scheduler import Request
+    r = Request(0, [1, 2, 3, 4], SamplingParams(), 0, generated=[10, 11, 12])
+    whole = r.tokens
+    assert whole == [1, 2, 3, 4, 10, 11, 12]
+    for start in range(len(whole) + 1):
+        for n in range(len(whole) - start + 1):
+            assert r.span(start, n) == whole[start:start + n], (start, n)
+
+
 # ---------------------------------------------------------------------------------------------
 # The host runtime's packed step against the same step put together call by call
 
