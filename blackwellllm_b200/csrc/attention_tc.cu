@@ -42,7 +42,7 @@ constexpr int Q_BYTES = NS * Q_SLICE, KV_BYTES = NS * KV_SLICE;
 constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + 16 * 8 + 16;   // 2 CTAs per SM at head size 128
 constexpr uint32_t TMEM_COLS = (128 + HD) <= 256 ? 256 : 512;   // S (two buffers of 64 columns), then O
 constexpr uint32_t IDESC_QK = bw::umma_idesc_bf16(BM, BN, false);
-constexpr uint32_t IDESC_PV = bw::umma_idesc_bf16(BM, 64, true);
+constexpr uint32_t IDESC_PV = bw::umma_idesc_bf16(BM, HD, true);   // all channels in one product
 
 __device__ int g_status = 0;
 
@@ -178,14 +178,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 bw::umma_commit(k_empty + 8 * s);
             };
             auto issue_pv = [&](int s, bool first) {   // P in the first 32 columns of S buffer s, values of stage s
+                // one product per 16 keys over all HD channels: the operand's 64-channel slices lie
+                // KV_SLICE bytes apart (the descriptor's leading byte offset)
 #pragma unroll
-                for (int h = 0; h < NS; ++h) {
-#pragma unroll
-                    for (int kk = 0; kk < BN / 16; ++kk) {
-                        const uint64_t db = bw::umma_smem_desc_mn_sw128(bw::smem_u32(v_s + s * KV_BYTES + h * KV_SLICE), KV_SLICE)
-                                            + (uint64_t)kk * (2048 >> 4);   // 16 keys = two 8-row groups
-                        bw::umma_bf16_ts(tmem_O + h * 64, tmem_S + 64 * s + 8 * kk, db, IDESC_PV, !(first && kk == 0));
-                    }
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint64_t db = bw::umma_smem_desc_mn_sw128(bw::smem_u32(v_s + s * KV_BYTES), KV_SLICE)
+                                        + (uint64_t)kk * (2048 >> 4);   // 16 keys = two 8-row groups
+                    bw::umma_bf16_ts(tmem_O, tmem_S + 64 * s + 8 * kk, db, IDESC_PV, !(first && kk == 0));
                 }
                 bw::umma_commit(pv_done + 8 * s);
                 bw::umma_commit(v_empty + 8 * s);
