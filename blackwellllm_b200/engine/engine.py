@@ -14,10 +14,8 @@ src/core/engine_prefill_coordinator.cpp:160-169).
 """
 from __future__ import annotations
 
-import json
-import os
 from dataclasses import dataclass
-from typing import Dict, List, Mapping, Optional, Sequence
+from typing import Dict, Mapping, Optional, Sequence
 
 import numpy as np
 import torch
@@ -70,7 +68,6 @@ class Engine:
         self.device = torch.device(options.device)
         self.dtype = _DTYPES[options.dtype]
         requests = model.cache_requests()
-        paged = [r for r in requests if isinstance(r, PagedKVRequest)]
         num_pages = self._decide_num_pages(options, requests)
         self.cache = CacheManager(requests, options.page_size, num_pages, options.max_requests,
                                   dtype=self.dtype, device=self.device)
@@ -80,7 +77,6 @@ class Engine:
         self._graph_width = -(-longest // options.page_size)
         self.steps_run = 0
         self.tokens_run = 0
-        del paged
 
     # ------------------------------------------------------------------ construction
     @staticmethod

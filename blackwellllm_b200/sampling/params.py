@@ -13,7 +13,7 @@ multiplied when not, before temperature, nucleus or argmax) is a parameter too.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional, Sequence, Tuple
 
 _M0, _M1 = 0xD2511F53, 0xCD9E8D57

@@ -75,7 +75,7 @@ def test_8b_shape_every_way_of_cutting(weights, case, dtype):
 def test_rope_scaling_at_far_positions():
     """llama3 scaling and theta 500000 at positions up to 16,640 (where float32 angles are coarse):
     rotated queries and keys of the engine's kernel against the plain rotation."""
-    from blackwellllm_b200.config.specs import Llama3RopeScaling, RopeSpec
+    from blackwellllm_b200.config.specs import Llama3RopeScaling
     from blackwellllm_b200.kernels import ops
     from blackwellllm_b200.parts.rope import rotary_inv_freq
     from plain_model import plain_inv_freq, plain_rope

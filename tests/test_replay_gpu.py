@@ -3,7 +3,6 @@ last 32 tokens one by one, in portions of changing size, and mixed with other
 requests in a pool so small that pages are used again; in 32-bit and in bfloat16;
 on tiny configurations that differ in every size and option."""
 import pytest
-import torch
 
 import replay
 import tiny

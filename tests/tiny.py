@@ -3,7 +3,6 @@ size and option: heads and groups, sizes that are no power of two, layers,
 vocabulary, the norms' eps, rope base and scaling, the rotated span of a head,
 bias, tied head."""
 import os
-import tempfile
 
 import torch
 
