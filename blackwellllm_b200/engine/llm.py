@@ -233,6 +233,8 @@ class BlackwellEngine:
                                        [len(r.generated) for r in samplers], [r.generated for r in samplers])
             sampled = {r.rid: t for r, t in zip(samplers, toks)}
         done = self.scheduler.commit(plan, sampled)
+        for r in done:   # handed to the caller here: a long-lived engine keeps no finished request
+            self.scheduler.finished.pop(r.rid, None)
         return [GenerationResult(r.rid, r.prompt, r.generated, r.finish_reason, r.preemptions) for r in done]
 
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
