@@ -505,40 +505,36 @@ _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_vo
 _TARGET_CTAS = 148 * 4
 
 
-def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128, rows_tile: int = 64,
-                   page_size: int = 16):
-    """Work lists of the tensor-core attention for this batch and group size, made
-    once per step and shared by all layers: segments of more than 16 stacked rows
-    (tokens x heads of a group) are cut into 64-row tiles; the others (decode tokens)
-    are cut into key slices so that the GPU is filled.  With ``batch.static_bound``
-    (graph replay) the number of slices depends on that bound, not on the lengths."""
-    key = ("attn_work", G, nkv, window, hd, rows_tile, page_size)
-    cached = batch.static_extras.get(key)
-    if cached is not None:
-        return cached
+def plan_attention_work(q_len, q_start, kv_len, G: int, nkv: int, window: Optional[int], hd: int = 128,
+                        rows_tile: int = 64, page_size: int = 16, static_bound: Optional[int] = None):
+    """The work lists of the tensor-core attention as plain lists (host arithmetic only):
+    ``rows`` items (request, first token, 0, 0) for segments of more than 16 stacked rows (tokens x
+    heads of a group), cut into tiles of ``rows_tile`` rows and ordered longest first; ``keys`` items
+    (request, slice, slices of the request, first slot of its partial results) for the others (decode
+    tokens), cut into key slices so that the GPU is filled; ``merge`` items (request, 0, slices, first
+    slot) for requests with more than one slice; and the number of partial-result slots."""
     tpt = rows_tile // G   # tokens of one tile of stacked rows
     rows_items, keys_items, merge_items = [], [], []
-    small = [r for r in range(batch.R) if batch.h_q_len[r] * G <= 16]
+    n_small = sum(1 for n in q_len if n * G <= 16)
     # CTAs of the key-slice kernel that fit on the GPU at once (shared memory bound)
     if hd % 64 == 0 and page_size in (8, 16, 32, 64):   # the TMA-fed kernel: 2 stages of unpadded tiles
         smem = 2 * 2 * 64 * hd * 2 + 16 * (hd * 2 + 16) + 2048
     else:
         smem = (16 + 4 * 64) * (hd * 2 + 16)
     slots = 148 * max(1, min(8, (227 * 1024) // (smem + 1024)))
-    heads = max(1, len(small) * nkv)
+    heads = max(1, n_small * nkv)
     if heads <= slots:
         want = slots // heads            # one full wave: all slices run side by side, no tail
     else:
         want = -(-4 * slots // heads)    # many short CTAs: at least four waves smooth the tail
     total_slices = 0
-    for r in range(batch.R):
-        q_len = batch.h_q_len[r]
-        if q_len * G > 16:
-            rows_items += [(r, t0, 0, 0) for t0 in range(0, q_len, tpt)]
+    for r, n_q in enumerate(q_len):
+        if n_q * G > 16:
+            rows_items += [(r, t0, 0, 0) for t0 in range(0, n_q, tpt)]
             continue
-        span = batch.static_bound or batch.h_kv_len[r]
+        span = static_bound or kv_len[r]
         if window:
-            span = min(span, window + q_len)
+            span = min(span, window + n_q)
         tiles = -(-span // 64)
         n = max(1, min(want, tiles // 2, 64))
         keys_items += [(r, s, n, total_slices) for s in range(n)]
@@ -546,7 +542,23 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
             merge_items.append((r, 0, n, total_slices))
         total_slices += n
     # the tiles with the most keys to walk (the latest tokens) go first, so the last wave is light
-    rows_items.sort(key=lambda it: -(batch.h_q_start[it[0]] + it[1]))
+    rows_items.sort(key=lambda it: -(q_start[it[0]] + it[1]))
+    return rows_items, keys_items, merge_items, total_slices
+
+
+def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128, rows_tile: int = 64,
+                   page_size: int = 16):
+    """The work lists of :func:`plan_attention_work` for this batch and group size on the device,
+    made once per step and shared by all layers.  With ``batch.static_bound`` (graph replay) the
+    number of key slices depends on that bound, not on the lengths."""
+    key = ("attn_work", G, nkv, window, hd, rows_tile, page_size)
+    cached = batch.static_extras.get(key)
+    if cached is not None:
+        return cached
+    R = batch.R
+    rows_items, keys_items, merge_items, total_slices = plan_attention_work(
+        batch.h_q_len[:R], batch.h_q_start[:R], batch.h_kv_len[:R], G, nkv, window, hd, rows_tile, page_size,
+        batch.static_bound)
     dev = batch.token_ids.device
 
     def up(items):
