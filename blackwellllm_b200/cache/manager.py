@@ -269,6 +269,13 @@ class CacheManager:
         if rc < 0:
             raise AssertionError(f"free_request({rid!r}): code {rc}: {_INVARIANTS.get(rc, 'bad request')}")
 
+    def num_blocks(self, rid, group: int) -> int:
+        """Entries of the block table of (request, group), released ones included."""
+        n = native().bwh_num_blocks(self._h, self._handles[rid], group)
+        if n < 0:
+            raise ValueError(f"no group {group}")
+        return n
+
     def block_row(self, rid, group: int) -> np.ndarray:
         """The block table of (request, group): int32 page ids, -1 where a window gave the page back."""
         h = self._handles[rid]

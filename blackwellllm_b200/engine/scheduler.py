@@ -151,7 +151,7 @@ class Scheduler:
         """Largest m <= n whose pages fit in ``free``."""
         ps = self.cache.page_size
         length = self.cache.length(req.rid) if self.cache.has(req.rid) else 0
-        have = [len(self.cache.block_table(req.rid, g)) for g in range(len(free))] if self.cache.has(req.rid) \
+        have = [self.cache.num_blocks(req.rid, g) for g in range(len(free))] if self.cache.has(req.rid) \
             else [0] * len(free)
         cap = min((h + f) * ps - length for h, f in zip(have, free)) if free else n
         return max(0, min(n, cap))
