@@ -41,14 +41,13 @@ class Sampler:
             return
         host = torch.empty((total + R + 1,), dtype=torch.int32, pin_memory=True)
         pen = torch.empty((R,), dtype=torch.float32, pin_memory=True)
-        at = 0
-        for r, a in enumerate(acts):
-            host[total + r] = at
+        ids, begin = host.numpy(), [0]
+        for a in acts:
             if a:
-                host[at:at + len(a)] = torch.tensor(a, dtype=torch.int32)
-            at += len(a)
-            pen[r] = params[r].repetition_penalty if a else 1.0
-        host[total + R] = at
+                ids[begin[-1]:begin[-1] + len(a)] = a
+            begin.append(begin[-1] + len(a))
+        ids[total:] = begin   # where each row's ids begin, and the end of the last
+        pen.numpy()[:] = [p.repetition_penalty if a else 1.0 for p, a in zip(params, acts)]
         dev = host.to(self.device, non_blocking=True)
         ops.repetition_penalty(logits, dev[:total], dev[total:], pen.to(self.device, non_blocking=True))
 
@@ -61,9 +60,9 @@ class Sampler:
         if all(p.greedy for p in params):
             return ops.sample(logits, None, None, None)
         host = torch.empty((3, R), dtype=torch.float32, pin_memory=True)
-        for r, p in enumerate(params):
-            host[0, r] = 0.0 if p.greedy else p.temperature
-            host[1, r] = p.top_p
-            host[2, r] = 0.0 if p.greedy else uniform(seeds[r], draw_index[r])
+        rows = host.numpy()   # filled row by row: one assignment each instead of one per request
+        rows[0] = [0.0 if p.greedy else p.temperature for p in params]
+        rows[1] = [p.top_p for p in params]
+        rows[2] = [0.0 if p.greedy else uniform(seeds[r], draw_index[r]) for r, p in enumerate(params)]
         dev = host.to(self.device, non_blocking=True)
         return ops.sample(logits, dev[0], dev[1], dev[2])
