@@ -16,6 +16,7 @@ import struct
 from dataclasses import dataclass
 from typing import Dict, Iterable, Mapping, Tuple
 
+import numpy as np
 import torch
 
 _DTYPES = {
@@ -121,10 +122,11 @@ class TensorFiles:
         mm = self._maps[ent.path][1]
         if ent.nbytes == 0:
             return torch.empty(ent.shape, dtype=ent.dtype)
-        buf = bytearray(mm[ent.begin:ent.begin + ent.nbytes])
-        if len(buf) != ent.nbytes:
+        if ent.begin + ent.nbytes > len(mm):
             raise SafetensorsError(f"{ent.path!r}: short read for tensor {ent.name!r}")
-        return torch.frombuffer(buf, dtype=ent.dtype).reshape(ent.shape)
+        out = torch.empty(ent.nbytes, dtype=torch.uint8)   # one copy, straight from the mapped pages
+        out.numpy()[:] = np.frombuffer(mm, dtype=np.uint8, count=ent.nbytes, offset=ent.begin)
+        return out.view(ent.dtype).reshape(ent.shape)
 
     def close(self):
         for f, mm in self._maps.values():
