@@ -154,7 +154,7 @@ def write_file(path: str, tensors: Mapping[str, torch.Tensor],
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"tensor {name!r}: dtype {t.dtype} cannot be stored")
-        raw = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [off, off + len(raw)]}
         off += len(raw)

@@ -180,3 +180,34 @@ def test_sharded_folder(tmp_path):
     write_file(str(tmp_path / "s2.safetensors"), {"y": b["y"], "x": a["x"]})
     with pytest.raises(SafetensorsError, match="more than one shard"):
         index_folder(str(tmp_path))
+
+
+def test_every_stored_type_and_odd_shapes_survive_the_file(tmp_path):
+    """Writer and reader on every type the container names here, a tensor without dimensions, an empty
+    one, and a file cut short after its header was written."""
+    from blackwellllm_b200.weights.safetensors_io import TensorFiles
+    ts = {"f32": torch.randn(3, 5), "bf16": torch.randn(7).to(torch.bfloat16), "f16": torch.randn(2, 2).half(),
+          "f64": torch.randn(4, dtype=torch.float64), "i64": torch.arange(5), "i32": torch.arange(6, dtype=torch.int32).reshape(2, 3),
+          "i16": torch.arange(3, dtype=torch.int16), "i8": torch.arange(-2, 2, dtype=torch.int8),
+          "u8": torch.arange(3, dtype=torch.uint8), "bool": torch.tensor([True, False, True]),
+          "scalar": torch.tensor(3.5), "empty": torch.empty(0, 4)}
+    path = str(tmp_path / "all.safetensors")
+    write_file(path, ts)
+    entries = read_header(path)
+    with TensorFiles() as files:
+        got = {n: files.read(e) for n, e in entries.items()}
+    assert set(got) == set(ts)
+    for n, t in ts.items():
+        assert got[n].dtype == t.dtype and got[n].shape == t.shape and torch.equal(got[n], t), n
+    got["f32"].zero_()                                   # a copy of its own: writable, the file is closed
+    with TensorFiles() as files:
+        assert torch.equal(files.read(entries["f32"]), ts["f32"])
+    # the file loses its tail after the header was read
+    size = os.path.getsize(path)
+    with open(path, "r+b") as f:
+        f.truncate(size - 8)
+    last = max(entries.values(), key=lambda e: e.begin + e.nbytes)
+    with TensorFiles() as files, pytest.raises(SafetensorsError, match="short read"):
+        files.read(last)
+    with pytest.raises(SafetensorsError, match="data_offsets"):
+        read_header(path)
