@@ -196,7 +196,9 @@ BWH_EXPORT int bwh_truncate(void* cache, int h, long long new_length) {
             return BWH_WINDOW_RELEASED;
     for (size_t gi = 0; gi < c->groups.size(); ++gi) {
         std::vector<int>& b = r->blocks[gi];
-        for (long long i = keep; i < (long long)b.size(); ++i)
+        // from the back, as the reference pops them (src/core/paging/paged_kv_cache.h:196-208): the page
+        // nearest to the kept prefix is the next to be handed out
+        for (long long i = (long long)b.size() - 1; i >= keep; --i)
             if (b[i] >= 0) { const int rc = free_pages_of(c->groups[gi], &b[i], 1); if (rc) return rc; }
         if ((long long)b.size() > keep) b.resize(keep);
         if (r->first_live[gi] > keep) r->first_live[gi] = (int)keep;
