@@ -20,6 +20,7 @@ from typing import Dict, List, Mapping, Optional, Sequence, Union
 
 import torch
 
+from ..config.registry import load_config, parse_config
 from ..kernels import ops
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
@@ -77,14 +78,16 @@ class BlackwellEngine:
                              max_context=rq.max_context_length, cuda_graphs=cuda_graphs)
         if (model is None) == (config is None):
             raise EngineError("give either a model folder or a config for random weights")
+        # the context is checked against the model before any weight is read
+        # (the reference's plan does the same, src/core/runtime_config.cpp:59-65)
+        mc = load_config(model) if model is not None else parse_config(config)
+        if mc.max_position_embeddings and rq.max_context_length > mc.max_position_embeddings:
+            raise EngineError(f"max_context_length {rq.max_context_length} exceeds the model's "
+                              f"max_position_embeddings {mc.max_position_embeddings}")
         if model is not None:
             self.engine = Engine.from_folder(model, options=opts)
         else:
             self.engine = Engine.from_config(config, seed=random_seed, std=random_std, options=opts)
-        mc = self.engine.config
-        if mc.max_position_embeddings and rq.max_context_length > mc.max_position_embeddings:
-            raise EngineError(f"max_context_length {rq.max_context_length} exceeds the model's "
-                              f"max_position_embeddings {mc.max_position_embeddings}")
         self.sampler = Sampler(self.engine.device)
         self.seed = seed
         self.chunk = chunk

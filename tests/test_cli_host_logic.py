@@ -138,3 +138,26 @@ def test_gen_protocol_caps_the_prompt_to_the_context(monkeypatch, capsys):
     # ctx - (max_new + 8) = 32 prompt tokens survive (main.cpp: the hard cap of a request)
     assert "prompt_tokens=32 gen_tokens=8 " in first and "trunc=1 prefill=loop>>>" in first
     assert sum(1 for c in e.calls if c[0] == "forward") == 32 + 8 and not any(c[0] == "prefill" for c in e.calls)
+
+
+def test_entry_point_refuses_before_anything_is_loaded(tmp_path):
+    """The request's checks of the reference's plan (src/core/runtime_config.cpp:53-65) come before any
+    weight is read or any device is asked for, so they show without a GPU."""
+    import json
+
+    import tiny
+    from blackwellllm_b200 import BlackwellEngine, EngineError, InferenceConfig
+    raw = dict(tiny.CONFIGS["llama"][0], max_position_embeddings=64)
+    with pytest.raises(EngineError, match="max_context_length must be > 0"):
+        BlackwellEngine(None, InferenceConfig(max_context_length=0), config=raw)
+    with pytest.raises(EngineError, match="max_batch_size >= 1"):
+        BlackwellEngine(None, InferenceConfig(max_batch_size=0), config=raw)
+    with pytest.raises(EngineError, match="either a model folder or a config"):
+        BlackwellEngine(None, InferenceConfig())
+    with pytest.raises(EngineError, match="either a model folder or a config"):
+        BlackwellEngine(str(tmp_path), InferenceConfig(), config=raw)
+    with pytest.raises(EngineError, match="exceeds the model's max_position_embeddings 64"):
+        BlackwellEngine(None, InferenceConfig(max_context_length=65), config=raw)
+    (tmp_path / "config.json").write_text(json.dumps(raw))               # a folder: the same check from its config.json
+    with pytest.raises(EngineError, match="exceeds the model's max_position_embeddings 64"):
+        BlackwellEngine(str(tmp_path), InferenceConfig(max_context_length=128))
