@@ -1,0 +1,123 @@
+"""The step function's host side without a GPU: what ``Engine.step`` checks, reserves, packs and
+gives back.  The model is a stand-in that runs no kernel: it records the batch it is handed and
+returns a logits row per wanted place that names the token and its position, so the test can see
+that the right tokens arrive at the right positions with the right block tables.  (The kernels
+behind the same call are covered by the GPU tests.)"""
+import contextlib
+
+import pytest
+import torch
+
+import tiny
+from blackwellllm_b200.cache.pages import OutOfPages
+from blackwellllm_b200.config.registry import parse_config
+from blackwellllm_b200.engine.engine import Engine, EngineError, EngineOptions, StepEntry
+from blackwellllm_b200.parts.base import FixedStateRequest, PagedKVRequest
+
+WINDOW = 24
+
+
+class StandInModel:
+    """Two cache groups (all keys; a window) and one fixed-size state, no arithmetic."""
+
+    def __init__(self, vocab):
+        self.vocab = vocab
+        self.blocks = []          # no mixer objects: nothing forbids a graph, graphs are switched off anyway
+        self.batches = []
+
+    def cache_requests(self):
+        return [PagedKVRequest(2, 16, None), PagedKVRequest(1, 16, WINDOW), FixedStateRequest((3,), torch.float32), None]
+
+    def forward(self, batch, views):
+        self.batches.append(batch)
+        rows = batch.logit_rows.tolist()
+        out = torch.zeros((len(rows), self.vocab), dtype=torch.float32)
+        for i, t in enumerate(rows):
+            out[i, 0] = float(batch.token_ids[t])
+            out[i, 1] = float(batch.positions[t])
+            out[i, 2] = float(batch.req_of_token[t])
+        return out
+
+
+@pytest.fixture
+def engine(monkeypatch):
+    # the step selects its CUDA device around the kernels; there is none here and the stand-in needs none
+    monkeypatch.setattr(torch.cuda, "device", lambda d: contextlib.nullcontext())
+    cfg = parse_config(tiny.CONFIGS["llama"][0])
+    model = StandInModel(cfg.vocab_size)
+    opts = EngineOptions(dtype="float32", page_size=8, num_pages=12, max_requests=3, max_batch_tokens=64,
+                         cuda_graphs=False, device="cpu")
+    return Engine(cfg, model, opts), model
+
+
+def test_a_mixed_step_arrives_whole(engine):
+    eng, model = engine
+    lg = eng.step([StepEntry("a", [5, 6, 7, 8, 9, 10, 11, 12, 13, 14], [0, 9]), StepEntry("b", [3, 4], [])])
+    assert lg[:, :3].tolist() == [[5, 0, 0], [14, 9, 0]]
+    lg = eng.step([StepEntry("b", [7], [0]), StepEntry("a", [1, 2, 3], [2]), StepEntry("c", [9, 9], [1])])
+    assert lg[:, :3].tolist() == [[7, 2, 0], [3, 12, 1], [9, 1, 2]]          # order of the entries and of want
+    b = model.batches[-1]
+    assert (b.T, b.R) == (6, 3) and b.cu_q.tolist() == [0, 1, 4, 6]
+    assert b.token_ids.tolist() == [7, 1, 2, 3, 9, 9] and b.positions.tolist() == [2, 10, 11, 12, 0, 1]
+    assert b.q_start.tolist() == [2, 10, 0] and b.kv_len.tolist() == [3, 13, 2] and b.rids == ["b", "a", "c"]
+    assert sorted(b.state_slot.tolist()) == [0, 1, 2]
+    for g in (0, 1):   # every request's block-table row, padded with -1, as the cache manager holds it
+        for r, rid in enumerate(b.rids):
+            row = b.block_tables[g][r].tolist()
+            held = eng.cache.block_table(rid, g)
+            assert row[:len(held)] == held and all(p == -1 for p in row[len(held):])
+    assert eng.steps_run == 2 and eng.tokens_run == 18
+    eng.cache.check_invariants()
+
+
+def test_the_window_gives_pages_back_after_the_step(engine):
+    eng, _ = engine
+    eng.step([StepEntry("a", list(range(40)), [39])])
+    assert eng.cache.block_table("a", 0) == [0, 1, 2, 3, 4]                   # all keys: 5 pages of 8
+    assert eng.cache.block_table("a", 1)[:2] == [-1, -1]                       # the window of 24 has passed 2 pages
+    assert eng.cache.free_pages() == [7, 9]
+    eng.end_request("a")
+    assert eng.cache.free_pages() == [12, 12] and not eng.has_request("a")
+
+
+def test_state_is_zeroed_when_a_slot_is_handed_out_again(engine):
+    eng, _ = engine
+    eng.step([StepEntry("a", [1], [])])
+    slot = eng.cache.slot("a")
+    eng.cache.views[2].state[slot] = 7.0
+    eng.end_request("a")
+    eng.step([StepEntry("b", [1], [])])
+    assert eng.cache.slot("b") == slot and eng.cache.views[2].state[slot].tolist() == [0.0, 0.0, 0.0]
+
+
+def test_refusals_change_nothing(engine):
+    eng, model = engine
+    eng.step([StepEntry("a", list(range(40)), [39])])       # 5 of the 12 pages of the first group
+    before = (eng.cache.free_pages(), eng.cache.length("a"), eng.cache.slots.num_free, len(model.batches))
+    bad = [
+        ([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])], EngineError, "twice"),
+        ([StepEntry("a", [], [])], EngineError, "at least one token"),
+        ([StepEntry("a", [1, 999], [0])], EngineError, "token id 999"),
+        ([StepEntry("a", [-1], [0])], EngineError, "token id -1"),
+        ([StepEntry("a", [1, 2], [2])], EngineError, "wanted place 2"),
+        ([StepEntry("n", [1], [-1])], EngineError, "wanted place -1"),
+        ([StepEntry("a", [1] * 65, [])], EngineError, "max_batch_tokens=64"),
+        ([StepEntry("a", [1], [0]), StepEntry("n", [1] * 63, [])], OutOfPages, "pages per group"),       # 1 + 8 pages, 7 are free
+        ([StepEntry("n1", [1], []), StepEntry("n2", [1], []), StepEntry("n3", [1], [])], OutOfPages, "request slots"),
+    ]
+    for entries, err, text in bad:
+        with pytest.raises(err, match=text):
+            eng.step(entries)
+        assert (eng.cache.free_pages(), eng.cache.length("a"), eng.cache.slots.num_free, len(model.batches)) == before
+        assert not any(eng.has_request(r) for r in ("n", "n1", "n2", "n3"))
+    eng.cache.check_invariants()
+    assert eng.step([]).shape == (0, eng.config.vocab_size)                   # an empty step is no step
+    assert eng.steps_run == 1
+
+
+def test_no_device_no_engine():
+    cfg = tiny.CONFIGS["llama"][0]
+    with pytest.raises(EngineError, match="no CPU path"):
+        Engine.from_config(cfg, device="cpu")
+    with pytest.raises(EngineError, match="dtype must be"):
+        Engine.from_config(cfg, dtype="float16")
