@@ -121,3 +121,125 @@ def test_no_device_no_engine():
         Engine.from_config(cfg, device="cpu")
     with pytest.raises(EngineError, match="dtype must be"):
         Engine.from_config(cfg, dtype="float16")
+
+
+# ---------------------------------------------------------------- the Python entry point above the step function
+class RuleModel(StandInModel):
+    """Logits that make greedy decoding follow a rule: after a token t at position p the best next
+    token is (t + p) % vocab."""
+
+    def cache_requests(self):
+        return [PagedKVRequest(2, 16, None)]
+
+    def forward(self, batch, views):
+        self.batches.append(batch)
+        rows = batch.logit_rows.tolist()
+        out = torch.zeros((len(rows), self.vocab), dtype=torch.float32)
+        for i, t in enumerate(rows):
+            out[i, (int(batch.token_ids[t]) + int(batch.positions[t])) % self.vocab] = 1.0
+        return out
+
+
+class ArgmaxSampler:
+    def __init__(self, device):
+        pass
+
+    def sample(self, logits, params, seeds, draw_index, generated=None):
+        assert all(p.greedy for p in params)
+        return logits.argmax(dim=1).tolist()
+
+
+def rule_continuation(prompt, n, vocab):
+    out, last, pos = [], prompt[-1], len(prompt) - 1
+    for _ in range(n):
+        last = (last + pos) % vocab
+        pos += 1
+        out.append(last)
+    return out
+
+
+@pytest.fixture
+def llm(monkeypatch):
+    import dataclasses
+
+    from blackwellllm_b200.engine import llm as llm_module
+    monkeypatch.setattr(torch.cuda, "device", lambda d: contextlib.nullcontext())
+    models = []
+
+    def from_config(raw, seed=0, std=0.02, options=None):
+        cfg = parse_config(raw)
+        models.append(RuleModel(cfg.vocab_size))
+        return Engine(cfg, models[-1], dataclasses.replace(options, device="cpu", cuda_graphs=False))
+    monkeypatch.setattr(llm_module.Engine, "from_config", staticmethod(from_config))
+    monkeypatch.setattr(llm_module, "Sampler", ArgmaxSampler)
+
+    def make(**kw):
+        from blackwellllm_b200 import BlackwellEngine, InferenceConfig
+        rq = InferenceConfig(max_context_length=kw.pop("ctx", 96), max_batch_size=kw.pop("batch", 3))
+        e = BlackwellEngine(None, rq, config=tiny.CONFIGS["llama"][0], page_size=8, **kw)
+        return e, models[-1]
+    return make
+
+
+def test_generate_batches_requests_and_returns_them_in_order(llm):
+    from blackwellllm_b200 import SamplingParams
+    e, model = llm(max_batch_tokens=16)
+    V = e.vocab_size
+    prompts = [[3, 4, 5], list(range(10, 40)), [7], [9, 8, 7, 6, 5, 4, 3, 2, 1, 0, 1, 2, 3, 4, 5, 6, 7]]
+    res = e.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True))
+    assert [r.prompt_token_ids for r in res] == prompts
+    for p, r in zip(prompts, res):
+        assert r.token_ids == rule_continuation(p, 6, V) and r.finish_reason == "limit"
+    assert all(b.T <= 16 for b in model.batches)                              # the token budget of a step
+    assert any(b.R > 1 and max(b.h_q_len) > 1 and min(b.h_q_len) == 1 for b in model.batches)   # portions beside decoded tokens
+    assert e.engine.cache.free_pages() == [3 * 12] and e.scheduler.finished == {} and not e.scheduler.has_work()
+    # one prompt, one SamplingParams per prompt, and the wrong number of them
+    one = e.generate([3, 4, 5], SamplingParams(temperature=0.0, max_new_tokens=2))
+    assert len(one) == 1 and one[0].token_ids == rule_continuation([3, 4, 5], 2, V)
+    with pytest.raises(EngineError, match="one SamplingParams per prompt"):
+        e.generate(prompts, [SamplingParams(temperature=0.0)])
+
+
+def test_generate_with_too_few_pages_preempts_and_still_follows_the_rule(llm):
+    from blackwellllm_b200 import SamplingParams
+    e, _ = llm(max_batch_tokens=32, num_pages=7, ctx=48)
+    V = e.vocab_size
+    prompts = [list(range(1, 18)), list(range(2, 20)), list(range(5, 15))]
+    res = e.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=14, ignore_eos=True))
+    for p, r in zip(prompts, res):
+        assert r.token_ids == rule_continuation(p, 14, V)
+    assert e.scheduler.stats.preemptions > 0 and sum(r.preemptions for r in res) == e.scheduler.stats.preemptions
+    assert e.engine.cache.free_pages() == [7]
+    e.engine.cache.check_invariants()
+
+
+def test_position_addressed_calls_reconcile_the_cache(llm):
+    from blackwellllm_b200 import DecodeRequest
+    e, model = llm(max_batch_tokens=8, batch=2)
+    V = e.vocab_size
+    ids = list(range(20, 41))                                                  # 21 tokens: three steps of at most 8
+    nxt = e.prefill(ids, 0, 0.0, 1.0, 0)
+    assert nxt == rule_continuation(ids, 1, V)[0] and [b.T for b in model.batches] == [8, 8, 5]
+    assert [len(b.logit_rows) for b in model.batches] == [0, 0, 1]            # logits only after the last token
+    nxt2 = e.forward(nxt, 21, 0.0, 1.0, 0)
+    assert [nxt, nxt2] == rule_continuation(ids, 2, V)
+    # an earlier position rewinds the sequence to it; a later one would leave a gap
+    again = e.forward(ids[10], 10, 0.0, 1.0, 0)
+    assert again == (ids[10] + 10) % V and e.engine.cache.length(("seq", 0)) == 11
+    with pytest.raises(EngineError, match="gap"):
+        e.forward(1, 13, 0.0, 1.0, 0)
+    with pytest.raises(EngineError, match="do not fit max_context_length"):
+        e.prefill([1] * 97, 0, 0.0, 1.0, 1)
+    # one token each of distinct sequences
+    out = e.forward_batch([DecodeRequest(0, 5, 11), DecodeRequest(1, 6, 0)])
+    assert out == [(5 + 11) % V, 6 % V]
+    with pytest.raises(EngineError, match="twice"):
+        e.forward_batch([DecodeRequest(0, 5, 12), DecodeRequest(0, 6, 13)])
+    with pytest.raises(EngineError, match="at least one request"):
+        e.forward_batch([])
+    e.rewind(0, 4)
+    assert e.engine.cache.length(("seq", 0)) == 4
+    with pytest.raises(EngineError, match="unknown sequence"):
+        e.rewind(5, 0)
+    e.release_sequence(0); e.reset_state(1); e.release_sequence(7)            # the last one never existed
+    assert e.engine.cache.live == [] and e.engine.cache.free_pages() == [2 * 12]
