@@ -53,6 +53,7 @@ def native():
                 "bwh_add_request": (ci, [vp]), "bwh_slot": (ci, [vp, ci]), "bwh_length": (ll, [vp, ci]),
                 "bwh_free_slots": (ci, [vp]), "bwh_free_pages": (ci, [vp, _c_int_p]),
                 "bwh_pages_needed": (ci, [vp, ci, ll, _c_int_p]), "bwh_append": (ll, [vp, ci, ll]),
+                "bwh_pages_needed_many": (ci, [vp, ci, vp, ll, _c_int_p]),
                 "bwh_release_passed": (ci, [vp, ci]), "bwh_truncate": (ci, [vp, ci, ll]),
                 "bwh_free_request": (ci, [vp, ci]), "bwh_num_blocks": (ci, [vp, ci, ci]),
                 "bwh_blocks": (ci, [vp, ci, ci, vp, ci]), "bwh_check": (ci, [vp]),
@@ -208,6 +209,13 @@ class CacheManager:
         """Pages each group must still hand out for the request to grow by ``n_new``."""
         if native().bwh_pages_needed(self._h, self._handles[rid], n_new, self._scratch) != 0:
             raise ValueError(f"request {rid!r} cannot grow by {n_new}")
+        return list(self._scratch[:len(self.groups)])
+
+    def pages_needed_many(self, rids, n_new: int) -> List[int]:
+        """Pages each group must still hand out for every one of the requests to grow by ``n_new``."""
+        hs = np.fromiter((self._handles[r] for r in rids), dtype=np.int32)
+        if native().bwh_pages_needed_many(self._h, len(hs), hs.ctypes.data, n_new, self._scratch) != 0:
+            raise ValueError(f"the requests cannot grow by {n_new}")
         return list(self._scratch[:len(self.groups)])
 
     def can_append(self, rid, n_new: int) -> bool:

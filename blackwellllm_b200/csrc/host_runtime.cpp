@@ -153,6 +153,19 @@ BWH_EXPORT int bwh_pages_needed(void* cache, int h, long long n_new, int* out) {
     return BWH_OK;
 }
 
+// The same for R requests that each grow by n_new tokens: the sums per group.
+BWH_EXPORT int bwh_pages_needed_many(void* cache, int R, const int* handles, long long n_new, int* out) {
+    Cache* c = (Cache*)cache;
+    if (R < 0 || n_new < 0) return BWH_BAD_ARG;
+    for (size_t g = 0; g < c->groups.size(); ++g) out[g] = 0;
+    for (int i = 0; i < R; ++i) {
+        Request* r = get(c, handles[i]);
+        if (!r) return BWH_BAD_ARG;
+        for (size_t g = 0; g < c->groups.size(); ++g) out[g] += pages_short(c, *r, (int)g, r->length + n_new);
+    }
+    return BWH_OK;
+}
+
 // Grows the request by n_new tokens: its old length, or BWH_OUT_OF_PAGES with nothing changed.
 BWH_EXPORT long long bwh_append(void* cache, int h, long long n_new) {
     Cache* c = (Cache*)cache;

@@ -184,9 +184,7 @@ class Scheduler:
         # 1. decodes, preempting the most recent admissions until their pages exist
         while True:
             decodes = [r for r in self.running if r.remaining == 1 and r.num_computed > 0]
-            need = [0] * n_groups
-            for r in decodes:
-                need = [a + b for a, b in zip(need, self._pages_for(r, 1))]
+            need = self.cache.pages_needed_many([r.rid for r in decodes], 1) if decodes else [0] * n_groups
             free = self.cache.free_pages()
             if all(n <= f for n, f in zip(need, free)) or not self.running:
                 break
