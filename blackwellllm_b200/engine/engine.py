@@ -161,17 +161,13 @@ class Engine:
         step's buffer are one call into the C++ host runtime."""
         cache = self.cache
         R = len(entries)
-        handles = np.empty(R, dtype=np.int32)
-        n_tok = np.empty(R, dtype=np.int32)
-        n_want = np.empty(R, dtype=np.int32)
-        seen = set()
-        for i, e in enumerate(entries):
-            if e.rid in seen:
-                raise EngineError(f"request {e.rid!r} appears twice in one step")
-            seen.add(e.rid)
-            handles[i] = cache.handle(e.rid)
-            n_tok[i] = len(e.tokens)
-            n_want[i] = len(e.want)
+        rids = [e.rid for e in entries]
+        if len(set(rids)) != R:
+            twice = next(r for i, r in enumerate(rids) if r in rids[:i])
+            raise EngineError(f"request {twice!r} appears twice in one step")
+        handles = np.fromiter(map(cache.handle, rids), dtype=np.int32, count=R)
+        n_tok = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=R)
+        n_want = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=R)
         T, W = int(n_tok.sum()), int(n_want.sum())
         if T == R:
             tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
@@ -214,7 +210,7 @@ class Engine:
                 raise EngineError("a request outgrew max_context: its block table no longer fits the graph")
             self._builder.send(host, int(total), into)
             return None
-        return self._builder.finish(host, T, R, W, widths, [e.rid for e in entries], into)
+        return self._builder.finish(host, T, R, W, widths, rids, into)
 
     def _explain(self, entries: Sequence[StepEntry], code: int) -> None:
         """Raises the error that the host runtime's code stands for, with the offending entry named."""
