@@ -243,3 +243,42 @@ def test_position_addressed_calls_reconcile_the_cache(llm):
         e.rewind(5, 0)
     e.release_sequence(0); e.reset_state(1); e.release_sequence(7)            # the last one never existed
     assert e.engine.cache.live == [] and e.engine.cache.free_pages() == [2 * 12]
+
+
+def test_sampler_uploads_what_the_kernels_expect(monkeypatch):
+    """The sampler's host side: the (temperature, top_p, uniform number) rows and the penalized ids with their
+    row boundaries, as the kernels receive them.  The kernels are stand-ins that record their arguments, and
+    pinned memory is ordinary memory here."""
+    import types
+
+    from blackwellllm_b200 import SamplingParams
+    from blackwellllm_b200.sampling import sampler as S
+    from blackwellllm_b200.sampling.params import uniform
+    seen = {}
+
+    def empty(*size, pin_memory=False, **kw):
+        return torch.empty(*size, **kw)
+    shim = types.SimpleNamespace(**{k: getattr(torch, k) for k in ("float32", "int32", "Tensor", "device", "tensor")}, empty=empty)
+    monkeypatch.setattr(S, "torch", shim)
+    monkeypatch.setattr(S.ops, "sample", lambda logits, t, p, u: seen.update(sample=(t, p, u)) or torch.zeros(logits.shape[0], dtype=torch.int32))
+    monkeypatch.setattr(S.ops, "repetition_penalty", lambda logits, ids, begin, pen: seen.update(pen=(ids, begin, pen)))
+    sm = S.Sampler(torch.device("cpu"))
+    logits = torch.zeros((4, 16))
+    params = [SamplingParams(temperature=0.0), SamplingParams(temperature=0.7, top_p=0.5),
+              SamplingParams(temperature=1.3, top_p=1.0, repetition_penalty=1.5, repetition_window=2),
+              SamplingParams(temperature=0.0, repetition_penalty=2.0, repetition_window=0)]
+    seeds, draws = [11, 12, 13, 14], [0, 5, 9, 2]
+    out = sm.sample(logits, params, seeds, draws, [[1, 2], [3], [4, 5, 6], [7, 8, 9, 7]])
+    assert out == [0, 0, 0, 0]
+    t, p, u = seen["sample"]
+    assert t.tolist() == pytest.approx([0.0, 0.7, 1.3, 0.0]) and p.tolist() == pytest.approx([0.9, 0.5, 1.0, 0.9])
+    assert u.tolist() == pytest.approx([0.0, uniform(12, 5), uniform(13, 9), 0.0])     # greedy rows draw nothing
+    ids, begin, pen = seen["pen"]
+    assert ids.tolist() == [5, 6, 7, 8, 9, 7] and begin.tolist() == [0, 0, 0, 2, 6]     # window 2; window 0: everything emitted
+    assert pen.tolist() == pytest.approx([1.0, 1.0, 1.5, 2.0])
+    # all greedy, no penalty: nothing is uploaded
+    seen.clear()
+    sm.sample(logits[:2], [SamplingParams(temperature=0.0)] * 2, [1, 2], [0, 0], [[1], [2]])
+    assert seen == {"sample": (None, None, None)}
+    with pytest.raises(ValueError, match="one SamplingParams per logits row"):
+        sm.sample(logits, params[:2], seeds, draws)
