@@ -27,6 +27,11 @@
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<multiple of 64>"
 #endif
+// 1 (the default): the MMA warp waits for the P V that reads a buffer before it issues the Q K^T that
+// overwrites it.  0: it relies on tensor instructions of one thread running in issue order (measurement only).
+#ifndef ATTN_STRICT_ORDER
+#define ATTN_STRICT_ORDER 1
+#endif
 
 using bf16 = __nv_bfloat16;
 
@@ -195,8 +200,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 const int s = i & 1;
                 if (i + 1 < n_tiles) {
                     // S of the next tile, while the softmax warps work on this one.  Its buffer holds
-                    // P of tile i - 1: the P V issued before reads it first (MMAs run in issue order)
+                    // P of tile i - 1, which the P V issued before still reads as its operand: that
+                    // product must be complete before this one may overwrite the buffer (the order of
+                    // two tensor instructions is promised only when they write the same accumulator).
                     if (!bw::mbar_wait(k_full + 8 * (s ^ 1), ((i + 1) >> 1) & 1, &g_status, 14)) break;
+#if ATTN_STRICT_ORDER
+                    if (i >= 1 && !bw::mbar_wait(pv_done + 8 * (s ^ 1), ((i - 1) >> 1) & 1, &g_status, 22)) break;
+#endif
                     bw::tc_fence_after();
                     issue_qk(s ^ 1);
                 }

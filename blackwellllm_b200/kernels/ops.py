@@ -593,7 +593,7 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
         part_o = torch.empty((slices * nkv * 16, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((slices * nkv * 16, 2), dtype=torch.float32, device=q.device)
     if use_tc and n_rows:
-        tc = _fn("attention_tc", "bw_attention_tc", _ATTN_TC_ARGS, macros={"HEAD_DIM": hd})
+        tc = _fn("attention_tc", "bw_attention_tc", _ATTN_TC_ARGS, macros=attention_tc_macros(hd))
         _check(tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
                   _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, q.shape[0],
                   nh, nkv, page_size, num_pages, int(window or 0), float(scale), _stream()), "attention_tc")
@@ -618,6 +618,17 @@ def attention_tc_supports(hd: int, G: int, page_size: int) -> bool:
     if os.environ.get("BW_ATTN_TC", "1") == "0":
         return False
     return hd % 64 == 0 and hd <= 256 and G <= 128 and page_size in (8, 16, 32, 64)
+
+
+def attention_tc_macros(hd: int) -> dict:
+    """The build of the tcgen05 prompt attention for this head size.  BW_ATTN_RELAXED_ORDER=1 in the
+    environment selects the variant whose MMA warp does not wait for the P V product that reads a
+    buffer before it overwrites it (for measuring what the wait costs; never the default)."""
+    import os
+    macros = {"HEAD_DIM": hd}
+    if os.environ.get("BW_ATTN_RELAXED_ORDER", "0") == "1":
+        macros["ATTN_STRICT_ORDER"] = 0
+    return macros
 
 
 def attention_tc_status() -> int:

@@ -19,3 +19,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """bfloat16 is measured, not only bounded: the replay tests' agreement with the plain implementation."""
+    try:
+        import replay
+    except Exception:
+        return
+    if replay.REPORT:
+        terminalreporter.write_sep("-", "engine against the plain implementation")
+        for line in replay.REPORT:
+            terminalreporter.write_line(line)

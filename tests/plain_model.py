@@ -58,7 +58,7 @@ def plain_config(raw: dict) -> dict:
 
 def plain_embedding(table: torch.Tensor, ids: Sequence[int]) -> torch.Tensor:
     """x[t, :] = E[id_t, :], no scaling (src/kernels/embedding.cu:45-69)."""
-    return table[torch.as_tensor(list(ids), dtype=torch.long)]
+    return table[torch.as_tensor(list(ids), dtype=torch.long, device=table.device)]
 
 
 def plain_rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -95,6 +95,7 @@ def plain_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor)
     sine and cosine are taken in x's dtype.
     """
     rd = 2 * inv_freq.numel()
+    positions, inv_freq = positions.to(x.device), inv_freq.to(x.device)
     ang = (positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]).to(x.dtype)
     cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     a, b = x[..., : rd // 2], x[..., rd // 2: rd]
@@ -120,13 +121,38 @@ def plain_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     kk = k.repeat_interleave(g, dim=1)
     vv = v.repeat_interleave(g, dim=1)
     s = torch.einsum("thd,shd->hts", q, kk) * scale
-    i = torch.arange(T)
+    i = torch.arange(T, device=q.device)
     mask = i[None, :] <= i[:, None]
     if window is not None:
         mask &= i[None, :] > i[:, None] - window
     s = s.masked_fill(~mask[None], float("-inf"))
     p = torch.softmax(s, dim=-1)
     return torch.einsum("hts,shd->thd", p, vv)
+
+
+def plain_attention_tail(q_tail: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optional[int] = None,
+                         rows_at_once: int = 512) -> torch.Tensor:
+    """The same attention for the LAST ``len(q_tail)`` positions of a sequence only (the queries of a
+    prompt portion, or a decode token, over all keys before them), a few hundred rows at a time so that
+    long sequences fit in memory.  q_tail: [n, nh, hd]; k, v: [T, nkv, hd] -> [n, nh, hd]."""
+    n, nh, hd = q_tail.shape
+    T, nkv = k.shape[0], k.shape[1]
+    g = nh // nkv
+    start = T - n
+    out = torch.empty_like(q_tail)
+    key_pos = torch.arange(T, device=q_tail.device)
+    for a in range(0, n, rows_at_once):
+        b = min(n, a + rows_at_once)
+        last = start + b                      # keys [0, last) can be seen by these rows
+        qq = q_tail[a:b].view(b - a, nkv, g, hd)
+        s = torch.einsum("tkgd,skd->kgts", qq, k[:last]) * hd ** -0.5
+        qpos = start + torch.arange(a, b, device=q_tail.device)
+        mask = key_pos[None, :last] <= qpos[:, None]
+        if window is not None:
+            mask &= key_pos[None, :last] > qpos[:, None] - window
+        p = torch.softmax(s.masked_fill(~mask[None, None], float("-inf")), dim=-1)
+        out[a:b] = torch.einsum("kgts,skd->tkgd", p, v[:last]).reshape(b - a, nh, hd)
+    return out
 
 
 def plain_swiglu(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
@@ -168,20 +194,25 @@ def plain_layer(x, positions, W: Dict[str, torch.Tensor], i: int, c: dict, inv_f
 
 
 def plain_logits(raw_config: dict, weights: Dict[str, torch.Tensor], ids: Sequence[int],
-                 dtype=torch.float64) -> torch.Tensor:
+                 dtype=torch.float64, rows: Optional[Sequence[int]] = None, device=None) -> torch.Tensor:
     """Logits [T, V] at every position of one whole sequence
     (src/core/engine.cpp:921-1041: embedding, layers, final norm, lm_head; the
-    head is the embedding table when tied, engine.cpp:668-670)."""
+    head is the embedding table when tied, engine.cpp:668-670).  ``rows``: only
+    these positions' logits (the whole sequence is computed all the same; the
+    final norm and the head run on these rows).  ``device``: where torch does the
+    arithmetic (the weights are copied there); the result comes back to the CPU."""
     c = plain_config(raw_config)
-    W = {k: v.to(dtype) for k, v in weights.items()}
+    W = {k: v.to(device=device, dtype=dtype) for k, v in weights.items()}
     x = plain_embedding(W["model.embed_tokens.weight"], ids)
     positions = torch.arange(len(ids))
     inv_freq = plain_inv_freq(c["hd"], c["theta"], c["scaling"], c["rd"])
     for i in range(c["L"]):
         x = plain_layer(x, positions, W, i, c, inv_freq)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long, device=x.device)]
     x = plain_rmsnorm(x, W["model.norm.weight"], c["eps"])
     head = W["model.embed_tokens.weight"] if c["tie"] else W["lm_head.weight"]
-    return plain_linear(x, head)
+    return plain_linear(x, head).cpu()
 
 
 def plain_greedy(raw_config: dict, weights, prompt: Sequence[int], steps: int,

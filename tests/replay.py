@@ -138,17 +138,31 @@ def trace_mixed(requests, max_tokens, seed=0, max_live=4, decode_tail=9):
     return steps
 
 
-def compare(rows, plain, tol_rel):
+REPORT = []   # lines for the summary at the end of the run (conftest.py prints them)
+
+
+def compare(rows, plain, tol_rel, label=None, min_cosine=None):
     """rows: {(id, pos): tensor}; plain: {id: [T, V] tensor}.  Returns the worst
-    error relative to the request's largest logit and where it is."""
+    error relative to the request's largest logit and where it is.  With a ``label`` the
+    lowest cosine between a returned row and the plain row, and the share of rows whose
+    largest logit is at the same token, go into the run's summary."""
     worst = (0.0, None)
+    low_cos, same_top = 1.0, 0
     for (rid, p), row in rows.items():
         ref = plain[rid]
         scale = float(ref.abs().max())
-        err = float((row.double() - ref[p].double()).abs().max()) / scale
-        if err > worst[0]:
+        got, want = row.double(), ref[p].double()
+        err = float((got - want).abs().max()) / scale
+        if err > worst[0] or err != err:
             worst = (err, (rid, p))
+        low_cos = min(low_cos, float(torch.dot(got, want) / (got.norm() * want.norm())))
+        same_top += int(torch.argmax(got) == torch.argmax(want))
     missing = [(rid, p) for rid, ref in plain.items() for p in range(ref.shape[0]) if (rid, p) not in rows]
     assert not missing, f"positions never returned: {missing[:5]}"
+    if label is not None:
+        REPORT.append(f"{label}: worst error {worst[0]:.2e} of the logit scale (bound {tol_rel:.1e}), lowest cosine "
+                      f"{low_cos:.6f}, same top-1 token at {same_top} of {len(rows)} positions")
     assert worst[0] <= tol_rel, f"worst error {worst[0]:.3e} of the logit scale at {worst[1]} (bound {tol_rel})"
+    if min_cosine is not None:
+        assert low_cos >= min_cosine, f"cosine {low_cos} below {min_cosine}"
     return worst

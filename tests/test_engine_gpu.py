@@ -75,6 +75,35 @@ def test_long_decoding_and_first_tokens(folders, dtype):
     assert eng.graph_kernel_count(1) > 0      # the decode steps ran from the captured graph
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["llama", "qwen"])
+def test_one_wrong_page_in_one_layer_exceeds_the_logit_bound(folders, name, dtype):
+    """Negative control of the whole-model bound: after a prompt, ONE page of ONE layer's cache gets the
+    contents of another page (what a stale block-table entry would read there).  The next token's logits
+    must then miss the plain implementation by more than the bound that every parity test allows, and
+    stay within it when the page is put right again."""
+    from blackwellllm_b200 import Engine, StepEntry
+    raw, _, page = tiny.CONFIGS[name]
+    folder = folders[(name, dtype)]
+    W = load_plain_weights(folder)
+    ids = tiny.prompt(3 * page + 2, raw["vocab_size"], 77)
+    ref = plain_logits(raw, W, ids)
+    scale = float(ref.abs().max())
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=page, max_tokens=256, cuda_graphs=False)
+    eng.step([StepEntry("a", ids[:-1], [])])
+    pool = eng.cache.groups[0].pool                   # [entries (layers), 2, pages, kv heads, page, head]
+    table = eng.cache.block_table("a", 0)
+    layer = pool.shape[0] - 1
+    saved = pool[layer, :, table[1]].clone()
+    pool[layer, :, table[1]] = pool[layer, :, table[0]]
+    bad = eng.step([StepEntry("a", [ids[-1]], [0])])[0].double().cpu()
+    assert float((bad - ref[-1]).abs().max()) / scale > tiny.TOL[dtype], "the bound cannot see a wrong page"
+    eng.cache.truncate("a", len(ids) - 1)
+    pool[layer, :, table[1]] = saved
+    good = eng.step([StepEntry("a", [ids[-1]], [0])])[0].double().cpu()
+    assert float((good - ref[-1]).abs().max()) / scale <= tiny.TOL[dtype]
+
+
 def test_sampling_kernel_matches_the_cpu_twin():
     from blackwellllm_b200.kernels import ops
     from blackwellllm_b200.sampling.params import uniform

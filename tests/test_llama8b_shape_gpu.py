@@ -72,6 +72,77 @@ def test_8b_shape_every_way_of_cutting(weights, case, dtype):
     check(out[15:], "a", len(a) - 9)
 
 
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    """The same weights (same seed, same tensor order) as a model folder, stored in bfloat16; the 32-bit
+    replay converts them at load."""
+    from blackwellllm_b200.weights.random_init import write_random_model
+    return write_random_model(str(tmp_path_factory.mktemp("llama8b_shape")), RAW, seed=3, std=0.02, dtype="bfloat16")
+
+
+@pytest.fixture(scope="module")
+def replay_case(weights):
+    """Six requests of 40 to 200 tokens and their plain logits (float64 through torch on the GPU: the
+    vocabulary of 128,256 makes the CPU too slow for the suite's minutes)."""
+    lengths = [40, 200, 97, 130, 65, 150]
+    reqs = {f"r{i}": tiny.prompt(n, RAW["vocab_size"], 300 + i) for i, n in enumerate(lengths)}
+    with torch.no_grad():
+        plain = {rid: plain_logits(RAW, weights, ids, dtype=torch.float64, device="cuda:0") for rid, ids in reqs.items()}
+    torch.cuda.empty_cache()
+    return reqs, plain
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("family", ["mixed", "tail"])
+def test_8b_shape_replay_mixed_with_page_reuse_and_tail(folder, replay_case, dtype, family):
+    """bin/trace_run at the 8B shape: up to four live requests, portions of some beside decoded tokens of
+    others, in a pool of 512 tokens for requests that need 960 (pages are used again); and each request
+    with its last 32 tokens one by one."""
+    import replay
+    reqs, plain = replay_case
+    if family == "mixed":
+        max_tokens = 512
+        steps = replay.trace_mixed(reqs, max_tokens, seed=5)
+        assert max(len(s["entries"]) for s in steps) >= 3
+    else:
+        steps, max_tokens = replay.trace_tail(reqs)
+    rows = replay.run_trace(folder, dtype, steps, max_tokens, RAW["vocab_size"], page_size=16, timeout=900)
+    replay.compare(rows, plain, tiny.TOL[dtype], label=f"8B shape (2 layers) {dtype} {family}",
+                   min_cosine=tiny.MIN_COSINE[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_8b_shape_long_prompt_in_portions_then_decode_from_the_graph(weights, dtype):
+    """The benchmarked path at its lengths: a prompt of 4,200 tokens in portions of 2,048 + 2,048 + 104, then
+    32 tokens decoded one by one from the CUDA graph; logits at the edges of the portions and at every
+    decoded position against the plain implementation (computed once for the whole sequence, asked for
+    those rows only)."""
+    from blackwellllm_b200 import Engine, StepEntry
+    from blackwellllm_b200.kernels import ops
+    ids = tiny.prompt(4232, RAW["vocab_size"], 41)
+    cuts = [(0, 2048), (2048, 4096), (4096, 4200)]
+    wanted = {(0, 2048): [0, 1, 63, 64, 1000, 2047], (2048, 4096): [2048, 2049, 3000, 4095], (4096, 4200): [4096, 4199]}
+    rows = [p for c in cuts for p in wanted[c]] + list(range(4200, 4232))
+    with torch.no_grad():
+        ref = plain_logits(RAW, weights, ids, dtype=torch.float64, rows=rows, device="cuda:0")
+    torch.cuda.empty_cache()
+    ref_of = {p: ref[i] for i, p in enumerate(rows)}
+    scale = float(ref.abs().max())
+    eng = Engine.from_tensors(RAW, weights, dtype=dtype, page_size=16, max_tokens=4352, max_requests=2,
+                              max_batch_tokens=2048)
+    worst = 0.0
+    for a, b in cuts:
+        out = eng.step([StepEntry("a", ids[a:b], [p - a for p in wanted[(a, b)]])]).double().cpu()
+        for i, p in enumerate(wanted[(a, b)]):
+            worst = max(worst, float((out[i] - ref_of[p]).abs().max()) / scale)
+    for p in range(4200, 4232):
+        out = eng.step([StepEntry("a", [ids[p]], [0])])[0].double().cpu()
+        worst = max(worst, float((out - ref_of[p]).abs().max()) / scale)
+    assert eng.graph_kernel_count(1) > 0
+    assert worst <= tiny.TOL[dtype], worst
+    assert ops.gemm_tc_status() == 0 and ops.attention_tc_status() == 0
+
+
 def test_rope_scaling_at_far_positions():
     """llama3 scaling and theta 500000 at positions up to 16,640 (where float32 angles are coarse):
     rotated queries and keys of the engine's kernel against the plain rotation."""

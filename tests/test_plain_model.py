@@ -5,7 +5,7 @@ import math
 import torch
 
 import tiny
-from plain_model import (plain_attention, plain_config, plain_greedy, plain_inv_freq, plain_logits, plain_rmsnorm,
+from plain_model import (plain_attention, plain_attention_tail, plain_config, plain_greedy, plain_inv_freq, plain_logits, plain_rmsnorm,
                          plain_rope, plain_swiglu)
 from plain_sampling import plain_log_prob, plain_repetition_penalty, plain_sample
 
@@ -59,6 +59,24 @@ def test_attention_causal_gqa_and_window():
     w3 = plain_attention(q, k, v, window=3)
     s3 = (k[2:5, 0] @ q[4, 0]) * hd ** -0.5
     assert torch.allclose(w3[4, 0], torch.softmax(s3, 0) @ v[2:5, 0])
+
+
+def test_attention_tail_is_the_tail_of_the_whole():
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(70, n, 8, generator=g, dtype=torch.float64) for n in (6, 2, 2))
+    for window in (None, 9):
+        whole = plain_attention(q, k, v, window=window)
+        for n in (1, 13, 70):
+            tail = plain_attention_tail(q[70 - n:], k, v, window=window, rows_at_once=5)
+            assert float((tail - whole[70 - n:]).abs().max()) < 1e-12
+    rows = plain_logits(tiny.TINY_QWEN, _tiny_weights(), list(range(9)), rows=[8, 2])
+    full = plain_logits(tiny.TINY_QWEN, _tiny_weights(), list(range(9)))
+    assert float((rows - full[[8, 2]]).abs().max()) < 1e-12
+
+
+def _tiny_weights():
+    from blackwellllm_b200.weights.random_init import model_param_specs, random_tensors
+    return random_tensors(model_param_specs(tiny.TINY_QWEN), seed=1, std=0.05, bias_std=0.1, dtype=torch.float32)
 
 
 def test_swiglu_by_hand():

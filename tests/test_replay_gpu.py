@@ -51,7 +51,7 @@ def test_replay(folders, name, dtype, family):
         steps = replay.trace_mixed(reqs, max_tokens, seed=3)
         assert max(len(s["entries"]) for s in steps) >= 3
     rows = replay.run_trace(folder, dtype, steps, max_tokens, raw["vocab_size"], page_size=page)
-    replay.compare(rows, plain, tiny.TOL[dtype])
+    replay.compare(rows, plain, tiny.TOL[dtype], label=f"{name} {dtype} {family}", min_cosine=tiny.MIN_COSINE[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -67,4 +67,7 @@ def scale_of(ref: torch.Tensor) -> float:
 
 
 # tolerances, relative to the largest logit magnitude of the compared rows
-TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+# (bfloat16: the worst measured over all configurations and ways of cutting is 7e-3; a single wrong page
+# in one layer of a tiny model moves the logits by more than this bound: tests/test_engine_gpu.py)
+TOL = {"float32": 1e-4, "bfloat16": 1.5e-2}
+MIN_COSINE = {"float32": 0.999999, "bfloat16": 0.999}
