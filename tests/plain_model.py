@@ -7,8 +7,10 @@ checkpoint names.
 
 This file rests on the reference's formulas (cited per function as
 file:line within fxslava/BlackwellLLM).  The reference's whole model needs a GPU
-and cannot run here; its CPU kernels (tests/common/cpu_reference.h) can, and
-``tests/golden/`` holds their outputs for the part-level comparison in
+and cannot run here; its CPU kernels (tests/common/cpu_reference.h) and its
+llama3 frequency rescaling (src/kernels/rope.cuh) can, and ``tests/golden/``
+holds their outputs: part by part, and composed into one whole tiny decoder in
+the order of the reference's layer loop, for the comparisons in
 ``test_plain_vs_reference_cpu.py``.  Where the reference rounds intermediate
 values to the bfloat16 grid to mimic a bfloat16 PyTorch run (rmsnorm.cu:133-138,
 swiglu.cu:23-34), this implementation does not: it is the exact arithmetic.
