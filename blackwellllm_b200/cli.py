@@ -57,6 +57,8 @@ def build_parser() -> argparse.ArgumentParser:
                     help="> 1 makes tokens already generated less likely (with --prompt-ids; default off)")
     ap.add_argument("--prompt-ids", default=None, help="comma-separated token ids: generate once and exit")
     ap.add_argument("--stats", action="store_true", help="print timing and scheduler counters")
+    ap.add_argument("--ignore-unexpected-tensors", action="store_true",
+                    help="pass over tensors of the checkpoint that the model does not use (default: an error)")
     return ap
 
 
@@ -106,7 +108,7 @@ def make_engine(args):
     model = args.model or args.model_pos
     if not model:
         raise SystemExit("give --model DIR (or --config JSON --random-weights)")
-    return BlackwellEngine(model, req, **kw)
+    return BlackwellEngine(model, req, ignore_unexpected=args.ignore_unexpected_tensors, **kw)
 
 
 def generate_once(engine, ids: List[int], max_new: int, temperature: float, top_p: float,

@@ -3,10 +3,12 @@
 ``register_architecture(name, parse)`` stores ``parse(raw_json) -> ModelConfig``.
 ``load_config`` reads ``config.json`` and dispatches on ``architectures[0]``,
 falling back to ``model_type`` (the reference keys on ``model_type`` strings
-only: src/core/config.cpp:81,226-227).
+only: src/core/config.cpp:81,226-227); end-of-sequence ids that a
+``generation_config.json`` in the same folder lists are added to config.json's.
 """
 from __future__ import annotations
 
+import dataclasses
 import json
 import os
 from typing import Any, Callable, Dict, Mapping
@@ -64,4 +66,30 @@ def load_config(model_dir: str) -> ModelConfig:
             raise ConfigError(f"{path}: not valid JSON: {e}") from e
     if not isinstance(raw, dict):
         raise ConfigError(f"{path}: top level must be an object")
-    return parse_config(raw)
+    cfg = parse_config(raw)
+    extra = _generation_eos(model_dir)
+    if extra:
+        merged = tuple(dict.fromkeys(tuple(extra) + tuple(cfg.eos_token_ids)))
+        cfg = dataclasses.replace(cfg, eos_token_ids=merged)
+    return cfg
+
+
+def _generation_eos(model_dir: str) -> tuple:
+    """End-of-sequence ids of ``generation_config.json`` beside config.json, if that file is there
+    (a checkpoint may list several there and only one, or none, in config.json).  They come first,
+    then those of config.json that are not among them."""
+    path = os.path.join(model_dir, "generation_config.json")
+    if not os.path.isfile(path):
+        return ()
+    with open(path, "r", encoding="utf-8") as f:
+        try:
+            gen = json.load(f)
+        except json.JSONDecodeError as e:
+            raise ConfigError(f"{path}: not valid JSON: {e}") from e
+    eos = gen.get("eos_token_id") if isinstance(gen, dict) else None
+    if eos is None:
+        return ()
+    ids = [eos] if isinstance(eos, int) and not isinstance(eos, bool) else eos
+    if not isinstance(ids, (list, tuple)) or not all(isinstance(i, int) and not isinstance(i, bool) and i >= 0 for i in ids):
+        raise ConfigError(f"{path}: 'eos_token_id' must be a non-negative integer or a list of them, got {eos!r}")
+    return tuple(ids)

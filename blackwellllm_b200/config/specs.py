@@ -120,6 +120,11 @@ class ModelConfig:
     embed_name: str = "model.embed_tokens.weight"
     final_norm_prefix: str = "model.norm."
     head_name: str = "lm_head.weight"
+    # what a decoder may do besides its blocks (all off by default): the embedding rows times a
+    # constant, the logits times a constant, and a soft cap  cap * tanh(logits / cap)
+    embedding_multiplier: float = 1.0
+    logit_scale: float = 1.0
+    logit_softcap: Optional[float] = None
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
     stored_dtype: str = "bfloat16"

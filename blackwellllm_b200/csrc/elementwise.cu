@@ -11,7 +11,7 @@ namespace {
 // ---------------------------------------------------------------- embedding
 template <typename WT>
 __global__ void embed_gather_kernel(const WT* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int H, int V) {
+                                    float* __restrict__ out, int H, int V, float scale) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     const int t = blockIdx.x;
@@ -23,7 +23,7 @@ __global__ void embed_gather_kernel(const WT* __restrict__ table, const int* __r
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int c = c0 + k * blockDim.x + threadIdx.x;
-        if (c < H) o[c] = bw::to_f32(row[c]);
+        if (c < H) o[c] = bw::to_f32(row[c]) * scale;   // scale 1: the stored value
     }
 }
 
@@ -204,19 +204,42 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
     }
 }
 
+// ---------------------------------------------------------------- logits
+// In place: x * scale, then cap * tanh(x / cap) when cap > 0 (a model's logit multiplier and soft cap).
+__global__ void logit_transform_kernel(float* __restrict__ x, long long n, float scale, float cap) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float v = x[i] * scale;
+        if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+        x[i] = v;
+    }
+}
+
 template <typename T> const T* cp(const void* p) { return reinterpret_cast<const T*>(p); }
 template <typename T> T* mp(void* p) { return reinterpret_cast<T*>(p); }
 
 }  // namespace
 
+BW_EXPORT int bw_logit_transform(float* logits, long long n, float scale, float cap, void* stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    const long long blocks = (n + threads - 1) / threads;
+    bw::launch(logit_transform_kernel, dim3((unsigned)(blocks < 148 * 16 ? blocks : 148 * 16)), dim3(threads), 0,
+               (cudaStream_t)stream, logits, n, scale, cap);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
 BW_EXPORT int bw_embed_gather(const void* table, int table_type, const int* ids, float* out,
-                              int T, int H, int V, void* stream) {
+                              int T, int H, int V, float scale, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
     const dim3 grid(T, (H + threads * 4 - 1) / (threads * 4));
-    if (table_type == BW_F32) bw::launch((embed_gather_kernel<float>), dim3(grid), dim3(threads), 0, s, cp<float>(table), ids, out, H, V);
-    else if (table_type == BW_BF16) bw::launch((embed_gather_kernel<bf16>), dim3(grid), dim3(threads), 0, s, cp<bf16>(table), ids, out, H, V);
+    if (table_type == BW_F32) bw::launch((embed_gather_kernel<float>), dim3(grid), dim3(threads), 0, s, cp<float>(table), ids, out, H, V, scale);
+    else if (table_type == BW_BF16) bw::launch((embed_gather_kernel<bf16>), dim3(grid), dim3(threads), 0, s, cp<bf16>(table), ids, out, H, V, scale);
     else return BW_ERR_BAD_ARG;
     BW_LAUNCH_CHECK();
     return 0;

@@ -49,7 +49,15 @@ BW_EXPORT int bw_gemm_tc_noalloc(const void* x, const void* w, const void* bias,
     if (K <= 0 || splits < 1) return BW_ERR_BAD_ARG;
     const int kb_total = (K + BK - 1) / BK;
     if (splits > kb_total) splits = kb_total;
-    if ((long long)splits * M * N > (long long)BW_NOALLOC_SCRATCH_FLOATS) return BW_NOALLOC_TOO_LARGE;
+    if (splits > 1) {
+        // only a product that is really split touches the arrays: its partial sums and one counter
+        // group per output tile must fit them (an unsplit product of any size goes through)
+        if ((long long)splits * M * N > (long long)BW_NOALLOC_SCRATCH_FLOATS) return BW_NOALLOC_TOO_LARGE;
+        int tr = 0, bn = 0;
+        bw_gemm_tc_plan(M, N, K, 0, 0, 0, &tr, &bn);
+        const long long tiles = tr ? (long long)ceil_div(N, BM) * ceil_div(M, bn) : (long long)ceil_div(M, BM) * ceil_div(N, bn);
+        if (tiles * 4 > (long long)BW_NOALLOC_COUNTERS) return BW_NOALLOC_TOO_LARGE;
+    }
     float* scratch = nullptr;
     int* counters = nullptr;
     const int rc = scratch_on_current_device(&scratch, &counters);

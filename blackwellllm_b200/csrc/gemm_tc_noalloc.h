@@ -18,8 +18,12 @@
 // cudaMalloc, cudaFree or other allocating call.
 //
 // Limits and rules:
-//   * splits * M * N must not exceed BW_NOALLOC_SCRATCH_FLOATS, else the call
-//     returns BW_NOALLOC_TOO_LARGE (-10) and launches nothing.
+//   * With more than one split (after the clamp to the number of 64-wide
+//     k-blocks), splits * M * N must not exceed BW_NOALLOC_SCRATCH_FLOATS and the
+//     product must not have more than BW_NOALLOC_COUNTERS / 4 output tiles (of
+//     128 features x up to 16..256 tokens), else the call returns
+//     BW_NOALLOC_TOO_LARGE (-10) and launches nothing.  A product with one split
+//     uses neither array and is not bounded by them.
 //   * The first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current) and keeps it.  Make that
 //     first call before any stream capture begins.

@@ -49,6 +49,7 @@ class EngineOptions:
     max_requests: int = 64
     max_batch_tokens: int = 8192
     max_context: Optional[int] = None  # longest request; None: what the pool holds
+    ignore_unexpected: bool = False  # tensors of a checkpoint that the model does not use: pass over, no error
     cuda_graphs: bool = True         # replay decode-only steps from a CUDA graph per batch size
     max_graph_batch: int = 256
     device: str = "cuda:0"
@@ -102,7 +103,7 @@ class Engine:
         options = cls._options(opts)
         config = load_config(model_dir)
         model, ctx = cls._build(config, options)
-        model.bind(load_weights(model_dir, model.param_specs(), ctx.dtype, ctx.device))
+        model.bind(load_weights(model_dir, model.param_specs(), ctx.dtype, ctx.device, options.ignore_unexpected))
         return cls(config, model, options)
 
     @classmethod
@@ -111,7 +112,8 @@ class Engine:
         options = cls._options(opts)
         config = parse_config(raw_config)
         model, ctx = cls._build(config, options)
-        model.bind(bind_tensors(tensors, model.param_specs(), ctx.dtype, ctx.device))
+        model.bind(bind_tensors(tensors, model.param_specs(), ctx.dtype, ctx.device,
+                                ignore_unexpected=options.ignore_unexpected))
         return cls(config, model, options)
 
     @classmethod
@@ -269,12 +271,15 @@ class Engine:
             self.prepare(entries, min_blocks=width, into=slot["buf"], replay_width=width)
             slot["graph"].replay()
             return slot["logits"]
+        # The first step of this batch size: the model runs ONCE, uncaptured, and that run is the
+        # step's result (a mixer with state of its own must not see the step twice).  Then the same
+        # launches are recorded (a capture executes nothing) for the later steps of this size.
         batch = self.prepare(entries, min_blocks=width, into=slot["buf"])
         if any(t.shape[1] != width for t in batch.block_tables.values()):
             raise EngineError("a request outgrew max_context: its block table no longer fits the graph")
         batch.static_bound = width * self.cache.page_size
         from ..kernels import ops
-        self.model.forward(batch, self.cache.views)           # warm-up: builds kernels, scratch
+        logits = self.model.forward(batch, self.cache.views)
         torch.cuda.synchronize(self.device)
         batch.extras.clear()   # what depends on this step's values is recomputed inside the graph
         graph = torch.cuda.CUDAGraph()
@@ -284,8 +289,7 @@ class Engine:
         slot["kernels"] = ops.launches - before
         slot["graph"] = graph
         slot["batch"] = batch   # keeps the per-step tensors that the captured kernels read alive
-        slot["graph"].replay()
-        return slot["logits"]
+        return logits
 
     def graph_kernel_count(self, batch_size: int) -> int:
         """Launcher calls captured in the decode graph of this batch size (0: none yet)."""
@@ -295,19 +299,47 @@ class Engine:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one batch; returns float32 logits [wanted, vocab] on the device, in the
         order of the entries and of each entry's ``want``.  The result of a graph
-        replay is overwritten by the next step of the same batch size."""
+        replay is overwritten by the next step of the same batch size.
+
+        A step that fails changes nothing: a refusal (bad entries, no pages) comes before
+        anything is reserved, and if the model raises after the requests have grown, they are
+        rolled back to their lengths before the step and requests that the step created are
+        freed (the reference rolls a failed chunk back to a coherent prefix likewise:
+        src/core/engine_prefill_coordinator.cpp:296-304)."""
         if not entries:
             return torch.empty((0, self.config.vocab_size), dtype=torch.float32, device=self.device)
-        with torch.cuda.device(self.device):
-            R = self._graph_key(entries)
-            if R is not None:
-                logits = self._step_graph(entries, R)
-                T = R
-            else:
-                batch = self.prepare(entries)
-                logits = self.model.forward(batch, self.cache.views)
-                T = batch.T
+        cache = self.cache
+        before = [(e.rid, cache.length(e.rid) if cache.has(e.rid) else None) for e in entries]
+        try:
+            with torch.cuda.device(self.device):
+                R = self._graph_key(entries)
+                if R is not None:
+                    logits = self._step_graph(entries, R)
+                    T = R
+                else:
+                    batch = self.prepare(entries)
+                    logits = self.model.forward(batch, self.cache.views)
+                    T = batch.T
+        except BaseException:
+            self._roll_back(before)
+            raise
         self.cache.release_passed_many([e.rid for e in entries])
         self.steps_run += 1
         self.tokens_run += T
         return logits
+
+    def _roll_back(self, before) -> None:
+        """Puts every request of a failed step back to its length before the step; a request
+        the step created is freed.  A request whose fixed-size state may have been advanced
+        cannot go back by part of its length: it is freed too (its owner starts it again)."""
+        cache = self.cache
+        for rid, old in dict(before).items():
+            if not cache.has(rid):
+                continue
+            if old is None:
+                cache.free_request(rid)
+            elif cache.length(rid) != old:
+                try:
+                    cache.truncate(rid, old)
+                except ValueError:
+                    cache.free_request(rid)

@@ -61,11 +61,13 @@ class BlackwellEngine:
                  config: Optional[Mapping[str, object]] = None, random_seed: int = 0, random_std: float = 0.02,
                  dtype: str = "bfloat16", page_size: int = 16, num_pages: Optional[int] = None,
                  max_batch_tokens: int = 2048, chunk: Optional[int] = None, kv_fraction: Optional[float] = None,
-                 seed: int = 0, device: str = "cuda:0", cuda_graphs: bool = True):
+                 seed: int = 0, device: str = "cuda:0", cuda_graphs: bool = True, ignore_unexpected: bool = False):
         """``model``: a folder with config.json and model.safetensors.  Or ``config``
         (the config.json object) for random weights from ``random_seed``.  The cache
         holds ``max_batch_size`` sequences of ``max_context_length`` tokens unless
-        ``num_pages`` or ``kv_fraction`` (of free device memory) says otherwise."""
+        ``num_pages`` or ``kv_fraction`` (of free device memory) says otherwise.
+        ``ignore_unexpected``: tensors of the checkpoint that the model does not use are
+        passed over with a note instead of being an error."""
         self.request = request or InferenceConfig()
         rq = self.request
         if rq.max_context_length <= 0 or rq.max_batch_size < 1:
@@ -75,7 +77,8 @@ class BlackwellEngine:
         opts = EngineOptions(dtype=dtype, page_size=page_size, num_pages=num_pages,
                              kv_fraction=kv_fraction or 0.6, max_requests=max(rq.max_batch_size, 1),
                              max_batch_tokens=max(max_batch_tokens, rq.max_batch_size), device=device,
-                             max_context=rq.max_context_length, cuda_graphs=cuda_graphs)
+                             max_context=rq.max_context_length, cuda_graphs=cuda_graphs,
+                             ignore_unexpected=ignore_unexpected)
         if (model is None) == (config is None):
             raise EngineError("give either a model folder or a config for random weights")
         # the context is checked against the model before any weight is read
@@ -92,7 +95,6 @@ class BlackwellEngine:
         self.seed = seed
         self.chunk = chunk
         self.max_batch_tokens = max_batch_tokens
-        self._draws: Dict[int, int] = {}
         self._last_logits: Dict[int, torch.Tensor] = {}   # rows of the LAST step's logits, by sequence
         self.scheduler = self._new_scheduler()
 
@@ -124,11 +126,10 @@ class BlackwellEngine:
             raise EngineError(f"position {pos} is outside max_context_length {self.request.max_context_length}")
 
     def _pick(self, logits: torch.Tensor, seq_ids: Sequence[int], temperature: float, top_p: float) -> List[int]:
+        # The random number of a draw is a function of (seed, sequence, position of the sampled token):
+        # the same prompt on the same sequence id gives the same tokens again, whatever ran before.
         p = SamplingParams(temperature=temperature, top_p=top_p)
-        draws = []
-        for s in seq_ids:
-            draws.append(self._draws.get(s, 0))
-            self._draws[s] = draws[-1] + 1
+        draws = [self.engine.cache.length(self._seq(s)) for s in seq_ids]
         seeds = [self.seed * 1_000_003 + s for s in seq_ids]
         return self.sampler.sample(logits, [p] * len(seq_ids), seeds, draws)
 
@@ -207,7 +208,6 @@ class BlackwellEngine:
         rid = self._seq(seq_id)
         if self.engine.cache.has(rid):
             self.engine.cache.free_request(rid)
-        self._draws.pop(seq_id, None)
         self._last_logits.pop(seq_id, None)
 
     def reset_state(self, seq_id: int = 0) -> None:

@@ -106,7 +106,9 @@ def _fn(lib_name: str, fn_name: str, argtypes, macros=None, extra_flags=(), tag=
 
 # ------------------------------------------------------------------ elementwise
 
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 scale: float = 1.0) -> torch.Tensor:
+    """float32 rows ``table[ids] * scale`` (the start of the residual stream)."""
     _dev(table, "table"); _dev(ids, "ids", torch.int32)
     V, H = table.shape
     T = ids.numel()
@@ -114,9 +116,19 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Ten
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     _dev(out, "out", torch.float32)
     fn = _fn("elementwise", "bw_embed_gather",
-             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(fn(_ptr(table), _code(table, "table"), _ptr(ids), _ptr(out), T, H, V, _stream()), "embed_gather")
+             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(table), _code(table, "table"), _ptr(ids), _ptr(out), T, H, V, float(scale), _stream()), "embed_gather")
     return out
+
+
+def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: Optional[float] = None) -> torch.Tensor:
+    """In place on float32 ``logits``: times ``scale``, then ``softcap * tanh(x / softcap)`` if a cap is given."""
+    _dev(logits, "logits", torch.float32)
+    if softcap is not None and not softcap > 0:
+        raise KernelError("logit_transform: the soft cap must be positive")
+    fn = _fn("elementwise", "bw_logit_transform", [c_void_p, c_ll, c_float, c_float, c_void_p])
+    _check(fn(_ptr(logits), logits.numel(), float(scale), float(softcap or 0.0), _stream()), "logit_transform")
+    return logits
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype,
@@ -482,11 +494,18 @@ def gemm_tc_status() -> int:
     return int(lib.bw_gemm_tc_status())
 
 
-def check_attention_supported(dtype: torch.dtype, head_dim: int) -> None:
+MAX_GROUP_BF16 = 16   # query heads per kv head that the bfloat16 attention kernels stack in one tile
+
+
+def check_attention_supported(dtype: torch.dtype, head_dim: int, group: int = 1) -> None:
+    """Raises for a geometry no attention kernel of this dtype takes (known when a model is built)."""
     if head_dim <= 0 or head_dim > 256:
         raise KernelError(f"attention: head_dim {head_dim} is not supported (1..256)")
     if dtype == torch.bfloat16 and head_dim % 16:
         raise KernelError(f"attention: the bfloat16 kernels take head sizes in steps of 16, got {head_dim}")
+    if dtype == torch.bfloat16 and group > MAX_GROUP_BF16:
+        raise KernelError(f"attention: {group} query heads per kv head exceed the bfloat16 kernels' limit of "
+                          f"{MAX_GROUP_BF16}")
 
 
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
@@ -502,7 +521,6 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
 
 _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
-_TARGET_CTAS = 148 * 4
 
 
 def plan_attention_work(q_len, q_start, kv_len, G: int, nkv: int, window: Optional[int], hd: int = 128,
@@ -577,12 +595,10 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     _dev(q, "q", torch.bfloat16); _dev(k_pages, "k_pages", torch.bfloat16); _dev(v_pages, "v_pages", torch.bfloat16)
     _dev(block_table, "block_table", torch.int32)
     num_pages, nkv, page_size, hd = k_pages.shape
-    check_attention_supported(torch.bfloat16, hd)
     if q.shape[1] != nh * hd or nh % nkv:
         raise KernelError("attention: q must be [T, nh * head_dim] with nh a multiple of the kv heads")
     G = nh // nkv
-    if G > 16:
-        raise KernelError(f"attention: {G} query heads per kv head exceed the kernel's limit of 16")
+    check_attention_supported(torch.bfloat16, hd, G)
     # prompt portions: the tcgen05 kernel (128-row tiles) where it takes the geometry, else mma.sync (64-row tiles)
     use_tc = attention_tc_supports(hd, G, page_size)
     rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices = attention_work(

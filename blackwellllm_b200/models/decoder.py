@@ -1,6 +1,8 @@
 """The decoder that every registered architecture is run by: an embedding, blocks
 built from the configuration's layer specs, a schedule that says in which order
-they run and whose cache each run uses, a final norm and the output head.
+they run and whose cache each run uses, a final norm and the output head; around
+them the configuration's optional constants (embedding multiplier, logit scale,
+logit soft cap).
 
 It is driven by :class:`ModelConfig` alone and knows no architecture by name.
 Reference for the sequence of operations: src/core/engine.cpp:921-1041.
@@ -73,7 +75,8 @@ class DecoderModel:
     def forward(self, batch, caches: List[object]) -> torch.Tensor:
         """Runs the batch's tokens through the schedule; returns float32 logits
         [len(batch.logit_rows), vocab] for the rows that were asked for."""
-        h = ops.embed_gather(self.embed, batch.token_ids)
+        c = self.config
+        h = ops.embed_gather(self.embed, batch.token_ids, scale=c.embedding_multiplier)
         for pos, e in enumerate(self.config.schedule):
             cache = caches[e.cache_of if e.cache_of is not None else pos]
             self.blocks[e.layer].forward(h, batch, cache, owns_cache=e.cache_of is None)
@@ -81,4 +84,7 @@ class DecoderModel:
         if n == 0:
             return torch.empty((0, self.config.vocab_size), dtype=torch.float32, device=h.device)
         x = self.final_norm.forward(h, rows=batch.logit_rows)
-        return self.head(x, out_dtype=torch.float32)
+        logits = self.head(x, out_dtype=torch.float32)
+        if c.logit_scale != 1.0 or c.logit_softcap is not None:
+            ops.logit_transform(logits, c.logit_scale, c.logit_softcap)
+        return logits

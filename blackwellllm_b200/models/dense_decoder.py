@@ -8,7 +8,8 @@ Keys and defaults follow src/core/config.cpp:113-284:
 * required: hidden_size, num_attention_heads, intermediate_size,
   num_hidden_layers, num_key_value_heads, vocab_size (config.cpp:126-131);
 * head_dim defaults to hidden_size // num_attention_heads (config.cpp:144-145);
-* rms_norm_eps defaults to 1e-6 (config.cpp:157); rope_theta to 10000 (config.cpp:188);
+* rms_norm_eps (or its alias layernorm_epsilon) defaults to 1e-6 (config.cpp:157); rope_theta to
+  10000 (config.cpp:188);
 * q/k/v bias: ``attention_bias`` if present, else true exactly for model_type
   "qwen2" (config.cpp:226-227);
 * tie_word_embeddings defaults to false (config.cpp:158);
@@ -90,7 +91,7 @@ def parse_dense_decoder(raw: Mapping[str, Any], *, architecture: str,
     act = raw.get("hidden_act", "silu")
     if act != "silu":
         raise ConfigError(f"hidden_act {act!r} is not supported (the feed-forward is SwiGLU: 'silu')")
-    eps = float(raw.get("rms_norm_eps", 1e-6))
+    eps = float(raw.get("rms_norm_eps", raw.get("layernorm_epsilon", 1e-6)))   # the alias: config.cpp:157
     if not eps > 0:
         raise ConfigError(f"rms_norm_eps must be > 0, got {eps!r}")
     theta = float(raw.get("rope_theta", 10000.0))

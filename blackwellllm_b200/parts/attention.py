@@ -31,7 +31,7 @@ class GQAAttention(Mixer):
         self.scale = float(spec.softmax_scale) if spec.softmax_scale is not None else self.hd ** -0.5
         self.ctx = ctx
         self.position = build_position(spec.position, self.hd, ctx)
-        ops.check_attention_supported(ctx.dtype, self.hd)
+        ops.check_attention_supported(ctx.dtype, self.hd, self.nh // self.nkv)
         self.qkv: Linear = None
         self.project = None
         self.o: Linear = None

@@ -1,7 +1,9 @@
 """Binds the tensors of a model folder to the names a model asks for.
 
 All names are checked before anything is copied: one :class:`WeightError` lists
-every missing tensor, every unexpected one and every wrong shape.  (The reference
+every missing tensor, every unexpected one and every wrong shape.  Derived buffers
+that some exporters store (``rotary_emb.inv_freq``) are passed over with a note, and
+with ``ignore_unexpected`` so is every other tensor the model does not ask for.  (The reference
 finds a missing tensor only at its first use: src/core/memory_pool.cpp:466-475.)
 
 Kept types: matrix operands and embedding tables are held in the compute dtype
@@ -51,10 +53,19 @@ def kept_dtype(spec: ParamSpec, stored: torch.dtype, compute: torch.dtype) -> to
     return torch.float32 if stored in (torch.float32, torch.float64) else torch.bfloat16
 
 
-def check_names(where: str, expected: Mapping[str, ParamSpec], found: Mapping[str, object]) -> None:
-    """``found`` maps name -> object with .shape and .dtype."""
+# Tensors some exporters store although they are no weights (derived tables): never an error.
+DERIVED_BUFFERS = (".rotary_emb.inv_freq",)
+
+
+def check_names(where: str, expected: Mapping[str, ParamSpec], found: Mapping[str, object],
+                ignore_unexpected: bool = False) -> list:
+    """``found`` maps name -> object with .shape and .dtype.  Returns the names that were found,
+    not asked for and passed over: derived buffers always (``DERIVED_BUFFERS``), any other
+    unexpected tensor only with ``ignore_unexpected`` (else it is part of the error)."""
     missing = [n for n, s in expected.items() if n not in found and not s.optional]
-    unexpected = [n for n in found if n not in expected]
+    extra = [n for n in found if n not in expected]
+    passed_over = [n for n in extra if ignore_unexpected or n.endswith(DERIVED_BUFFERS)]
+    unexpected = [n for n in extra if n not in passed_over]
     wrong_shape, wrong_type = [], []
     for n, s in expected.items():
         if n in found:
@@ -65,12 +76,18 @@ def check_names(where: str, expected: Mapping[str, ParamSpec], found: Mapping[st
                 wrong_type.append((n, dt))
     if missing or unexpected or wrong_shape or wrong_type:
         raise WeightError(where, sorted(missing), sorted(unexpected), sorted(wrong_shape), sorted(wrong_type))
+    if passed_over:
+        import sys
+        shown = ", ".join(sorted(passed_over)[:4]) + (" ..." if len(passed_over) > 4 else "")
+        print(f"[blackwellllm_b200] {where}: {len(passed_over)} tensor(s) the model does not use were "
+              f"passed over: {shown}", file=sys.stderr)
+    return sorted(passed_over)
 
 
 def load_weights(model_dir: str, expected: Mapping[str, ParamSpec], compute: torch.dtype,
-                 device: torch.device) -> Dict[str, torch.Tensor]:
+                 device: torch.device, ignore_unexpected: bool = False) -> Dict[str, torch.Tensor]:
     entries = index_folder(model_dir)
-    check_names(model_dir, expected, entries)
+    check_names(model_dir, expected, entries, ignore_unexpected)
     out: Dict[str, torch.Tensor] = {}
     with TensorFiles() as files:
         for name, spec in expected.items():
@@ -82,9 +99,10 @@ def load_weights(model_dir: str, expected: Mapping[str, ParamSpec], compute: tor
 
 
 def bind_tensors(tensors: Mapping[str, torch.Tensor], expected: Mapping[str, ParamSpec],
-                 compute: torch.dtype, device: torch.device, where: str = "<tensors>") -> Dict[str, torch.Tensor]:
+                 compute: torch.dtype, device: torch.device, where: str = "<tensors>",
+                 ignore_unexpected: bool = False) -> Dict[str, torch.Tensor]:
     """The same binding for tensors already in memory (used by tests and by
     ``Engine.from_tensors``)."""
-    check_names(where, expected, tensors)
+    check_names(where, expected, tensors, ignore_unexpected)
     return {n: tensors[n].to(kept_dtype(s, tensors[n].dtype, compute)).to(device)
             for n, s in expected.items() if n in tensors}

@@ -362,6 +362,7 @@ def _pack(cm, entries, vocab=1000, min_blocks=0, max_tokens=10 ** 6, cap=1 << 16
 def test_packed_step_equals_the_step_built_call_by_call(seed):
     import torch
     from blackwellllm_b200.cache import manager as M
+    from batch_packer import pack_batch
     from blackwellllm_b200.engine.batch import BatchBuilder
     rng = random.Random(seed)
     pages = rng.randint(12, 30)
@@ -406,7 +407,7 @@ def test_packed_step_equals_the_step_built_call_by_call(seed):
             rows += [t0 + x for x in w]
             t0 += len(t)
         block_rows = {g: [b.block_table(rid, g) for rid, _, _ in entries] for g in range(2)}
-        ref = BatchBuilder(torch.device("cpu")).build(segs, rows, block_rows, min_blocks=min_blocks)
+        ref = pack_batch(BatchBuilder(torch.device("cpu")), segs, rows, block_rows, min_blocks=min_blocks)
         T, R = ref.T, ref.R
         flat = torch.cat([ref.token_ids, ref.positions, ref.req_of_token, ref.cu_q, ref.q_start, ref.kv_len,
                           ref.state_slot, ref.logit_rows] + [ref.block_tables[g].reshape(-1) for g in range(2)])

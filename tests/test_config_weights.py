@@ -129,6 +129,45 @@ def test_weight_error_lists_everything(tmp_path):
         assert frag in s
 
 
+def test_unexpected_tensors_derived_buffers_and_the_switch(capsys):
+    """A derived buffer that old exporters store is passed over with a note; any other tensor the model
+    does not ask for is an error unless the caller says to ignore it."""
+    specs = model_param_specs(tiny.TINY_LLAMA)
+    t = random_tensors(specs, 0, dtype=torch.float32)
+    t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    out = bind_tensors(t, specs, torch.float32, torch.device("cpu"))
+    assert "model.layers.0.self_attn.rotary_emb.inv_freq" not in out and "passed over" in capsys.readouterr().err
+    t["model.extra.weight"] = torch.zeros(3)
+    with pytest.raises(WeightError) as e:
+        bind_tensors(t, specs, torch.float32, torch.device("cpu"))
+    assert e.value.unexpected == ["model.extra.weight"]
+    out = bind_tensors(t, specs, torch.float32, torch.device("cpu"), ignore_unexpected=True)
+    assert set(out) == {n for n, s_ in specs.items() if not s_.optional}
+    assert "2 tensor(s)" in capsys.readouterr().err
+
+
+def test_generation_config_adds_end_of_sequence_ids(tmp_path):
+    d = str(tmp_path / "m")
+    os.makedirs(d)
+    raw = dict(tiny.TINY_LLAMA, eos_token_id=7)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(raw, f)
+    assert load_config(d).eos_token_ids == (7,)
+    with open(os.path.join(d, "generation_config.json"), "w") as f:
+        json.dump({"eos_token_id": [9, 7, 11], "temperature": 0.6}, f)
+    assert load_config(d).eos_token_ids == (9, 7, 11)
+    with open(os.path.join(d, "generation_config.json"), "w") as f:
+        json.dump({"eos_token_id": 3}, f)
+    assert load_config(d).eos_token_ids == (3, 7)
+    with open(os.path.join(d, "generation_config.json"), "w") as f:
+        json.dump({"eos_token_id": "no"}, f)
+    with pytest.raises(ConfigError, match="eos_token_id"):
+        load_config(d)
+    assert parse_config(dict(tiny.TINY_LLAMA, layernorm_epsilon=3e-7, rms_norm_eps=None) | {"rms_norm_eps": 2e-6}).layers[0].mixer_norm.eps == 2e-6
+    alias = {k: v for k, v in tiny.TINY_LLAMA.items() if k != "rms_norm_eps"}
+    assert parse_config(dict(alias, layernorm_epsilon=3e-7)).final_norm.eps == 3e-7
+
+
 def test_tied_head_tolerates_a_stored_lm_head():
     specs = model_param_specs(tiny.TINY_QWEN)
     t = random_tensors(specs, 0, dtype=torch.float32)

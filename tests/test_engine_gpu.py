@@ -273,6 +273,24 @@ def test_position_addressed_calls(folders):
     assert llm.engine.cache.free_pages() == [g.num_pages for g in llm.engine.cache.groups]
 
 
+def test_sampled_tokens_of_the_position_addressed_calls_do_not_depend_on_what_ran_before(folders):
+    """Temperature 1: the same prompt from position 0 on the same sequence id gives the same tokens again
+    (the draw is a function of seed, sequence and position, not of how many draws came before)."""
+    raw, _, page = tiny.CONFIGS["qwen"]
+    llm = make(folders[("qwen", "float32")], "float32", page_size=page, seed=5)
+    p = tiny.prompt(15, raw["vocab_size"], 8)
+
+    def run():
+        out = [llm.prefill(p, 0, 1.0, 1.0, seq_id=0)]
+        for i in range(5):
+            out.append(llm.forward(out[-1], len(p) + i, 1.0, 1.0, seq_id=0))
+        return out
+    first = run()
+    llm.forward(3, 4, 1.0, 1.0, seq_id=0)        # something else in between, on the same sequence
+    assert run() == first
+    assert len(set(first)) > 1
+
+
 def test_pages_run_out_preemption_reproduces_the_tokens(folders):
     from blackwellllm_b200 import SamplingParams
     raw, _, page = tiny.CONFIGS["llama"]

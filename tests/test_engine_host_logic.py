@@ -115,6 +115,128 @@ def test_refusals_change_nothing(engine):
     assert eng.steps_run == 1
 
 
+class NoStateModel(StandInModel):
+    """One cache group, no fixed-size state; fails on demand after the requests have grown."""
+    fail = None
+
+    def cache_requests(self):
+        return [PagedKVRequest(2, 16, None)]
+
+    def forward(self, batch, views):
+        if self.fail is not None:
+            raise self.fail
+        return super().forward(batch, views)
+
+
+def test_a_forward_that_raises_leaves_lengths_and_pages_as_they_were(monkeypatch):
+    """The model fails after the step's pages were reserved and the requests grown (a kernel refusing a
+    size, a CUDA error): every request is back at its length before the step, a request the step created
+    is gone, no page is lost; the next step runs as if nothing had happened."""
+    from blackwellllm_b200.kernels.ops import KernelError
+    monkeypatch.setattr(torch.cuda, "device", lambda d: contextlib.nullcontext())
+    cfg = parse_config(tiny.CONFIGS["llama"][0])
+    model = NoStateModel(cfg.vocab_size)
+    eng = Engine(cfg, model, EngineOptions(dtype="float32", page_size=8, num_pages=12, max_requests=3,
+                                           max_batch_tokens=64, cuda_graphs=False, device="cpu"))
+    eng.step([StepEntry("a", list(range(20)), [19]), StepEntry("b", [1, 2, 3], [])])
+    before = (eng.cache.free_pages(), eng.cache.length("a"), eng.cache.length("b"), eng.cache.slots.num_free,
+              eng.cache.block_table("a", 0), eng.steps_run)
+    model.fail = KernelError("attention: refused")
+    with pytest.raises(KernelError, match="refused"):
+        eng.step([StepEntry("a", [5, 6, 7, 8, 9], [4]), StepEntry("n", list(range(17)), []), StepEntry("b", [4], [0])])
+    assert (eng.cache.free_pages(), eng.cache.length("a"), eng.cache.length("b"), eng.cache.slots.num_free,
+            eng.cache.block_table("a", 0), eng.steps_run) == before
+    assert not eng.has_request("n")
+    eng.cache.check_invariants()
+    model.fail = None
+    lg = eng.step([StepEntry("a", [5], [0])])
+    assert lg[0, :2].tolist() == [5, 20]                                       # position 20: nothing of the failed step stayed
+
+
+def test_a_failed_step_frees_a_request_whose_state_cannot_go_back(engine):
+    """Fixed-size state cannot be rolled back by part of a request's length: such a request is freed."""
+    eng, model = engine
+    eng.step([StepEntry("a", list(range(10)), [])])
+
+    def boom(batch, views):
+        raise RuntimeError("boom")
+    model.forward = boom
+    with pytest.raises(RuntimeError, match="boom"):
+        eng.step([StepEntry("a", [1, 2], [1]), StepEntry("n", [3], [0])])
+    assert not eng.has_request("a") and not eng.has_request("n")
+    assert eng.cache.free_pages() == [12, 12] and eng.cache.slots.num_free == 3
+    eng.cache.check_invariants()
+
+
+def test_the_first_step_of_a_decode_batch_size_runs_the_model_once(monkeypatch):
+    """Decode-only steps are replayed from a graph per batch size.  The step that records the graph must run
+    the model once, not twice: a mixer with state of its own would otherwise advance its state twice for
+    one token.  The graph here is a stand-in that records what a capture records (the launches, without
+    running them) and runs them at replay; the model counts what actually ran."""
+    monkeypatch.setattr(torch.cuda, "device", lambda d: contextlib.nullcontext())
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+    capturing = []
+
+    class FakeGraph:
+        def __init__(self):
+            self.recorded = []
+
+        def replay(self):
+            for fn in self.recorded:
+                fn()
+
+    @contextlib.contextmanager
+    def fake_capture(graph):
+        capturing.append(graph)
+        try:
+            yield
+        finally:
+            capturing.pop()
+    monkeypatch.setattr(torch.cuda, "CUDAGraph", FakeGraph)
+    monkeypatch.setattr(torch.cuda, "graph", fake_capture)
+
+    class StatefulModel(StandInModel):
+        """Per request slot a count of the tokens it has seen (its 'state'), bumped by every run."""
+
+        def __init__(self, vocab):
+            super().__init__(vocab)
+            self.seen = torch.zeros(8, dtype=torch.int64)
+            self.runs = 0
+
+        def cache_requests(self):
+            return [PagedKVRequest(2, 16, None)]
+
+        def _run(self, batch, out):
+            self.runs += 1
+            for t in range(batch.T):
+                self.seen[int(batch.state_slot[int(batch.req_of_token[t])])] += 1
+            for i, t in enumerate(batch.logit_rows.tolist()):
+                out[i, 0], out[i, 1] = float(batch.token_ids[t]), float(batch.positions[t])
+
+        def forward(self, batch, views):
+            out = torch.zeros((len(batch.logit_rows), self.vocab), dtype=torch.float32)
+            if capturing:
+                capturing[-1].recorded.append(lambda: self._run(batch, out))    # recorded, not run
+            else:
+                self._run(batch, out)
+            return out
+
+    cfg = parse_config(tiny.CONFIGS["llama"][0])
+    model = StatefulModel(cfg.vocab_size)
+    eng = Engine(cfg, model, EngineOptions(dtype="float32", page_size=8, num_pages=12, max_requests=3,
+                                           max_batch_tokens=64, cuda_graphs=True, device="cpu"))
+    eng.step([StepEntry("a", [1, 2, 3], []), StepEntry("b", [4], [])])      # prompts: not a decode-only step
+    assert model.runs == 1 and eng.graph_kernel_count(2) == 0
+    slot_a, slot_b = eng.cache.slot("a"), eng.cache.slot("b")
+    lg = eng.step([StepEntry("a", [7], [0]), StepEntry("b", [8], [0])])     # the first decode step of batch size 2
+    assert model.runs == 2                                                   # once: not a warm-up run and a replay
+    assert model.seen[slot_a] == 4 and model.seen[slot_b] == 2
+    assert lg[:, :2].tolist() == [[7, 3], [8, 1]]
+    lg = eng.step([StepEntry("b", [9], [0]), StepEntry("a", [6], [0])])     # replayed
+    assert model.runs == 3 and model.seen[slot_a] == 5 and model.seen[slot_b] == 3
+    assert lg[:, :2].tolist() == [[9, 2], [6, 4]]
+
+
 def test_no_device_no_engine():
     cfg = tiny.CONFIGS["llama"][0]
     with pytest.raises(EngineError, match="no CPU path"):

@@ -18,6 +18,7 @@ def rnd(*shape, seed=0, scale=1.0):
 
 def make_batch(cache, segments, want_all=True):
     """segments: [(rid, n_tokens)]: grows the requests in ``cache`` and packs a batch."""
+    from batch_packer import pack_batch
     from blackwellllm_b200.engine.batch import BatchBuilder
     segs, rows, t0 = [], [], 0
     for rid, n in segments:
@@ -28,7 +29,7 @@ def make_batch(cache, segments, want_all=True):
         rows += list(range(t0, t0 + n))
         t0 += n
     block_rows = {g: [cache.block_table(rid, g) for rid, _ in segments] for g in range(len(cache.groups))}
-    return BatchBuilder(DEV).build(segs, rows if want_all else [], block_rows)
+    return pack_batch(BatchBuilder(DEV), segs, rows if want_all else [], block_rows)
 
 
 TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
@@ -529,3 +530,119 @@ def test_toy_routed_ffn_and_toy_position_encoding(dtype):
             # compare the rows where the engine's rounding cannot have flipped a choice
             close = (out - ref[r]).abs().amax(dim=1) <= tol * float(ref[r].abs().max())
             assert float(close.double().mean()) >= 0.8, r
+
+
+# ---------------------------------------------------------------------------------------------
+# A mixer with state of its own that CAN be captured (device work only): decode steps of a model
+# with it run from the CUDA graph, and the step that records the graph must advance the state once.
+
+@dataclass(frozen=True)
+class ToyCountSpec:
+    kind: str = "toy_count"
+
+
+def register_toy_count():
+    from blackwellllm_b200.config import ModelConfig, ScheduleEntry, register_architecture
+    from blackwellllm_b200.config.specs import LayerSpec, RMSNormSpec
+    from blackwellllm_b200.parts import FixedStateRequest, Mixer, register_mixer
+
+    class ToyCount(Mixer):
+        """state[slot] += 1 per token; adds the request's count so far to every channel of the token."""
+        graph_safe = True
+
+        def __init__(self, spec, hidden_size, ctx):
+            self.H = hidden_size
+
+        def cache_request(self):
+            return FixedStateRequest((1,), torch.float32)
+
+        def forward(self, x, residual, batch, cache, owns_cache=True):
+            slots = batch.state_slot.long()[batch.req_of_token.long()]           # [T], no host round trip
+            before = cache.state[slots, 0]
+            rank = (torch.arange(batch.T, device=x.device) - batch.cu_q.long()[batch.req_of_token.long()]).float()
+            residual += (before + rank + 1.0)[:, None]
+            cache.state.index_put_((slots, torch.zeros_like(slots)), torch.ones_like(before), accumulate=True)
+
+    register_mixer("toy_count", ToyCount)
+
+    def parse(raw):
+        layer = LayerSpec(ToyCountSpec(), None, RMSNormSpec(1e-5), None, mixer_prefix="count.")
+        return ModelConfig(architecture="ToyCountForCausalLM", hidden_size=raw["hidden_size"], vocab_size=raw["vocab_size"],
+                           layers=(layer,), schedule=(ScheduleEntry(0),), final_norm=RMSNormSpec(1e-5),
+                           tie_word_embeddings=True, max_position_embeddings=0, raw=dict(raw))
+
+    register_architecture("ToyCountForCausalLM", parse)
+
+
+def test_graph_safe_stateful_mixer_is_advanced_once_by_the_step_that_records_the_graph():
+    from blackwellllm_b200 import Engine, StepEntry
+    from blackwellllm_b200.weights.random_init import model_param_specs, random_tensors
+    register_toy_count()
+    raw = {"architectures": ["ToyCountForCausalLM"], "hidden_size": 32, "vocab_size": 50}
+    W = random_tensors(model_param_specs(raw), seed=2, std=0.3, dtype=torch.float32)
+
+    def run(graphs):
+        eng = Engine.from_tensors(raw, W, dtype="float32", page_size=8, max_tokens=64, max_requests=2, cuda_graphs=graphs)
+        outs = [eng.step([StepEntry("a", [1, 2, 3], [2]), StepEntry("b", [4], [0])]).clone()]
+        for t in (5, 6, 7):                       # decode-only steps of batch size 2: recorded at the first, replayed after
+            outs.append(eng.step([StepEntry("a", [t], [0]), StepEntry("b", [t + 10], [0])]).clone())
+        state = eng.cache.views[0].state.clone()
+        return outs, state, eng
+
+    with_graph, state_g, eng = run(True)
+    without, state_n, _ = run(False)
+    assert eng.graph_kernel_count(2) > 0
+    assert sorted(state_g[:, 0].tolist()) == [4.0, 6.0] and torch.equal(state_g, state_n)
+    for a, b in zip(with_graph, without):
+        assert torch.allclose(a, b, rtol=0, atol=1e-5)
+
+
+# ---------------------------------------------------------------------------------------------
+# The decoder's optional constants: an architecture whose embedding rows are multiplied by a constant
+# and whose logits are scaled and soft-capped is a parser only.
+
+def register_toy_scaled():
+    import dataclasses
+
+    from blackwellllm_b200.config import register_architecture
+    from blackwellllm_b200.models.dense_decoder import parse_dense_decoder
+
+    def parse(raw):
+        base = parse_dense_decoder(raw, architecture="ToyScaledForCausalLM", default_qkv_bias=False)
+        return dataclasses.replace(base, embedding_multiplier=float(raw["embedding_multiplier"]),
+                                   logit_scale=float(raw["logit_scale"]), logit_softcap=raw.get("final_logit_softcapping"))
+
+    register_architecture("ToyScaledForCausalLM", parse)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("softcap", [None, 2.5])
+def test_embedding_multiplier_logit_scale_and_soft_cap(dtype, softcap):
+    from blackwellllm_b200 import Engine, StepEntry
+    from blackwellllm_b200.weights.random_init import model_param_specs, random_tensors
+    import tiny
+    from plain_model import plain_config, plain_embedding, plain_layer
+    register_toy_scaled()
+    raw = dict(tiny.TINY_LLAMA, architectures=["ToyScaledForCausalLM"], embedding_multiplier=8.0, logit_scale=0.25)
+    if softcap is not None:
+        raw["final_logit_softcapping"] = softcap
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    W = random_tensors(model_param_specs(raw), seed=3, std=0.05, dtype=tdt)
+    ids = tiny.prompt(37, raw["vocab_size"], 5)
+    # the plain twin: the plain layers around the three constants
+    c = plain_config(raw)
+    Wd = {k: v.double() for k, v in W.items()}
+    x = plain_embedding(Wd["model.embed_tokens.weight"], ids) * 8.0
+    inv = plain_inv_freq(c["hd"], c["theta"], c["scaling"], c["rd"])
+    for i in range(c["L"]):
+        x = plain_layer(x, torch.arange(len(ids)), Wd, i, c, inv)
+    ref = plain_linear(plain_rmsnorm(x, Wd["model.norm.weight"], c["eps"]), Wd["lm_head.weight"]) * 0.25
+    if softcap is not None:
+        ref = softcap * torch.tanh(ref / softcap)
+    eng = Engine.from_tensors(raw, W, dtype=dtype, page_size=16, max_tokens=64, max_requests=1)
+    out = torch.cat([eng.step([StepEntry("a", ids[:20], list(range(20)))]),
+                     eng.step([StepEntry("a", ids[20:], list(range(17)))])]).double().cpu()
+    tol = 1e-4 if dtype == "float32" else 1.5e-2
+    assert float((out - ref).abs().max()) <= tol * float(ref.abs().max())
+    plain_unscaled = plain_linear(plain_rmsnorm(x, Wd["model.norm.weight"], c["eps"]), Wd["lm_head.weight"])
+    assert float((out - plain_unscaled).abs().max()) > 0.1 * float(plain_unscaled.abs().max())   # the constants matter

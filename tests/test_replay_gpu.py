@@ -68,3 +68,16 @@ def test_cutting_changes_only_rounding(folders, dtype):
     b = replay.run_trace(folder, dtype, s2, m2, raw["vocab_size"], page_size=page)
     worst = max(float((a[k] - b[k]).abs().max()) / float(a[k].abs().max()) for k in a)
     assert worst <= tiny.TOL[dtype], worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_with_pages_of_24_tokens(folders, dtype):
+    """A page size that does not divide 64 (nor the kernels' key tiles): mixed steps in a pool where pages
+    are used again."""
+    name = "llama3"
+    raw = tiny.CONFIGS[name][0]
+    folder = folders[(name, dtype)]
+    reqs, plain = requests_and_plain(name, dtype, folder)
+    steps = replay.trace_mixed(reqs, 384, seed=8)
+    rows = replay.run_trace(folder, dtype, steps, 384, raw["vocab_size"], page_size=24)
+    replay.compare(rows, plain, tiny.TOL[dtype], label=f"{name} {dtype} mixed, pages of 24")

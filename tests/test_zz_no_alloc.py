@@ -29,7 +29,9 @@ def _entry():
     vp, i, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     fn.argtypes = [vp, vp, vp, i, vp, i, i, i, i, ll, ll, i, i, vp]
     fn.restype = i
-    return fn
+    lib.bw_gemm_tc_status.argtypes = []
+    lib.bw_gemm_tc_status.restype = i
+    return fn, lib.bw_gemm_tc_status
 
 
 def _call(fn, x, w, bias, out, accumulate, splits):
@@ -53,15 +55,22 @@ def _case(M, N, K, seed):
 
 def test_no_alloc_entry_matches_the_regular_one_twice_in_a_row():
     from blackwellllm_b200.kernels import ops
-    fn = _entry()
+    fn, status = _entry()
     # the second call is smaller, so the scratch still holds the first call's sums around its own
     for (M, N, K, splits, seed) in [(48, 1000, 2048, 4, 1), (5, 520, 1024 + 192, 3, 2)]:
         x, w, bias, base = _case(M, N, K, seed)
         mine = base.clone()
-        before = torch.cuda.memory_allocated(DEV)
+        assert _call(fn, x, w, bias, mine, True, splits) == 0     # the first call also loads the kernels
+        torch.cuda.synchronize()
+        mine.copy_(base)
+        # what the DEVICE reports as free (cudaMemGetInfo: it sees every allocation, whoever makes it) and
+        # torch's own counter, around a call that is complete before the second reading
+        free_before, held_before = torch.cuda.mem_get_info(DEV)[0], torch.cuda.memory_allocated(DEV)
         rc = _call(fn, x, w, bias, mine, True, splits)
+        torch.cuda.synchronize()
         assert rc == 0, rc
-        assert torch.cuda.memory_allocated(DEV) == before
+        assert torch.cuda.mem_get_info(DEV)[0] == free_before and torch.cuda.memory_allocated(DEV) == held_before
+        assert status() == 0                                      # this library's own bounded waits never gave up
         theirs = base.clone()
         ops.gemm_tc(x, w, bias, out=theirs, accumulate=True, force_splits=splits)
         torch.cuda.synchronize()
@@ -77,7 +86,7 @@ def test_no_alloc_entry_matches_the_regular_one_twice_in_a_row():
 
 
 def test_no_alloc_entry_refuses_what_its_scratch_cannot_hold():
-    fn = _entry()
+    fn, status = _entry()
     M, N, K = 256, 8192, 1024           # 4 splits x 256 x 8192 floats > 4 Mi
     x, w, _, _ = _case(M, N, K, 3)
     out = torch.full((M, N), 7.0, device=DEV)
@@ -88,3 +97,17 @@ def test_no_alloc_entry_refuses_what_its_scratch_cannot_hold():
     assert _call(fn, x, w, None, out, False, 2) == 0   # 2 x 256 x 8192 = 4 Mi floats: just fits
     ref = x.double() @ w.double().T
     assert float((out.double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+    # one split uses neither array: a product far beyond the scratch goes through
+    M, N, K = 2048, 4096, 512
+    x, w, _, _ = _case(M, N, K, 4)
+    big = torch.empty(M, N, device=DEV)
+    assert M * N > SCRATCH_FLOATS and _call(fn, x, w, None, big, False, 1) == 0
+    ref = x.double() @ w.double().T
+    assert float((big.double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+    # more output tiles than there are counters: the documented code, nothing launched
+    M, N, K = 1, 128 * 4100, 128
+    x, w, _, _ = _case(M, N, K, 5)
+    row = torch.full((M, N), 7.0, device=DEV)
+    assert 2 * M * N <= SCRATCH_FLOATS and _call(fn, x, w, None, row, False, 2) == TOO_LARGE
+    torch.cuda.synchronize()
+    assert bool((row == 7.0).all()) and status() == 0
