@@ -38,8 +38,7 @@ constexpr int A_BYTES = BM * BK * 2;
 constexpr int THREADS = 192;
 constexpr int NUM_SMS = 148;
 // Epilogue staging, per epilogue warp a 32 x 33 float block or two 32 x 32 boxes for TMA.  Only the normal
-// orientation uses it, and that has tiles of 128 columns or more: the narrow kernels do without, which
-// keeps two of them on an SM.
+// orientation uses it, and that has tiles of 128 columns or more: the narrow kernels do without.
 template <int BN> __host__ __device__ constexpr int staging_bytes() { return BN >= 128 ? 4 * 2 * 4096 : 0; }
 constexpr int SMEM_BUDGET = 226 * 1024 - staging_bytes<256>() - 2048;
 constexpr int FUSED_REDUCE_MAX_TOKENS = 16;   // split-K sums inside the kernel up to this many tokens
@@ -122,9 +121,13 @@ __device__ __forceinline__ void rope_store(const RopeOut& ro, const RopeSlot& sl
 template <int BN> __host__ __device__ constexpr int stages_for() {
     constexpr int per = A_BYTES + BN * BK * 2;
     constexpr int s = SMEM_BUDGET / per;
-    // the narrowest tile (decode with up to 16 tokens) keeps 5 stages, so that two CTAs fit on an
-    // SM and the next product's CTAs can start loading weights while this one's drain
-    return BN <= 16 ? 5 : (s > 8 ? 8 : s);
+    // The narrowest tile (decode with up to 16 tokens): 8 stages of 18 KB.  A CTA streams what its
+    // stages hold in flight over the latency of a load (about 2 us from DRAM): 5 stages drew about
+    // 40 GB/s, less than an SM's share of the bandwidth.  Measured on a decode step at batch 8 and
+    // context 8,192 (ms): 5 stages 5.08, 6: 4.94, 7: 4.93, 8: 4.91, 10: 4.95, 12: 5.02.  (With 5
+    // stages two CTAs fit on an SM and the next product's CTAs could request weights while this
+    // one's drained; the deeper ring is worth more.)
+    return BN <= 16 ? 8 : (s > 8 ? 8 : s);
 }
 
 // The rotary epilogue of G consecutive tokens of one feature (one lane), in two halves: what does
@@ -365,7 +368,7 @@ struct Items {
 };
 
 template <int BN, bool ROPE>
-__global__ void __launch_bounds__(THREADS, BN <= 16 ? 2 : 1)
+__global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, Epilogue ep, int kb_total, int kb_per_split, int tiles_a, int tiles_b, int num_work) {
     constexpr int STAGES = stages_for<BN>();
@@ -616,11 +619,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             RopeCtx<8> cx;
                             if constexpr (ROPE) rope_prefetch<8>(ep, cx, token0, nv, ga, ga < a_rows);
                             if (ga < a_rows)
-                                for (int s = 0; s < nparts; ++s) {
-                                    const float* src = ep.partial + (size_t)s * plane + (size_t)token0 * ep.features + ga;
+                                for (int s0 = 0; s0 < nparts; s0 += 4) {   // four parts' loads in flight, added in part order
+                                    float t[4][8];
 #pragma unroll
-                                    for (int c = 0; c < 8; ++c)
-                                        if (c < nv) vals[c] += __ldcg(src + (size_t)c * ep.features);
+                                    for (int j = 0; j < 4; ++j) {
+                                        const float* src = ep.partial + (size_t)(s0 + j) * plane + (size_t)token0 * ep.features + ga;
+#pragma unroll
+                                        for (int c = 0; c < 8; ++c)
+                                            t[j][c] = (s0 + j < nparts && c < nv) ? __ldcg(src + (size_t)c * ep.features) : 0.f;
+                                    }
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j)
+                                        if (s0 + j < nparts) {
+#pragma unroll
+                                            for (int c = 0; c < 8; ++c) vals[c] += t[j][c];
+                                        }
                                 }
                             if constexpr (ROPE) rope_finish<8>(ep, cx, vals, token0, nv, ga < a_rows);
                             else emit<8, false>(ep, nullptr, vals, token0, nv, ga, ga < a_rows);
