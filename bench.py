@@ -410,17 +410,17 @@ def main():
                 step_points[f"step_{w}_tokens_ms"] = time_prompt_step(w)[0]
 
     # ---------------- decode at context C: caches of B requests filled with random keys and values
-    def fill_cache(B):
+    def fill_cache(B, context=None):
         for rid in list(eng.cache.live):
             eng.cache.free_request(rid)
         for g in eng.cache.groups:
             g.pool.normal_(0.0, 0.5)
         for b in range(B):
             eng.cache.add_request(("seq", b))
-            eng.cache.append(("seq", b), args.context - 1)
+            eng.cache.append(("seq", b), (context or args.context) - 1)
 
-    def decode_device(B, steps, warmup):
-        fill_cache(B)
+    def decode_device(B, steps, warmup, context=None):
+        fill_cache(B, context)
         toks = torch.randint(0, V, (B,), generator=gen).tolist()
 
         def one():
@@ -438,6 +438,8 @@ def main():
         return s.elapsed_time(e) / steps, (ops.launches - l0)
 
     def decode_e2e(B, steps, warmup):
+        """Every step: host token ids in (they go to the device in the step's packed buffer, from pinned
+        memory), host token ids out (read back before the next step is made)."""
         fill_cache(B)
         toks = torch.randint(0, V, (B,), generator=gen).tolist()
         pos = args.context - 1
@@ -451,6 +453,55 @@ def main():
             pos += 1
         torch.cuda.synchronize()
         return (time.perf_counter() - t0) * 1e3 / steps
+
+    def decode_e2e_pipelined(B, steps, warmup):
+        """The same loop as a server runs it: step n + 1 is queued (its packed buffer from pinned memory,
+        its token ids taken on the device from step n's sampler) before step n's tokens are read on the
+        host; every step's tokens still reach the host, one step late."""
+        from blackwellllm_b200 import FROM_LAST
+        fill_cache(B)
+        toks = torch.randint(0, V, (B,), generator=gen).tolist()
+        pos = args.context - 1
+        pending = llm.forward_batch_async([DecodeRequest(b, toks[b], pos) for b in range(B)])
+        got = 0
+        for i in range(warmup + steps):
+            if i == warmup:
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+            pos += 1
+            nxt = llm.forward_batch_async([DecodeRequest(b, FROM_LAST, pos) for b in range(B)])
+            got += len(pending.result())
+            pending = nxt
+        pending.result()
+        torch.cuda.synchronize()
+        assert got == (warmup + steps) * B
+        return (time.perf_counter() - t0) * 1e3 / steps
+
+    def generate_decode_steps(B, prompt_len, pipeline, steps=40):
+        """Wall-clock ms per decode-only step of ``generate()``'s own loop (scheduler, sampler, read-back of
+        the tokens) at batch B: what the host adds shows against the device-only time of the same step."""
+        from blackwellllm_b200 import SamplingParams
+        for rid in list(eng.cache.live):
+            eng.cache.free_request(rid)
+        llm.pipeline = pipeline
+        sp = SamplingParams(temperature=0.0, max_new_tokens=steps + 20, ignore_eos=True)
+        for b in range(B):
+            llm.add_request(torch.randint(0, V, (prompt_len,), generator=gen).tolist(), sp)
+        sch = llm.scheduler
+        while sch.waiting or any(r.remaining > 1 for r in sch.running):
+            llm.step()
+        for _ in range(8):      # the first decode step of this batch size records its graph
+            llm.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            llm.step()
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3 / steps
+        while sch.has_work():
+            llm.step()
+        llm.pipeline = True
+        return ms
 
     points = dict(step_points)
     if args.only == "prefill":
@@ -468,9 +519,16 @@ def main():
     ms_step, launches = decode_device(B, args.steps, args.warmup)
     clocks = sampler.stop()
     e2e_ms = decode_e2e(B, args.steps, args.warmup)
+    e2e_pipe_ms = decode_e2e_pipelined(B, args.steps, args.warmup)
     graph_launches = getattr(eng, "graph_kernel_count", lambda n: 0)(B)
     if graph_launches:
         launches = graph_launches * args.steps
+
+    # what the host adds to a decode step of generate() at batch 32 (short contexts, where it weighs most)
+    if 32 <= max_b and args.only == "all":
+        points["generate_b32_ms_per_step"] = generate_decode_steps(32, 512, True)
+        points["generate_b32_ms_per_step_unpipelined"] = generate_decode_steps(32, 512, False)
+        points["generate_b32_device_ms_per_step"] = decode_device(32, 20, args.warmup, context=512 + 40)[0]
 
     # the share of each kernel in a decode step: one more step, uncaptured and timed launcher by launcher
     fill_cache(B)
@@ -494,6 +552,9 @@ def main():
         "e2e": {"value": B / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 4 * (3 * B + (B + 1) + 3 * B + B + B * blocks_w),
                 "d2h_bytes_per_step": 4 * B},
+        # a server's loop: the next step is queued before this step's tokens are read (they are fed on the device)
+        "e2e_pipelined": {"value": B / (e2e_pipe_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_pipe_ms,
+                          "h2d_bytes_per_step": 4 * (3 * B + (B + 1) + 3 * B + B + B * blocks_w), "d2h_bytes_per_step": 4 * B},
         "gpu_launches": launches,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",

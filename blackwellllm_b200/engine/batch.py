@@ -89,9 +89,16 @@ class BatchBuilder:
         """A pinned int32 buffer of at least ``n`` words from the ring (the one :meth:`finish` sends)."""
         return self._pinned(n)
 
-    def send(self, host: torch.Tensor, total: int, into: Optional[torch.Tensor] = None) -> torch.Tensor:
+    @property
+    def last_ring_slot(self) -> int:
+        """The ring slot of the buffer that :meth:`pinned` handed out last."""
+        return self._slot
+
+    def send(self, host: torch.Tensor, total: int, into: Optional[torch.Tensor] = None,
+             ring_slot: Optional[int] = None) -> torch.Tensor:
         """Copies the first ``total`` words of the pinned buffer to the device (into ``into``, a buffer of
-        exactly that size at a fixed address, or a new tensor) and marks the ring slot busy until then."""
+        exactly that size at a fixed address, or a new tensor) and marks the ring slot busy until then
+        (``ring_slot``: the buffer's slot if it is not the one handed out last)."""
         if into is not None:
             if into.numel() != total:
                 raise ValueError(f"static batch buffer holds {into.numel()} words, this batch needs {total}")
@@ -100,9 +107,10 @@ class BatchBuilder:
             dev = torch.empty(total, dtype=torch.int32, device=self.device)
         dev.copy_(host[:total], non_blocking=True)
         if self.device.type == "cuda":
-            ev = self._events[self._slot] or torch.cuda.Event()
+            i = self._slot if ring_slot is None else ring_slot
+            ev = self._events[i] or torch.cuda.Event()
             ev.record()
-            self._events[self._slot] = ev
+            self._events[i] = ev
         return dev
 
     def finish(self, host: torch.Tensor, T: int, R: int, n_want: int, widths: Dict[int, int], rids: List[object],

@@ -61,6 +61,17 @@ def require_cuda(device: torch.device) -> None:
                           "there is no CPU path")
 
 
+@dataclass
+class PreparedDecode:
+    """A decode-only step whose bookkeeping is done and whose token ids are still to come."""
+    rids: list
+    host: torch.Tensor        # the packed step in pinned memory; its first len(rids) words are the token ids
+    total: int
+    slot: dict                # the graph of this batch size and its device buffer
+    ring_slot: int            # where the pinned buffer sits in the uploader's ring
+    rids_done: bool = False   # launched or cancelled
+
+
 class Engine:
     def __init__(self, config: ModelConfig, model: DecoderModel, options: EngineOptions):
         self.config = config
@@ -74,6 +85,7 @@ class Engine:
                                   dtype=self.dtype, device=self.device)
         self._builder = BatchBuilder(self.device)
         self._graphs: Dict[int, dict] = {}
+        self._grown = None
         longest = options.max_context or num_pages * options.page_size
         self._graph_width = -(-longest // options.page_size)
         self.steps_run = 0
@@ -157,7 +169,7 @@ class Engine:
 
     # ------------------------------------------------------------------ the step
     def prepare(self, entries: Sequence[StepEntry], min_blocks: int = 0, into=None,
-                replay_width: Optional[int] = None) -> Optional[StepBatch]:
+                replay_width: Optional[int] = None, defer_send: bool = False):
         """Checks the entries, reserves pages for all their tokens (all or nothing)
         and uploads the batch.  The checks, the page bookkeeping and the packing of the
         step's buffer are one call into the C++ host runtime."""
@@ -205,11 +217,14 @@ class Engine:
             cache.adopt(entries[i].rid, int(handles[i]))
             cache.zero_state(int(new_slots[k]))
             k += 1
+        self._grown = (entries, was_new)     # what to take back if the model fails after this point
         widths = {g: int(meta[4 + g]) for g in range(G)}
         if replay_width is not None:
             # a graph replay: the captured kernels read the buffer at its fixed address, no views needed
             if any(w != replay_width for w in widths.values()):
                 raise EngineError("a request outgrew max_context: its block table no longer fits the graph")
+            if defer_send:
+                return host, int(total)     # the caller sends it later (a step prepared ahead)
             self._builder.send(host, int(total), into)
             return None
         return self._builder.finish(host, T, R, W, widths, rids, into)
@@ -258,7 +273,7 @@ class Engine:
                 return None
         return len(entries)
 
-    def _step_graph(self, entries: Sequence[StepEntry], R: int) -> torch.Tensor:
+    def _step_graph(self, entries: Sequence[StepEntry], R: int, token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         width = self._graph_width
         slot = self._graphs.get(R)
         if slot is None:
@@ -269,6 +284,8 @@ class Engine:
             self._graphs[R] = slot
         if slot["graph"] is not None:
             self.prepare(entries, min_blocks=width, into=slot["buf"], replay_width=width)
+            if token_source is not None:
+                slot["buf"][:R].copy_(token_source)     # the token ids lead the packed layout
             slot["graph"].replay()
             return slot["logits"]
         # The first step of this batch size: the model runs ONCE, uncaptured, and that run is the
@@ -278,6 +295,8 @@ class Engine:
         if any(t.shape[1] != width for t in batch.block_tables.values()):
             raise EngineError("a request outgrew max_context: its block table no longer fits the graph")
         batch.static_bound = width * self.cache.page_size
+        if token_source is not None:
+            batch.token_ids.copy_(token_source)
         from ..kernels import ops
         logits = self.model.forward(batch, self.cache.views)
         torch.cuda.synchronize(self.device)
@@ -296,10 +315,69 @@ class Engine:
         slot = self._graphs.get(batch_size)
         return slot["kernels"] if slot else 0
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    # ------------------------------------------------------------------ a decode step prepared ahead
+    # While the GPU runs step n, the host can already do step n + 1's bookkeeping if it is a decode-only
+    # step of known requests: check, reserve pages, grow the requests, pack block tables, positions and
+    # lengths into pinned memory.  Only the token ids are missing (they are being sampled).  Once they are
+    # known they are written into the packed buffer and the step is launched: one small copy and a graph
+    # replay stand between the read-back of step n's tokens and the start of step n + 1.
+    def prepare_decode_ahead(self, rids: Sequence[object]) -> Optional["PreparedDecode"]:
+        """Reserves and packs a step of one token (still unknown) for each request.  None if such a
+        step cannot be prepared ahead: no captured graph for this batch size yet, a cache with
+        fixed-size state (a reservation there cannot be taken back), or no pages (the scheduler then
+        decides whom to preempt).  The requests are longer by one token until the step is launched
+        or cancelled."""
+        R = len(rids)
+        slot = self._graphs.get(R)
+        if (slot is None or slot["graph"] is None or self.cache._states
+                or self._graph_key([StepEntry(r, [0], [0]) for r in rids]) != R):
+            return None
+        entries = [StepEntry(r, [0], [0]) for r in rids]
+        try:
+            host, total = self.prepare(entries, min_blocks=self._graph_width, into=slot["buf"],
+                                       replay_width=self._graph_width, defer_send=True)
+        except (OutOfPages, EngineError):
+            return None
+        return PreparedDecode(list(rids), host, total, slot, self._builder.last_ring_slot)
+
+    def launch_prepared(self, prep: "PreparedDecode", tokens: Sequence[int]) -> torch.Tensor:
+        """Fills in the tokens of a step prepared ahead and runs it (a graph replay)."""
+        V = self.config.vocab_size
+        if len(tokens) != len(prep.rids) or any(not 0 <= int(t) < V for t in tokens):
+            self.cancel_prepared(prep)
+            raise EngineError(f"a prepared step needs one token id in [0, {V}) per request")
+        prep.host[:len(tokens)] = torch.as_tensor(list(tokens), dtype=torch.int32)   # token ids lead the packed layout
+        try:
+            with torch.cuda.device(self.device):
+                self._builder.send(prep.host, prep.total, prep.slot["buf"], ring_slot=prep.ring_slot)
+                prep.slot["graph"].replay()
+        except BaseException:
+            self.cancel_prepared(prep)
+            raise
+        prep.rids_done = True
+        self.cache.release_passed_many(prep.rids)
+        self.steps_run += 1
+        self.tokens_run += len(prep.rids)
+        return prep.slot["logits"]
+
+    def cancel_prepared(self, prep: "PreparedDecode") -> None:
+        """Takes a prepared step back: every request that is still live loses the token it was grown by."""
+        if prep.rids_done:
+            return
+        prep.rids_done = True
+        for rid in prep.rids:
+            if self.cache.has(rid):
+                self.cache.truncate(rid, self.cache.length(rid) - 1)
+
+    def step(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs one batch; returns float32 logits [wanted, vocab] on the device, in the
         order of the entries and of each entry's ``want``.  The result of a graph
         replay is overwritten by the next step of the same batch size.
+
+        ``token_source``: an int32 tensor on the device with one token id per token of the step, used
+        INSTEAD of the entries' own ids (which are then placeholders): the tokens a sampler has just
+        chosen go into the next step without a round trip through the host.  Their range is the
+        sampler's responsibility (it chooses among the vocabulary).
 
         A step that fails changes nothing: a refusal (bad entries, no pages) comes before
         anything is reserved, and if the model raises after the requests have grown, they are
@@ -308,38 +386,44 @@ class Engine:
         src/core/engine_prefill_coordinator.cpp:296-304)."""
         if not entries:
             return torch.empty((0, self.config.vocab_size), dtype=torch.float32, device=self.device)
-        cache = self.cache
-        before = [(e.rid, cache.length(e.rid) if cache.has(e.rid) else None) for e in entries]
+        self._grown = None
         try:
             with torch.cuda.device(self.device):
                 R = self._graph_key(entries)
                 if R is not None:
-                    logits = self._step_graph(entries, R)
+                    logits = self._step_graph(entries, R, token_source)
                     T = R
                 else:
                     batch = self.prepare(entries)
+                    if token_source is not None:
+                        batch.token_ids.copy_(token_source)
                     logits = self.model.forward(batch, self.cache.views)
                     T = batch.T
         except BaseException:
-            self._roll_back(before)
+            self._roll_back()
             raise
         self.cache.release_passed_many([e.rid for e in entries])
         self.steps_run += 1
         self.tokens_run += T
         return logits
 
-    def _roll_back(self, before) -> None:
+    def _roll_back(self) -> None:
         """Puts every request of a failed step back to its length before the step; a request
         the step created is freed.  A request whose fixed-size state may have been advanced
-        cannot go back by part of its length: it is freed too (its owner starts it again)."""
+        cannot go back by part of its length: it is freed too (its owner starts it again).
+        Nothing to do if the step failed before the requests were grown."""
+        grown, self._grown = self._grown, None
+        if grown is None:
+            return
         cache = self.cache
-        for rid, old in dict(before).items():
-            if not cache.has(rid):
+        entries, was_new = grown
+        for e, new in zip(entries, was_new):
+            if not cache.has(e.rid):
                 continue
-            if old is None:
-                cache.free_request(rid)
-            elif cache.length(rid) != old:
-                try:
-                    cache.truncate(rid, old)
-                except ValueError:
-                    cache.free_request(rid)
+            if new:
+                cache.free_request(e.rid)
+                continue
+            try:
+                cache.truncate(e.rid, cache.length(e.rid) - len(e.tokens))
+            except ValueError:
+                cache.free_request(e.rid)

@@ -56,6 +56,43 @@ class GenerationResult:
     preemptions: int = 0
 
 
+_GREEDY = SamplingParams(temperature=0.0, top_p=1.0)
+FROM_LAST = -1   # DecodeRequest.token_id: the token that the previous forward_batch sampled for the sequence
+
+
+class PendingTokens:
+    """Tokens that the device is still choosing: the read-back into pinned memory is queued behind the
+    sampler; :meth:`result` waits for it."""
+
+    def __init__(self, picked: torch.Tensor):
+        self._host = torch.empty(picked.shape, dtype=picked.dtype, pin_memory=picked.is_cuda)
+        self._host.copy_(picked, non_blocking=True)
+        self._event = None
+        if picked.is_cuda:
+            self._event = torch.cuda.Event()
+            self._event.record()
+
+    def result(self) -> List[int]:
+        if self._event is not None:
+            self._event.synchronize()
+        return self._host.tolist()
+
+
+class _RowsOf:
+    """The rows of a step's logits by sequence, looked up when asked for (a graph replay's logits are
+    overwritten by the next step of the same batch size: ask before it)."""
+
+    def __init__(self, logits: torch.Tensor, seqs: Sequence[int]):
+        self._logits, self._index = logits, {s: i for i, s in enumerate(seqs)}
+
+    def get(self, seq_id, default=None):
+        i = self._index.get(seq_id)
+        return default if i is None else self._logits[i]
+
+    def pop(self, seq_id, default=None):
+        self._index.pop(seq_id, None)
+
+
 class BlackwellEngine:
     def __init__(self, model: Optional[str] = None, request: Optional[InferenceConfig] = None, *,
                  config: Optional[Mapping[str, object]] = None, random_seed: int = 0, random_std: float = 0.02,
@@ -96,6 +133,9 @@ class BlackwellEngine:
         self.chunk = chunk
         self.max_batch_tokens = max_batch_tokens
         self._last_logits: Dict[int, torch.Tensor] = {}   # rows of the LAST step's logits, by sequence
+        self._fed = None            # (sequences, their sampled tokens on the device) of the last forward_batch
+        self._ahead = None          # (plan, prepared step) of the next scheduler step, made while the last one ran
+        self.pipeline = True        # prepare decode steps ahead (see step())
         self.scheduler = self._new_scheduler()
 
     def _new_scheduler(self) -> Scheduler:
@@ -112,9 +152,16 @@ class BlackwellEngine:
     def _seq(self, seq_id: int):
         return ("seq", int(seq_id))
 
+    def _drop_ahead(self) -> None:
+        """Takes back a scheduler step that was prepared ahead (another kind of call comes first)."""
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None:
+            self.engine.cancel_prepared(ahead[1])
+
     def _reconcile(self, seq_id: int, pos: int) -> None:
         """pos < length rewinds to pos; pos > length is a gap and an error
         (src/core/kv_cache/paged_kv_manager.cpp:72-92)."""
+        self._drop_ahead()
         rid = self._seq(seq_id)
         cache = self.engine.cache
         length = cache.length(rid) if cache.has(rid) else 0
@@ -187,16 +234,53 @@ class BlackwellEngine:
 
     def forward_batch(self, requests: Sequence[DecodeRequest]) -> List[int]:
         """One token each of distinct sequences, greedy (src/core/engine.cpp:1576-1616)."""
+        return self.forward_batch_async(requests).result()
+
+    def forward_batch_async(self, requests: Sequence[DecodeRequest]) -> "PendingTokens":
+        """:meth:`forward_batch` without waiting for its tokens: the step and the read-back of the
+        sampled tokens are queued on the device and a handle is returned; ``handle.result()`` waits
+        and gives the tokens.  A request whose ``token_id`` is :data:`FROM_LAST` takes the token that
+        the previous ``forward_batch`` call sampled for its sequence, straight from the device (all
+        requests of the call, the same sequences in the same order as in that call).  So a decode loop
+        can queue step n + 1 before it reads step n's tokens, and the device never waits for the host:
+
+            pending = llm.forward_batch_async([DecodeRequest(s, first[s], pos) for s in seqs])
+            while ...:
+                pos += 1
+                nxt = llm.forward_batch_async([DecodeRequest(s, FROM_LAST, pos) for s in seqs])
+                tokens = pending.result()          # step n's tokens, while step n + 1 runs
+                pending = nxt
+        """
         if not requests:
             raise EngineError("forward_batch needs at least one request")
+        self._drop_ahead()
         seqs = [r.seq_id for r in requests]
         if len(set(seqs)) != len(seqs):
             raise EngineError("forward_batch: a sequence appears twice")
+        fed = [r.token_id == FROM_LAST for r in requests]
+        source = None
+        if any(fed):
+            if not all(fed) or self._fed is None or self._fed[0] != seqs:
+                raise EngineError("forward_batch: FROM_LAST needs every request of the call to use it, for the "
+                                  "same sequences in the same order as the call before")
+            source = self._fed[1]
+        cache, limit = self.engine.cache, self.request.max_context_length
+        entries = []
         for r in requests:
-            self._reconcile(r.seq_id, r.pos)
-        logits = self.engine.step([StepEntry(self._seq(r.seq_id), [r.token_id], [0]) for r in requests])
-        self._last_logits = {s: logits[i] for i, s in enumerate(seqs)}
-        return self._pick(logits, seqs, 0.0, 1.0)
+            rid = ("seq", int(r.seq_id))
+            length = cache.length(rid) if cache.has(rid) else 0
+            if r.pos != length:
+                if r.pos > length:
+                    raise EngineError(f"sequence {r.seq_id}: position {r.pos} leaves a gap after its {length} cached tokens")
+                cache.truncate(rid, r.pos)
+            if r.pos >= limit:
+                raise EngineError(f"position {r.pos} is outside max_context_length {limit}")
+            entries.append(StepEntry(rid, [0 if source is not None else r.token_id], [0]))
+        logits = self.engine.step(entries, token_source=source)
+        self._last_logits = _RowsOf(logits, seqs)
+        picked = self.sampler.sample_async(logits, [_GREEDY] * len(seqs), seqs, seqs)   # greedy, as the reference's batched decode
+        self._fed = (seqs, picked)
+        return PendingTokens(picked)
 
     def rewind(self, seq_id: int, pos: int) -> None:
         rid = self._seq(seq_id)
@@ -221,24 +305,73 @@ class BlackwellEngine:
         return self.scheduler.add_request(prompt_token_ids, params).rid
 
     def step(self) -> List[GenerationResult]:
-        """One scheduler step; returns the requests that finished in it."""
-        plan = self.scheduler.plan()
-        if not plan.entries:
-            return []
-        entries = [StepEntry(e.request.rid, e.tokens, [len(e.tokens) - 1] if e.samples else [])
-                   for e in plan.entries]
+        """One scheduler step; returns the requests that finished in it.
+
+        While the GPU runs a step after which every running request decodes, the host prepares the
+        next one (the same requests, one token each: pages reserved, block tables and positions
+        packed), so that only the sampled tokens have to be filled in before it is launched.  If the
+        step turns out differently (a request ended on an end-of-sequence token, one arrived), what
+        was prepared is taken back and the step is planned the ordinary way."""
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None and (self.scheduler.waiting or [e.request for e in ahead[0].entries] != self.scheduler.running):
+            self.engine.cancel_prepared(ahead[1])
+            ahead = None
+        if ahead is not None:
+            plan, prep = ahead
+            logits = self.engine.launch_prepared(prep, [e.tokens[0] for e in plan.entries])
+        else:
+            plan = self.scheduler.plan()
+            if not plan.entries:
+                return []
+            entries = [StepEntry(e.request.rid, e.tokens, [len(e.tokens) - 1] if e.samples else [])
+                       for e in plan.entries]
+            logits = self.engine.step(entries)
         self._last_logits = {}
-        logits = self.engine.step(entries)
         samplers = [e.request for e in plan.entries if e.samples]
         sampled: Dict[int, int] = {}
+        picked = None
         if samplers:
-            toks = self.sampler.sample(logits, [r.params for r in samplers], [r.seed for r in samplers],
-                                       [len(r.generated) for r in samplers], [r.generated for r in samplers])
-            sampled = {r.rid: t for r, t in zip(samplers, toks)}
-        done = self.scheduler.commit(plan, sampled)
+            picked = self.sampler.sample_async(logits, [r.params for r in samplers], [r.seed for r in samplers],
+                                               [len(r.generated) for r in samplers], [r.generated for r in samplers])
+        nxt = self._prepare_ahead(plan)        # host work while the GPU runs this step
+        if picked is not None:
+            sampled = {r.rid: t for r, t in zip(samplers, picked.tolist())}     # waits for the step
+        try:
+            done = self.scheduler.commit(plan, sampled)
+        except BaseException:
+            if nxt is not None:
+                self.engine.cancel_prepared(nxt[1])
+            raise
+        if nxt is not None:
+            if done or self.scheduler.waiting:
+                self.engine.cancel_prepared(nxt[1])
+            else:
+                for e in nxt[0].entries:    # the tokens that were being sampled while the step was prepared
+                    e.tokens = [sampled[e.request.rid]]
+                self._ahead = nxt
         for r in done:   # handed to the caller here: a long-lived engine keeps no finished request
             self.scheduler.finished.pop(r.rid, None)
         return [GenerationResult(r.rid, r.prompt, r.generated, r.finish_reason, r.preemptions) for r in done]
+
+    def _prepare_ahead(self, plan):
+        """The next step, prepared while this one runs, if it is certain to be "one token for each
+        running request": every running request samples in this step, none of them reaches its limit
+        of new tokens or of context with the token being sampled, nobody waits.  (A request may still
+        end on an end-of-sequence token: then what is prepared here is cancelled.)"""
+        sch = self.scheduler
+        if not self.pipeline or sch.waiting or not plan.entries or len(plan.entries) != len(sch.running):
+            return None
+        for e in plan.entries:
+            r = e.request
+            if not e.samples or len(r.generated) + 1 >= r.params.max_new_tokens:
+                return None
+            if sch.max_context is not None and len(r.prompt) + len(r.generated) + 1 >= sch.max_context:
+                return None
+        prep = self.engine.prepare_decode_ahead([r.rid for r in sch.running])
+        if prep is None:
+            return None
+        from .scheduler import PlannedEntry, StepPlan
+        return StepPlan([PlannedEntry(r, [0], True) for r in sch.running], []), prep
 
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[GenerationResult]:

@@ -273,6 +273,51 @@ def test_position_addressed_calls(folders):
     assert llm.engine.cache.free_pages() == [g.num_pages for g in llm.engine.cache.groups]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_forward_batch_async_feeds_the_sampled_tokens_on_the_device(folders, dtype):
+    """A decode loop that queues step n + 1 before it reads step n's tokens (FROM_LAST: the token ids go
+    from the sampler into the next step on the device) gives the tokens of the loop that waits every step."""
+    from blackwellllm_b200 import FROM_LAST, DecodeRequest, EngineError
+    raw, _, page = tiny.CONFIGS["qwen"]
+    folder = folders[("qwen", dtype)]
+    llm = make(folder, dtype, page_size=page)
+    prompts = {0: tiny.prompt(20, raw["vocab_size"], 3), 2: tiny.prompt(11, raw["vocab_size"], 4), 5: tiny.prompt(33, raw["vocab_size"], 6)}
+
+    def decode(pipelined, steps=7):
+        first = {s: llm.prefill(p, 0, 0.0, 1.0, seq_id=s) for s, p in prompts.items()}
+        seqs = list(prompts)
+        out = {s: [first[s]] for s in seqs}
+        pos = {s: len(prompts[s]) for s in seqs}
+        if not pipelined:
+            for _ in range(steps):
+                toks = llm.forward_batch([DecodeRequest(s, out[s][-1], pos[s]) for s in seqs])
+                for s, t in zip(seqs, toks):
+                    out[s].append(t); pos[s] += 1
+            return out
+        pending = llm.forward_batch_async([DecodeRequest(s, first[s], pos[s]) for s in seqs])
+        for _ in range(steps - 1):
+            for s in seqs:
+                pos[s] += 1
+            nxt = llm.forward_batch_async([DecodeRequest(s, FROM_LAST, pos[s]) for s in seqs])
+            for s, t in zip(seqs, pending.result()):
+                out[s].append(t)
+            pending = nxt
+        for s, t in zip(seqs, pending.result()):
+            out[s].append(t)
+        return out
+
+    waited = decode(False)
+    assert decode(True) == waited
+    if dtype == "float32":
+        W = load_plain_weights(folder)
+        for s, p in prompts.items():
+            assert waited[s] == plain_greedy(raw, W, p, 8)
+    with pytest.raises(EngineError, match="FROM_LAST"):
+        llm.forward_batch_async([DecodeRequest(2, FROM_LAST, 18), DecodeRequest(0, FROM_LAST, 27), DecodeRequest(5, FROM_LAST, 40)])
+    with pytest.raises(EngineError, match="FROM_LAST"):
+        llm.forward_batch_async([DecodeRequest(0, FROM_LAST, 27), DecodeRequest(2, 3, 18), DecodeRequest(5, FROM_LAST, 40)])
+
+
 def test_sampled_tokens_of_the_position_addressed_calls_do_not_depend_on_what_ran_before(folders):
     """Temperature 1: the same prompt from position 0 on the same sequence id gives the same tokens again
     (the draw is a function of seed, sequence and position, not of how many draws came before)."""

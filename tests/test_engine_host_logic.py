@@ -266,9 +266,12 @@ class ArgmaxSampler:
     def __init__(self, device):
         pass
 
-    def sample(self, logits, params, seeds, draw_index, generated=None):
+    def sample_async(self, logits, params, seeds, draw_index, generated=None):
         assert all(p.greedy for p in params)
-        return logits.argmax(dim=1).tolist()
+        return logits.argmax(dim=1)
+
+    def sample(self, logits, params, seeds, draw_index, generated=None):
+        return self.sample_async(logits, params, seeds, draw_index, generated).tolist()
 
 
 def rule_continuation(prompt, n, vocab):
@@ -333,6 +336,96 @@ def test_generate_with_too_few_pages_preempts_and_still_follows_the_rule(llm):
     assert e.scheduler.stats.preemptions > 0 and sum(r.preemptions for r in res) == e.scheduler.stats.preemptions
     assert e.engine.cache.free_pages() == [7]
     e.engine.cache.check_invariants()
+
+
+def test_decode_steps_prepared_ahead_give_the_same_tokens_and_are_taken_back_on_a_surprise(monkeypatch):
+    """generate() prepares the next decode step while the current one runs.  With stand-ins for the graph
+    (what a capture records runs at replay) and a model that follows a rule: the tokens are those of the
+    unpipelined run; a request that ends on an end-of-sequence token (which nobody could know ahead)
+    makes the engine take the prepared step back, and no page or slot is lost."""
+    import dataclasses
+
+    from blackwellllm_b200 import BlackwellEngine, InferenceConfig, SamplingParams
+    from blackwellllm_b200.engine import llm as llm_module
+    monkeypatch.setattr(torch.cuda, "device", lambda d: contextlib.nullcontext())
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+    capturing = []
+
+    class FakeGraph:
+        def __init__(self):
+            self.recorded = []
+
+        def replay(self):
+            for fn in self.recorded:
+                fn()
+
+    @contextlib.contextmanager
+    def fake_capture(graph):
+        capturing.append(graph)
+        try:
+            yield
+        finally:
+            capturing.pop()
+    monkeypatch.setattr(torch.cuda, "CUDAGraph", FakeGraph)
+    monkeypatch.setattr(torch.cuda, "graph", fake_capture)
+
+    class CapturableRuleModel(RuleModel):
+        def forward(self, batch, views):
+            out = torch.zeros((len(batch.logit_rows), self.vocab), dtype=torch.float32)
+
+            def run():
+                out.zero_()
+                for i, t in enumerate(batch.logit_rows.tolist()):
+                    out[i, (int(batch.token_ids[t]) + int(batch.positions[t])) % self.vocab] = 1.0
+            if capturing:
+                capturing[-1].recorded.append(run)
+            else:
+                self.batches.append(batch)
+                run()
+            return out
+
+    engines = []
+
+    def from_config(raw, seed=0, std=0.02, options=None):
+        cfg = parse_config(raw)
+        engines.append(Engine(cfg, CapturableRuleModel(cfg.vocab_size), dataclasses.replace(options, device="cpu")))
+        return engines[-1]
+    monkeypatch.setattr(llm_module.Engine, "from_config", staticmethod(from_config))
+    monkeypatch.setattr(llm_module, "Sampler", ArgmaxSampler)
+
+    def run(pipeline, eos):
+        raw = dict(tiny.CONFIGS["llama"][0], eos_token_id=eos)
+        e = BlackwellEngine(None, InferenceConfig(max_context_length=96, max_batch_size=3), config=raw, page_size=8,
+                            max_batch_tokens=32, cuda_graphs=True)
+        e.pipeline = pipeline
+        launched = {"ahead": 0, "cancelled": 0}
+        real_launch, real_cancel = e.engine.launch_prepared, e.engine.cancel_prepared
+
+        def launch(prep, tokens):
+            launched["ahead"] += 1
+            return real_launch(prep, tokens)
+
+        def cancel(prep):
+            launched["cancelled"] += 0 if prep.rids_done else 1
+            return real_cancel(prep)
+        e.engine.launch_prepared, e.engine.cancel_prepared = launch, cancel
+        prompts = [[3, 4, 5], list(range(10, 27)), [7, 8]]
+        res = e.generate(prompts, [SamplingParams(temperature=0.0, max_new_tokens=n) for n in (20, 12, 16)])
+        assert e.engine.cache.free_pages() == [3 * 12] and e.engine.cache.slots.num_free == 3
+        e.engine.cache.check_invariants()
+        return [(r.token_ids, r.finish_reason) for r in res], launched
+
+    V = tiny.CONFIGS["llama"][0]["vocab_size"]
+    plain, n0 = run(False, eos=None)
+    piped, n1 = run(True, eos=None)
+    assert piped == plain and n0["ahead"] == 0 and n1["ahead"] >= 10       # most decode steps were prepared ahead
+    assert [t for t, _ in plain][0] == rule_continuation([3, 4, 5], 20, V)
+    # the sixth token of the first request is now an end-of-sequence token: nobody knows before it is sampled
+    eos = plain[0][0][5]
+    plain_eos, _ = run(False, eos=eos)
+    piped_eos, n2 = run(True, eos=eos)
+    assert piped_eos == plain_eos and plain_eos[0][1] == "eos" and len(plain_eos[0][0]) <= 6
+    assert n2["cancelled"] >= 1 and n2["ahead"] >= 5
 
 
 def test_position_addressed_calls_reconcile_the_cache(llm):
