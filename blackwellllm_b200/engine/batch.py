@@ -94,6 +94,14 @@ class BatchBuilder:
         """The ring slot of the buffer that :meth:`pinned` handed out last."""
         return self._slot
 
+    def mark_sent(self, ring_slot: int) -> None:
+        """A copy from the buffer in ``ring_slot`` was queued on the current stream by someone else: the
+        slot is busy until that copy is done."""
+        if self.device.type == "cuda":
+            ev = self._events[ring_slot] or torch.cuda.Event()
+            ev.record()
+            self._events[ring_slot] = ev
+
     def send(self, host: torch.Tensor, total: int, into: Optional[torch.Tensor] = None,
              ring_slot: Optional[int] = None) -> torch.Tensor:
         """Copies the first ``total`` words of the pinned buffer to the device (into ``into``, a buffer of

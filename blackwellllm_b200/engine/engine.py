@@ -51,6 +51,7 @@ class EngineOptions:
     max_context: Optional[int] = None  # longest request; None: what the pool holds
     ignore_unexpected: bool = False  # tensors of a checkpoint that the model does not use: pass over, no error
     cuda_graphs: bool = True         # replay decode-only steps from a CUDA graph per batch size
+    native_decode: bool = True       # greedy decode-only steps of live requests go through the C entry point
     max_graph_batch: int = 256
     device: str = "cuda:0"
 
@@ -90,6 +91,7 @@ class Engine:
         self._graph_width = -(-longest // options.page_size)
         self.steps_run = 0
         self.tokens_run = 0
+        self.native_steps = 0      # steps that went through the C entry point (csrc/decode_step.h)
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -368,6 +370,32 @@ class Engine:
         for rid in prep.rids:
             if self.cache.has(rid):
                 self.cache.truncate(rid, self.cache.length(rid) - 1)
+
+    def decode_native(self, rids: Sequence[object], tokens: Sequence[int], positions: Sequence[int],
+                      token_source: Optional[torch.Tensor] = None, wait: bool = True):
+        """A decode-only greedy step of live requests through the C entry point (``csrc/decode_step.h``):
+        one token each at the given positions (a lower position than a request's length rewinds it first).
+        Returns (logits, sampled tokens on the device, the same in pinned host memory), or None when the
+        step is not one the C path takes (no captured graph of this batch size yet, a request the cache
+        does not hold, a refusal): the caller then takes :meth:`step`, which explains a refusal."""
+        R = len(rids)
+        slot = self._graphs.get(R)
+        if (not self.options.native_decode or slot is None or slot["graph"] is None or self.cache._states
+                or not all(getattr(b.mixer, "graph_safe", True) for b in self.model.blocks)):
+            return None
+        from . import native_step
+        nat = slot.get("native")
+        if nat is None:
+            nat = slot["native"] = native_step.NativeDecodeSlot(self, R, slot)
+        with torch.cuda.device(self.device):
+            rc, host = native_step.decode_step(self, nat, rids, tokens, positions, token_source, wait)
+        if rc != native_step.SUCCESS:
+            return None
+        self.cache.release_passed_many(rids)
+        self.steps_run += 1
+        self.tokens_run += R
+        self.native_steps += 1
+        return slot["logits"], nat.sampled, host
 
     def step(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs one batch; returns float32 logits [wanted, vocab] on the device, in the

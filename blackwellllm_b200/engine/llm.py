@@ -64,11 +64,14 @@ class PendingTokens:
     """Tokens that the device is still choosing: the read-back into pinned memory is queued behind the
     sampler; :meth:`result` waits for it."""
 
-    def __init__(self, picked: torch.Tensor):
-        self._host = torch.empty(picked.shape, dtype=picked.dtype, pin_memory=picked.is_cuda)
-        self._host.copy_(picked, non_blocking=True)
+    def __init__(self, picked: torch.Tensor, host: Optional[torch.Tensor] = None, done: bool = False):
+        """``host``: pinned memory into which the read-back is already queued (``done``: and complete)."""
+        if host is None:
+            host = torch.empty(picked.shape, dtype=picked.dtype, pin_memory=picked.is_cuda)
+            host.copy_(picked, non_blocking=True)
+        self._host = host
         self._event = None
-        if picked.is_cuda:
+        if picked.is_cuda and not done:
             self._event = torch.cuda.Event()
             self._event.record()
 
@@ -234,9 +237,9 @@ class BlackwellEngine:
 
     def forward_batch(self, requests: Sequence[DecodeRequest]) -> List[int]:
         """One token each of distinct sequences, greedy (src/core/engine.cpp:1576-1616)."""
-        return self.forward_batch_async(requests).result()
+        return self.forward_batch_async(requests, wait=True).result()
 
-    def forward_batch_async(self, requests: Sequence[DecodeRequest]) -> "PendingTokens":
+    def forward_batch_async(self, requests: Sequence[DecodeRequest], wait: bool = False) -> "PendingTokens":
         """:meth:`forward_batch` without waiting for its tokens: the step and the read-back of the
         sampled tokens are queued on the device and a handle is returned; ``handle.result()`` waits
         and gives the tokens.  A request whose ``token_id`` is :data:`FROM_LAST` takes the token that
@@ -265,9 +268,19 @@ class BlackwellEngine:
                                   "same sequences in the same order as the call before")
             source = self._fed[1]
         cache, limit = self.engine.cache, self.request.max_context_length
+        rids = [("seq", int(r.seq_id)) for r in requests]
+        # the hot path: one C call does the whole step (see csrc/decode_step.h); it declines what it does
+        # not take (a new sequence, no captured graph yet, any refusal), and the ordinary path below explains
+        native = self.engine.decode_native(rids, [0 if source is not None else r.token_id for r in requests],
+                                           [r.pos for r in requests], source, wait=wait) \
+            if all(0 <= r.pos < limit for r in requests) else None
+        if native is not None:
+            logits, picked, host = native
+            self._last_logits = _RowsOf(logits, seqs)
+            self._fed = (seqs, picked)
+            return PendingTokens(picked, host, done=wait)
         entries = []
-        for r in requests:
-            rid = ("seq", int(r.seq_id))
+        for r, rid in zip(requests, rids):
             length = cache.length(rid) if cache.has(rid) else 0
             if r.pos != length:
                 if r.pos > length:

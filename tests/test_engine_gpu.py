@@ -307,7 +307,12 @@ def test_forward_batch_async_feeds_the_sampled_tokens_on_the_device(folders, dty
         return out
 
     waited = decode(False)
+    assert llm.engine.native_steps >= 5          # once the graph of this batch size exists, the C entry point runs the steps
     assert decode(True) == waited
+    before = llm.engine.native_steps
+    llm.engine.options.native_decode = False     # the same loops through the Python path
+    assert decode(False) == waited and decode(True) == waited and llm.engine.native_steps == before
+    llm.engine.options.native_decode = True
     if dtype == "float32":
         W = load_plain_weights(folder)
         for s, p in prompts.items():
