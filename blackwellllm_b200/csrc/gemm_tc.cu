@@ -682,7 +682,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 template <int BN, bool ROPE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, Epilogue ep, int kb_total, int tiles_a, int tiles_b, int num_work) {
+                 const __grid_constant__ CUtensorMap tmC, Epilogue ep, int kb_total, int kb_per_split, int tiles_a, int tiles_b,
+                 int num_work) {
     constexpr int BH = BN / 2;                       // weight rows this CTA loads
     constexpr int B_BYTES = BH * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -726,7 +727,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            Items items(ep, kb_total, kb_total, tiles, num_work, pair, n_pairs);
+            Items items(ep, kb_total, kb_per_split, tiles, num_work, pair, n_pairs);
             Item im;
             BW_PDL_WAIT();
             while (ok && items.next(im)) {
@@ -738,8 +739,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     const uint32_t a_dst = bw::smem_u32(smem + s * STAGE_BYTES);
                     const uint32_t lead_full = bw::pair_leader_addr(full0 + 8 * s);
                     if (rank == 0) bw::mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);   // the bytes of both CTAs
-                    bw::tma_load_2d_pair(a_dst, &tmA, lead_full, i * BK, tile_a * 2 * BM + (int)rank * BM);
-                    bw::tma_load_2d_pair(a_dst + A_BYTES, &tmB, lead_full, i * BK, tile_b * BN + (int)rank * BH);
+                    bw::tma_load_2d_pair(a_dst, &tmA, lead_full, (im.kb0 + i) * BK, tile_a * 2 * BM + (int)rank * BM);
+                    bw::tma_load_2d_pair(a_dst + A_BYTES, &tmB, lead_full, (im.kb0 + i) * BK, tile_b * BN + (int)rank * BH);
                 }
             }
         }
@@ -747,7 +748,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0 && rank == 0) {
             uint32_t it = 0, n = 0;
             bool ok = true;
-            Items items(ep, kb_total, kb_total, tiles, num_work, pair, n_pairs);
+            Items items(ep, kb_total, kb_per_split, tiles, num_work, pair, n_pairs);
             Item im;
             for (; ok && items.next(im); ++n) {
                 const uint32_t acc = n & 1, accph = (n >> 1) & 1;
@@ -776,7 +777,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         float* stage = staging + (warp - 2) * (32 * 33);
         const int a_rows = ep.tokens, b_rows = ep.features;
         uint32_t n = 0;
-        Items items(ep, kb_total, kb_total, tiles, num_work, pair, n_pairs);
+        Items items(ep, kb_total, kb_per_split, tiles, num_work, pair, n_pairs);
         Item im;
         for (; items.next(im); ++n) {
             const int tile_a = im.tile % tiles_a, tile_b = im.tile / tiles_a;
@@ -785,13 +786,30 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             bw::tc_fence_after();
             const uint32_t lane_addr = tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16);
             const int row0 = tile_a * 2 * BM + (int)rank * BM + quarter * 32;   // first token of this warp
+            float* part = (ep.partial && im.nparts > 1) ? ep.partial + (size_t)im.part * ((size_t)ep.tokens * ep.features) : nullptr;
             int rope_kv = -1;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
                 bw::tmem_ld_32x32(lane_addr + c0, v);
                 bw::tmem_ld_wait();
-                if (ep.tma_add) {
+                if (part) {
+                    // a K split: this item's sums go to its plane of the scratch as they are (the lane's token,
+                    // 32 consecutive features); a second kernel adds the planes in split order
+                    const int token = row0 + lane, f0 = tile_b * BN + c0;
+                    if (token < a_rows && c0 < BN) {
+                        float* dst = part + (size_t)token * ep.features + f0;
+                        if ((ep.features & 3) == 0 && f0 + 32 <= b_rows) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *reinterpret_cast<uint4*>(dst + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                if (f0 + c < b_rows && c0 + c < BN) dst[c] = __uint_as_float(v[c]);
+                        }
+                    }
+                } else if (ep.tma_add) {
                     if constexpr (!ROPE) {
                         const int chunk = c0 / 32;
                         uint8_t* box = (uint8_t*)staging + ((warp - 2) * 2 + (chunk & 1)) * 4096;
@@ -854,6 +872,25 @@ __global__ void splitk_reduce_kernel(Epilogue ep) {
     const size_t plane = (size_t)ep.tokens * ep.features;
     const int width = ep.swiglu ? ep.features / 2 : ep.features;
     const size_t total = (size_t)ep.tokens * width;
+    if (!ep.swiglu && !ep.rope_on && ep.out_type == BW_F32 && (ep.features & 3) == 0 && (ep.ldo & 3) == 0 &&
+        ((uintptr_t)ep.out & 15) == 0) {
+        // float32 result, four features a thread: 16-byte loads of every plane, one 16-byte store
+        const size_t quads = total / 4;
+        for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (size_t)gridDim.x * blockDim.x) {
+            const size_t i = q * 4;
+            const int token = (int)(i / ep.features), j = (int)(i - (size_t)token * ep.features);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < ep.splits; ++s) {
+                const float4 t = *reinterpret_cast<const float4*>(ep.partial + (size_t)s * plane + i);
+                v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+            }
+            if (ep.bias) { v.x += bias_at(ep, j); v.y += bias_at(ep, j + 1); v.z += bias_at(ep, j + 2); v.w += bias_at(ep, j + 3); }
+            float4* o = reinterpret_cast<float4*>((float*)ep.out + (size_t)token * ep.ldo + j);
+            if (ep.accumulate) { const float4 old = *o; v.x = old.x + v.x; v.y = old.y + v.y; v.z = old.z + v.z; v.w = old.w + v.w; }
+            *o = v;
+        }
+        return;
+    }
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int token = (int)(i / width), j = (int)(i - (size_t)token * width);
         if (ep.swiglu) {
@@ -942,7 +979,7 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, con
 
 template <int BN, bool ROPE>
 int launch_pair(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const Epilogue& ep, int kb_total,
-                int tiles_a, int tiles_b, cudaStream_t s) {
+                int kb_per_split, int tiles_a, int tiles_b, cudaStream_t s) {
     constexpr int STAGES = pair_stages<BN>();
     constexpr int smem = STAGES * (A_BYTES + (BN / 2) * BK * 2) + staging_bytes<BN>() + (2 * STAGES + 4) * 8 + 16 + 1024;
     static_assert(smem <= 227 * 1024, "shared memory budget");
@@ -952,10 +989,10 @@ int launch_pair(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
-    const int num_work = tiles_a * tiles_b;
+    const int num_work = tiles_a * tiles_b * (ep.splits > 1 ? ep.splits : 1);
     const int pairs = num_work < NUM_SMS / 2 ? num_work : NUM_SMS / 2;
-    bw::launch_pairs((gemm_pair_kernel<BN, ROPE>), dim3(2 * pairs), dim3(THREADS), smem, s, a, b, c, ep, kb_total, tiles_a,
-                     tiles_b, num_work);
+    bw::launch_pairs((gemm_pair_kernel<BN, ROPE>), dim3(2 * pairs), dim3(THREADS), smem, s, a, b, c, ep, kb_total, kb_per_split,
+                     tiles_a, tiles_b, num_work);
     BW_LAUNCH_CHECK();
     return 0;
 }
@@ -1023,6 +1060,46 @@ BW_EXPORT int bw_gemm_tc_plan(int M, int N, int K, int swiglu, long long workspa
     return best;
 }
 
+// The estimates below count time in units of one feature column times one k-block on a tile of 256 tokens
+// at the rate of a CTA pair (1.7 ns).  Adding the planes of a K split costs a second kernel (2.5 us) and
+// (splits + 2) passes over the float32 result at about 5 TB/s (the planes mostly stay in L2).
+namespace {
+double split_sum_cost(int M, int N, int s) {
+    return s <= 1 ? 0.0 : (2.5e-6 + (double)(s + 2) * M * N * 4.0 / 5e12) / 1.73e-9;
+}
+// single CTAs on tiles of 128 tokens x bn features: measured 15-20 % slower per flop than pairs at 224 to 256
+// columns, and at 53-66 % of a pair's rate at 128 columns (steps of 512 tokens, o and down of the 8B shape)
+double gemm_single_cost(int M, int N, int K, int bn, long long tiles, int splits) {
+    const int kb_total = ceil_div(K, BK);
+    return (double)ceil_div(tiles * splits, NUM_SMS) * ceil_div(kb_total, splits) * bn * (bn == 128 ? 1.7 : 1.18) +
+           split_sum_cost(M, N, splits);
+}
+}  // namespace
+
+// CTA pairs for out[M, N] = x[M, K] . w[N, K]^T with M > 256: the tile width (256 or 224) and the number of K
+// splits (1 to 4, each of 8 k-blocks or more, their planes within the scratch) with the lowest estimate, which
+// is returned (negative: pairs cannot take it).  force_splits > 0 fixes the splits.
+BW_EXPORT double bw_gemm_tc_pair_plan(int M, int N, int K, int force_splits, long long workspace_elems, int* width, int* splits) {
+    const int kb_total = ceil_div(K, BK), pa = ceil_div(M, 2 * BM);
+    const int widths[2] = {256, 224};   // (240 works but was measured no faster than 256)
+    double best = -1.0;
+    for (int i = 0; i < 2; ++i) {
+        const long long t = (long long)pa * ceil_div(N, widths[i]);
+        for (int ps = 1; ps <= 4; ++ps) {
+            if (force_splits > 0 && ps != (force_splits > kb_total ? kb_total : force_splits)) continue;
+            // Measured on the 8B layer sizes at 300 to 1,024 tokens: a split pays only as TWO halves of a long K
+            // (128 k-blocks or more: the down projection) whose items still fit one round of the 74 pairs
+            // (down at 300 tokens: 59 against 73 us; at 512: 68 against 72); everywhere else the planes'
+            // way through memory costs more than the idle pairs (o at 512 tokens: 38 against 26 us).
+            if (ps > 1 && force_splits <= 0 && (ps != 2 || kb_total < 128 || t * ps > NUM_SMS / 2)) continue;
+            if (ps > kb_total || (ps > 1 && (long long)ps * M * N > workspace_elems)) continue;
+            const double cost = (double)ceil_div(t * ps, NUM_SMS / 2) * ceil_div(kb_total, ps) * widths[i] + split_sum_cost(M, N, ps);
+            if (best < 0.0 || cost < best * 0.995) { best = cost; *width = widths[i]; *splits = ps; }
+        }
+    }
+    return best;
+}
+
 // out[M, N] (=|+=) x[M, K] . w[N, K]^T (+ bias[N]).  x, w bf16; out float32 or bf16
 // (accumulate: float32).  swiglu != 0: w holds gate and up rows interleaved in blocks of 16
 // (16 gate rows, the 16 up rows of the same features, ...), N = 2 I with I a multiple of 16,
@@ -1053,6 +1130,20 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
         if (splits > 1 && (!can_split || (long long)splits * M * N > workspace_elems ||
                            (long long)tiles_a * tiles_b * 4 > n_counters))
             return BW_ERR_BAD_ARG;
+    }
+    // More than 256 tokens: CTA pairs on tiles of 256 tokens, or single CTAs: whichever the estimate says
+    // is faster (mode 0: never pairs; 1: the estimate; 2: pairs whenever they can; BW_GEMM_PAIR or
+    // bw_gemm_tc_pair_mode).  With few tiles for the 74 pairs (steps of 300 to 1,000 tokens on the
+    // products with few output features) the pairs split K as well; the partial sums are added in split
+    // order by the second kernel.
+    if (g_pair_mode < 0) { const char* e = getenv("BW_GEMM_PAIR"); g_pair_mode = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1; }
+    int pbn = 256, psplits = 1;
+    bool use_pairs = false;
+    if (g_pair_mode > 0 && !tr && M > 256) {
+        const double pair = bw_gemm_tc_pair_plan(M, N, K, force_splits, can_split ? workspace_elems : 0, &pbn, &psplits);
+        const double single = gemm_single_cost(M, N, K, bn, (long long)tiles_a * tiles_b, splits);
+        use_pairs = pair >= 0.0 && (g_pair_mode == 2 || pair <= single);
+        if (use_pairs) splits = psplits;
     }
     const int kb_per_split = ceil_div(kb_total, splits);
     splits = ceil_div(kb_total, kb_per_split);   // no empty split
@@ -1100,32 +1191,15 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
         case 240: rc = launch<240, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         case 256: rc = launch<256, R>(ta, tb, tc, ep, kb_total, kb_per_split, tiles_a, tiles_b, num_work, s); break; \
         default: return BW_ERR_BAD_ARG; }
-    // many tokens, no K split: CTA pairs on tiles of 256 tokens (mode 0: never; 1: when their rounds of
-    // tiles take less time; 2: whenever they can; from BW_GEMM_PAIR or bw_gemm_tc_pair_mode)
-    if (g_pair_mode < 0) { const char* e = getenv("BW_GEMM_PAIR"); g_pair_mode = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1; }
-    // pairs or single CTAs: whichever needs less time for its rounds of tiles.  A round of pair tiles
-    // (256 tokens x W features on two CTAs) costs W / 1.18 (pairs were measured 15-20 % faster per
-    // flop), a round of single tiles W (W / 0.9 at 128 columns).
-    int pbn = 256; double pair_cost = 0.0;
-    const int pa = ceil_div(M, 2 * BM);
-    {
-        const int widths[2] = {256, 224};   // (240 works but was measured no faster than 256)
-        for (int i = 0; i < 2; ++i) {
-            const long long t = (long long)pa * ceil_div(N, widths[i]);
-            const double cost = (double)ceil_div(t, NUM_SMS / 2) * widths[i] / 1.18;
-            if (i == 0 || cost < pair_cost * 0.995) { pair_cost = cost; pbn = widths[i]; }
-        }
-    }
-    const double single_cost = (double)ceil_div((long long)tiles_a * tiles_b, NUM_SMS) * bn * (bn == 128 ? 1.0 / 0.9 : 1.0);
-    if (g_pair_mode > 0 && !tr && splits == 1 && M > 256 && (g_pair_mode == 2 || pair_cost <= single_cost)) {
+    if (use_pairs) {
         CUtensorMap tb2;
         if (!make_map(&tb2, b_ptr, b_rows, K, b_ld, pbn / 2)) return BW_ERR_DRIVER;
-        const int pb = ceil_div(N, pbn);
-#define BW_PAIR_LAUNCH(W) (rope ? launch_pair<W, true>(ta, tb2, tc, ep, kb_total, pa, pb, s) \
-                                : launch_pair<W, false>(ta, tb2, tc, ep, kb_total, pa, pb, s))
-        return pbn == 256 ? BW_PAIR_LAUNCH(256) : BW_PAIR_LAUNCH(224);
+        const int pa = ceil_div(M, 2 * BM), pb = ceil_div(N, pbn);
+#define BW_PAIR_LAUNCH(W) (rope ? launch_pair<W, true>(ta, tb2, tc, ep, kb_total, kb_per_split, pa, pb, s) \
+                                : launch_pair<W, false>(ta, tb2, tc, ep, kb_total, kb_per_split, pa, pb, s))
+        rc = pbn == 256 ? BW_PAIR_LAUNCH(256) : BW_PAIR_LAUNCH(224);
 #undef BW_PAIR_LAUNCH
-    }
+    } else
     if (rope) BW_GEMM_LAUNCH(true) else BW_GEMM_LAUNCH(false)
 #undef BW_GEMM_LAUNCH
     if (rc) return rc;

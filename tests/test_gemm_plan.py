@@ -86,3 +86,33 @@ def test_decode_shapes_fill_the_gpu(plan):
             tiles = ceil_div(N, BM) * ceil_div(M, bn)
             assert tr == 1 and tiles < NUM_SMS
             assert NUM_SMS // 2 <= tiles * splits <= NUM_SMS, (M, N, K, splits)
+
+
+def test_pair_plan_splits_k_only_where_the_pairs_would_idle():
+    """CTA pairs for more than 256 tokens: K is split only where it was measured to pay: in two halves, a long K
+    (the down projection) at a few hundred tokens, when both halves of every tile fit one round of the 74 pairs."""
+    from blackwellllm_b200.kernels.build import load_library
+    lib = load_library("gemm_tc")
+    fn = lib.bw_gemm_tc_pair_plan
+    fn.restype = ctypes.c_double
+    fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_longlong,
+                   ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+
+    def plan(M, N, K, force=0, workspace=1 << 24):
+        wd, sp = ctypes.c_int(-1), ctypes.c_int(-1)
+        cost = fn(M, N, K, force, workspace, ctypes.byref(wd), ctypes.byref(sp))
+        return cost, wd.value, sp.value
+
+    for M in (300, 512, 1024, 2048, 8192):
+        for N, K in PRODUCTS[:14]:
+            cost, wd, sp = plan(M, N, K)
+            assert cost > 0 and wd in (224, 256) and 1 <= sp <= 4, (M, N, K)
+            kb = ceil_div(K, BK)
+            tiles = ceil_div(M, 2 * BM) * ceil_div(N, wd)
+            if sp > 1:   # two halves of a long K whose items fit one round of the 74 pairs, planes within the scratch
+                assert sp == 2 and kb >= 128 and tiles * 2 <= NUM_SMS // 2 and sp * M * N <= 1 << 24
+            assert plan(M, N, K, workspace=0)[2] == 1            # no scratch, no split
+    assert plan(512, 4096, 14336)[2] == 2                        # down at 512 tokens: 32 tiles for 74 pairs
+    assert plan(512, 4096, 4096)[2] == 1 and plan(768, 4096, 14336)[2] == 1
+    assert plan(2048, 28672, 4096)[2] == 1                       # gate/up at 2,048 tokens: rounds of whole tiles
+    assert plan(700, 520, 2240, force=3)[2] == 3                 # a forced split is taken as it is

@@ -73,6 +73,45 @@ def test_gemm_tc_split_k(ops, M, splits):
     assert torch.equal(out, again)  # split sums are added in a fixed order
 
 
+@pytest.mark.parametrize("mode", ["bias_accumulate", "swiglu", "bf16"])
+@pytest.mark.parametrize("M,splits", [(300, 2), (700, 3), (1000, 4)])
+def test_gemm_tc_split_k_on_cta_pairs(ops, M, splits, mode):
+    """K splits of the CTA-pair kernel (steps of a few hundred tokens on products with few output features):
+    every split writes its plane, the second kernel adds them in split order: right, and bit-equal when repeated."""
+    N, K = 520, 2048 + 64 * 3
+    x = rand(M, K, dtype=torch.bfloat16, seed=5).to(DEV)
+    before = ops.gemm_pair_mode(2)       # pairs whenever they can
+    try:
+        if mode == "swiglu":
+            I = 272
+            wg = rand(I, K, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+            wu = rand(I, K, dtype=torch.bfloat16, seed=3, scale=0.05).to(DEV)
+            w = ops.interleave_gate_up(wg, wu)
+            run = lambda: ops.gemm_tc(x, w, swiglu=True, force_splits=splits)
+            ref = plain_swiglu(x.double() @ wg.double().T, x.double() @ wu.double().T)
+            tol = 2 ** -7
+        else:
+            w = rand(N, K, dtype=torch.bfloat16, seed=6, scale=0.05).to(DEV)
+            if mode == "bf16":
+                run = lambda: ops.gemm_tc(x, w, force_splits=splits)
+                ref, tol = x.double() @ w.double().T, 2 ** -8
+            else:
+                b = rand(N, seed=7).to(DEV)
+                base = rand(M, N, seed=8).to(DEV)
+
+                def run():
+                    out = base.clone()
+                    ops.gemm_tc(x, w, b, out=out, accumulate=True, force_splits=splits)
+                    return out
+                ref, tol = x.double() @ w.double().T + b.double() + base.double(), 1e-5
+        out = run()
+        assert ops.gemm_tc_status() == 0
+        assert float((out.double() - ref).abs().max()) <= tol * float(ref.abs().max())
+        assert torch.equal(run(), out)
+    finally:
+        ops.gemm_pair_mode(before if before >= 0 else 1)
+
+
 def test_gemm_tc_split_k_on_a_tile_width_that_is_no_power_of_two(ops):
     M, N, K = 2048, 4096, 256     # 16 x 18 tiles of 240 columns: the last one of a row is cut at 4096
     x = rand(M, K, dtype=torch.bfloat16, seed=5).to(DEV)
