@@ -43,6 +43,12 @@ template <int BN> __host__ __device__ constexpr int staging_bytes() { return BN 
 constexpr int SMEM_BUDGET = 226 * 1024 - staging_bytes<256>() - 2048;
 constexpr int FUSED_REDUCE_MAX_TOKENS = 16;   // split-K sums inside the kernel up to this many tokens
 constexpr int SWIGLU_BLOCK = 16;   // gate/up features are interleaved in blocks of 16 rows of the weight
+#ifndef GEMM_NARROW_STAGES
+#define GEMM_NARROW_STAGES 8       // stages of the ring of the kernel for up to 16 tokens
+#endif
+#ifndef GEMM_NARROW_CTAS
+#define GEMM_NARROW_CTAS 1         // CTAs of that kernel the register allocation leaves room for on an SM
+#endif
 
 __device__ int g_status = 0;  // 0 ok; else the code of the first wait that gave up
 int g_pair_mode = -1;         // see bw_gemm_tc_pair_mode
@@ -127,7 +133,7 @@ template <int BN> __host__ __device__ constexpr int stages_for() {
     // context 8,192 (ms): 5 stages 5.08, 6: 4.94, 7: 4.93, 8: 4.91, 10: 4.95, 12: 5.02.  (With 5
     // stages two CTAs fit on an SM and the next product's CTAs could request weights while this
     // one's drained; the deeper ring is worth more.)
-    return BN <= 16 ? 8 : (s > 8 ? 8 : s);
+    return BN <= 16 ? GEMM_NARROW_STAGES : (s > 8 ? 8 : s);
 }
 
 // The rotary epilogue of G consecutive tokens of one feature (one lane), in two halves: what does
@@ -368,7 +374,7 @@ struct Items {
 };
 
 template <int BN, bool ROPE>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, BN <= 16 ? GEMM_NARROW_CTAS : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, Epilogue ep, int kb_total, int kb_per_split, int tiles_a, int tiles_b, int num_work) {
     constexpr int STAGES = stages_for<BN>();

@@ -351,6 +351,17 @@ GEMM_FUSED_REDUCE_MAX_TOKENS = 16  # up to here gemm_tc sums its K splits inside
 SWIGLU_BLOCK = 16  # gate/up rows of a fused SwiGLU weight alternate in blocks of this many
 
 
+def _gemm_macros():
+    """Build options of the tensor-core product from the environment, for measurements:
+    BW_GEMM_NARROW="<stages>,<CTAs per SM>" of the kernel for up to 16 tokens (default: the source's)."""
+    import os
+    v = os.environ.get("BW_GEMM_NARROW")
+    if not v:
+        return None
+    st, ctas = v.split(",")
+    return {"GEMM_NARROW_STAGES": int(st), "GEMM_NARROW_CTAS": int(ctas)}
+
+
 def _workspace(device: torch.device):
     """Scratch for split-K, one per device, made at first use: float32 partial sums and
     int32 counters (zero between launches; the kernel returns them to zero)."""
@@ -414,7 +425,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         if bias.numel() != N:
             raise KernelError("gemm: bias must have N entries")
     ws, counters = _workspace(x.device)
-    fn = _fn("gemm_tc", "bw_gemm_tc", _GEMM_TC_ARGS, tag=f"{M}x{N}x{K}" if _timings is not None else None)
+    fn = _fn("gemm_tc", "bw_gemm_tc", _GEMM_TC_ARGS, macros=_gemm_macros(), tag=f"{M}x{N}x{K}" if _timings is not None else None)
     _check(fn(_ptr(x), _ptr(w), _ptr(bias), _code(bias, "bias") if bias is not None else 0, _ptr(out),
               _code(out, "out"), M, N, K, x.stride(0), out.stride(0), int(accumulate), int(swiglu), _ptr(ws),
               ws.numel(), _ptr(counters), counters.numel(), int(force_splits), _stream()), "gemm_tc")
@@ -471,7 +482,7 @@ def gemm_tc_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
             raise KernelError("gemm_tc_rope: bias must have one entry per row of w")
     q_out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=x.device)
     ws, counters = _workspace(x.device)
-    fn = _fn("gemm_tc", "bw_gemm_tc_rope", _GEMM_TC_ROPE_ARGS,
+    fn = _fn("gemm_tc", "bw_gemm_tc_rope", _GEMM_TC_ROPE_ARGS, macros=_gemm_macros(),
              tag=f"rope{T}x{w.shape[0]}x{K}" if _timings is not None else None)
     _check(fn(_ptr(x), _ptr(w), _ptr(bias), _code(bias, "bias") if bias is not None else 0, T, K, x.stride(0),
               _ptr(table), _ptr(kv_slot), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), nh, nkv, hd, rotary_dim,
@@ -483,13 +494,13 @@ def gemm_tc_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
 def gemm_pair_mode(mode: int) -> int:
     """When products of more than 256 tokens run on CTA pairs: 0 never, 1 when estimated faster (the
     default), 2 whenever possible.  Returns the mode before (-1: not set yet, i.e. the default)."""
-    fn = _fn("gemm_tc", "bw_gemm_tc_pair_mode", [c_int])
+    fn = _fn("gemm_tc", "bw_gemm_tc_pair_mode", [c_int], macros=_gemm_macros())
     return fn(int(mode))
 
 
 def gemm_tc_status() -> int:
     """0 if no bounded wait in the tensor-core kernels ever gave up (synchronises the device)."""
-    lib = load_library("gemm_tc")
+    lib = load_library("gemm_tc", _gemm_macros())
     lib.bw_gemm_tc_status.restype = c_int
     return int(lib.bw_gemm_tc_status())
 
