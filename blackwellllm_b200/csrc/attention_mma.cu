@@ -737,13 +737,9 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
     const int G = nh / nkv;
     if (G > 16) return BW_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(attn_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ROWS);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_KEYS);
-        if (e != cudaSuccess) return (int)e;
-        attr_done = true;
-    }
+    static bool rows_attr_done[bw::MAX_DEVICES], keys_attr_done[bw::MAX_DEVICES];
+    if (cudaError_t e = bw::allow_dynamic_smem(attn_rows_kernel, SMEM_ROWS, rows_attr_done); e != cudaSuccess) return (int)e;
+    if (cudaError_t e = bw::allow_dynamic_smem(attn_keys_kernel, SMEM_KEYS, keys_attr_done); e != cudaSuccess) return (int)e;
     Params p;
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages; p.out = (bf16*)out;
     p.cu_q = cu_q; p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
@@ -762,12 +758,8 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
 #if HEAD_DIM % 64 == 0
         if ((page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
             (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0) {
-            static bool tma_attr_done = false;
-            if (!tma_attr_done) {
-                cudaError_t e = cudaFuncSetAttribute(attn_keys_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_KEYS_TMA);
-                if (e != cudaSuccess) return (int)e;
-                tma_attr_done = true;
-            }
+            static bool tma_attr_done[bw::MAX_DEVICES];
+            if (cudaError_t e = bw::allow_dynamic_smem(attn_keys_tma_kernel, SMEM_KEYS_TMA, tma_attr_done); e != cudaSuccess) return (int)e;
             CUtensorMap tk, tv;
             cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)num_pages * nkv * page_size};
             cuuint64_t strides[1] = {(cuuint64_t)HD * 2};

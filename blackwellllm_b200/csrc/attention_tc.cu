@@ -401,12 +401,8 @@ BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_
         cuuint32_t box[2] = {64, (cuuint32_t)page_size};
         if (!encode(&tk, k_pages, 2, dims, strides, box) || !encode(&tv, v_pages, 2, dims, strides, box)) return BW_ERR_DRIVER;
     }
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        attr_done = true;
-    }
+    static bool attr_done[bw::MAX_DEVICES];
+    if (cudaError_t e = bw::allow_dynamic_smem(attn_tc_kernel, SMEM_BYTES, attr_done); e != cudaSuccess) return (int)e;
     Params p;
     p.out = (bf16*)out; p.cu_q = cu_q; p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
     p.work = work; p.max_blocks = max_blocks; p.nh = nh; p.nkv = nkv; p.G = G; p.page_size = page_size;

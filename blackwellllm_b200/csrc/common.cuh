@@ -69,6 +69,34 @@ inline cudaError_t launch_pairs(void (*kernel)(KArgs...), dim3 grid, dim3 block,
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// The current device's number (0 where none can be asked: host-only use of a planner) and its number of SMs
+// (148, the B200's, where none can be asked), looked up once per device.
+constexpr int MAX_DEVICES = 64;
+inline int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) { cudaGetLastError(); return 0; }
+    return dev;
+}
+inline int num_sms() {
+    static int cached[MAX_DEVICES] = {0};
+    const int dev = current_device();
+    if (cached[dev] <= 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 148; }
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+// Raises a kernel's dynamic shared-memory limit once per device (`done`: one flag per device, zero-initialised).
+template <typename K>
+inline cudaError_t allow_dynamic_smem(K kernel, int bytes, bool (&done)[MAX_DEVICES]) {
+    const int dev = current_device();
+    if (done[dev]) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done[dev] = true;
+    return e;
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                           Args&&... args) {

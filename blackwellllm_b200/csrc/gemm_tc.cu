@@ -36,7 +36,6 @@ constexpr int BK = 64;        // k-block: 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int THREADS = 192;
-constexpr int NUM_SMS = 148;
 // Epilogue staging, per epilogue warp a 32 x 33 float block or two 32 x 32 boxes for TMA.  Only the normal
 // orientation uses it, and that has tiles of 128 columns or more: the narrow kernels do without.
 template <int BN> __host__ __device__ constexpr int staging_bytes() { return BN >= 128 ? 4 * 2 * 4096 : 0; }
@@ -970,12 +969,9 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, con
     constexpr int STAGES = stages_for<BN>();
     constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + staging_bytes<BN>() + (2 * STAGES + 4) * 8 + 16 + 1024;
     static_assert(smem <= 227 * 1024, "shared memory budget");
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        attr_done = true;
-    }
+    static bool attr_done[bw::MAX_DEVICES];
+    if (cudaError_t e = bw::allow_dynamic_smem(gemm_tc_kernel<BN, ROPE>, smem, attr_done); e != cudaSuccess) return (int)e;
+    const int NUM_SMS = bw::num_sms();
     const int grid = num_work < NUM_SMS ? num_work : NUM_SMS;
     bw::launch((gemm_tc_kernel<BN, ROPE>), dim3(grid), dim3(THREADS), smem, s, a, b, c, ep, kb_total, kb_per_split,
                tiles_a, tiles_b, num_work);
@@ -989,12 +985,9 @@ int launch_pair(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c
     constexpr int STAGES = pair_stages<BN>();
     constexpr int smem = STAGES * (A_BYTES + (BN / 2) * BK * 2) + staging_bytes<BN>() + (2 * STAGES + 4) * 8 + 16 + 1024;
     static_assert(smem <= 227 * 1024, "shared memory budget");
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        attr_done = true;
-    }
+    static bool attr_done[bw::MAX_DEVICES];
+    if (cudaError_t e = bw::allow_dynamic_smem(gemm_pair_kernel<BN, ROPE>, smem, attr_done); e != cudaSuccess) return (int)e;
+    const int NUM_SMS = bw::num_sms();
     const int num_work = tiles_a * tiles_b * (ep.splits > 1 ? ep.splits : 1);
     const int pairs = num_work < NUM_SMS / 2 ? num_work : NUM_SMS / 2;
     bw::launch_pairs((gemm_pair_kernel<BN, ROPE>), dim3(2 * pairs), dim3(THREADS), smem, s, a, b, c, ep, kb_total, kb_per_split,
@@ -1020,6 +1013,9 @@ int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 }  // namespace
 
+// The number of SMs the planners and launchers count with (the current device's; 148 where none can be asked).
+BW_EXPORT int bw_num_sms() { return bw::num_sms(); }
+
 // Whether bw_gemm_tc takes these operands: bf16, K a multiple of 8 (a TMA row stride
 // is a multiple of 16 bytes), 16-byte aligned bases and strides.
 BW_EXPORT int bw_gemm_tc_supported(const void* x, const void* w, int K, long long ldx) {
@@ -1030,6 +1026,7 @@ BW_EXPORT int bw_gemm_tc_supported(const void* x, const void* w, int K, long lon
 // out[M, N] = x[M, K] . w[N, K]^T.  Returns splits; *transposed and *bn are set.
 BW_EXPORT int bw_gemm_tc_plan(int M, int N, int K, int swiglu, long long workspace_elems, long long n_counters,
                               int* transposed, int* bn) {
+    const int NUM_SMS = bw::num_sms();
     const int kb_total = ceil_div(K, BK);
     int tr = M <= 256, b;
     if (tr) { b = 16; while (b < M) b *= 2; }
@@ -1076,6 +1073,7 @@ double split_sum_cost(int M, int N, int s) {
 // single CTAs on tiles of 128 tokens x bn features: measured 15-20 % slower per flop than pairs at 224 to 256
 // columns, and at 53-66 % of a pair's rate at 128 columns (steps of 512 tokens, o and down of the 8B shape)
 double gemm_single_cost(int M, int N, int K, int bn, long long tiles, int splits) {
+    const int NUM_SMS = bw::num_sms();
     const int kb_total = ceil_div(K, BK);
     return (double)ceil_div(tiles * splits, NUM_SMS) * ceil_div(kb_total, splits) * bn * (bn == 128 ? 1.7 : 1.18) +
            split_sum_cost(M, N, splits);
@@ -1086,6 +1084,7 @@ double gemm_single_cost(int M, int N, int K, int bn, long long tiles, int splits
 // splits (1 to 4, each of 8 k-blocks or more, their planes within the scratch) with the lowest estimate, which
 // is returned (negative: pairs cannot take it).  force_splits > 0 fixes the splits.
 BW_EXPORT double bw_gemm_tc_pair_plan(int M, int N, int K, int force_splits, long long workspace_elems, int* width, int* splits) {
+    const int NUM_SMS = bw::num_sms();
     const int kb_total = ceil_div(K, BK), pa = ceil_div(M, 2 * BM);
     const int widths[2] = {256, 224};   // (240 works but was measured no faster than 256)
     double best = -1.0;
@@ -1117,6 +1116,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
                        float* workspace, long long workspace_elems, int* counters, long long n_counters,
                        int force_splits, const RopeOut* rope, void* stream) {
     if (M <= 0 || N <= 0) return 0;
+    const int NUM_SMS = bw::num_sms();
     if (!bw_gemm_tc_supported(x, w, K, ldx)) return BW_ERR_UNSUPPORTED;
     if (accumulate && out_type != BW_F32) return BW_ERR_BAD_ARG;
     if (swiglu && (N % (2 * SWIGLU_BLOCK) != 0 || out_type != BW_BF16 || accumulate || bias || ldo < N / 2))

@@ -534,8 +534,23 @@ _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_vo
                                    c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
 
 
+_sm_counts = {}
+
+
+def num_sms(device=None) -> int:
+    """SMs of the device (148, the B200's, where there is no device to ask)."""
+    if device is None or not torch.cuda.is_available():
+        return 148
+    device = torch.device(device)
+    n = _sm_counts.get(device)
+    if n is None:
+        n = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
+
+
 def plan_attention_work(q_len, q_start, kv_len, G: int, nkv: int, window: Optional[int], hd: int = 128,
-                        rows_tile: int = 64, page_size: int = 16, static_bound: Optional[int] = None):
+                        rows_tile: int = 64, page_size: int = 16, static_bound: Optional[int] = None,
+                        sms: int = 148):
     """The work lists of the tensor-core attention as plain lists (host arithmetic only):
     ``rows`` items (request, first token, 0, 0) for segments of more than 16 stacked rows (tokens x
     heads of a group), cut into tiles of ``rows_tile`` rows and ordered longest first; ``keys`` items
@@ -550,7 +565,7 @@ def plan_attention_work(q_len, q_start, kv_len, G: int, nkv: int, window: Option
         smem = 2 * 2 * 64 * hd * 2 + 16 * (hd * 2 + 16) + 2048
     else:
         smem = (16 + 4 * 64) * (hd * 2 + 16)
-    slots = 148 * max(1, min(8, (227 * 1024) // (smem + 1024)))
+    slots = sms * max(1, min(8, (227 * 1024) // (smem + 1024)))
     heads = max(1, n_small * nkv)
     if heads <= slots:
         want = slots // heads            # one full wave: all slices run side by side, no tail
@@ -587,7 +602,7 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
     R = batch.R
     rows_items, keys_items, merge_items, total_slices = plan_attention_work(
         batch.h_q_len[:R], batch.h_q_start[:R], batch.h_kv_len[:R], G, nkv, window, hd, rows_tile, page_size,
-        batch.static_bound)
+        batch.static_bound, num_sms(batch.token_ids.device))
     dev = batch.token_ids.device
 
     def up(items):
