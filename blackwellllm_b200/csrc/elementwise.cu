@@ -89,6 +89,85 @@ __global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, const WT* __res
     }
 }
 
+// v += p[0] + p[stride] + ... (n values, added in that order; four loads in flight at a time)
+__device__ __forceinline__ void add_planes4(float4& v, const float* p, int n, size_t stride) {
+    for (int p0 = 0; p0 < n; p0 += 4) {
+        float4 t[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) t[j] = p0 + j < n ? load4(p + (size_t)(p0 + j) * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
+    }
+}
+__device__ __forceinline__ void add_planes1(float& v, const float* p, int n, size_t stride) {
+    for (int p0 = 0; p0 < n; p0 += 4) {
+        float t[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) t[j] = p0 + j < n ? p[(size_t)(p0 + j) * stride] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v += t[j];
+    }
+}
+
+// x += planes[0] + planes[1] + ... (in that order), then the norm of the new x: the planes are a matrix
+// product that its kernel left unsummed (bw_gemm_tc_planes).  One block per output row.  With
+// `rows` (the final norm on chosen rows, which may repeat) x is left as it is and only the norm's
+// input is the sum.  Every thread re-reads only what it wrote itself.
+template <typename WT, typename OT, bool VEC>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ planes, int n_planes,
+                                   size_t plane_stride, const WT* __restrict__ w, const int* __restrict__ rows,
+                                   OT* __restrict__ out, int H, float eps) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    __shared__ float scratch[32];
+    const int i = blockIdx.x;
+    const int src = rows ? rows[i] : i;
+    float* xr = x + (size_t)src * H;
+    const float* pr = planes + (size_t)src * H;
+    OT* o = out + (size_t)i * H;
+    constexpr int W = VEC ? 4 : 1;
+    float ss = 0.f;
+    for (int c = threadIdx.x * W; c < H; c += blockDim.x * W) {
+        if constexpr (VEC) {
+            float4 v = load4(xr + c);
+            add_planes4(v, pr + c, n_planes, plane_stride);
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            if (!rows) store4(xr + c, v);
+        } else {
+            float v = xr[c];
+            add_planes1(v, pr + c, n_planes, plane_stride);
+            ss = fmaf(v, v, ss);
+            if (!rows) xr[c] = v;
+        }
+    }
+    ss = bw::block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x * W; c < H; c += blockDim.x * W) {
+        if constexpr (VEC) {
+            float4 v = load4(xr + c);
+            if (rows) add_planes4(v, pr + c, n_planes, plane_stride);
+            const float4 g = load4(w + c);
+            store4(o + c, make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w));
+        } else {
+            float v = xr[c];
+            if (rows) add_planes1(v, pr + c, n_planes, plane_stride);
+            o[c] = bw::from_f32<OT>(v * r * bw::to_f32(w[c]));
+        }
+    }
+}
+
+// x += planes[0] + planes[1] + ... (in that order)
+__global__ void add_planes_kernel(float* __restrict__ x, const float* __restrict__ planes, int n_planes,
+                                  size_t plane_stride, size_t total) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = x[i];
+        add_planes1(v, planes + i, n_planes, plane_stride);
+        x[i] = v;
+    }
+}
+
 // ---------------------------------------------------------------- SwiGLU
 // in: [T, 2I] with gate in columns [0, I) and up in [I, 2I); out: [T, I].
 template <typename IT, typename OT>
@@ -149,7 +228,7 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
                                    const float* __restrict__ inv_freq, const float* __restrict__ table,
                                    int rotary_dim, OT* __restrict__ q_out, OT* __restrict__ k_pages,
                                    OT* __restrict__ v_pages, int nh, int nkv, int hd,
-                                   int page_size, int num_pages, int paired) {
+                                   int page_size, int num_pages, int paired, int n_planes, size_t plane_stride) {
     BW_PDL_TRIGGER();
     // A block takes ROPE_HPB heads of one token; a thread takes one channel of each of them: the
     // loads of the heads are independent and in flight together, the angle is looked up once.
@@ -187,6 +266,26 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
             const int h = h0 + k;
             v[k] = h < n_heads ? bw::to_f32(row[(size_t)h * hd + (h < nh + nkv ? sc : c)]) : 0.f;
             w[k] = (h < nh + nkv && rot_c) ? bw::to_f32(row[(size_t)h * hd + pc]) : 0.f;
+        }
+        // qkv left as planes by its matrix product: the further planes are added in order
+        for (int p0 = 1; p0 < n_planes; p0 += 2) {   // two planes' loads in flight together
+            float tv[2][ROPE_HPB], tw[2][ROPE_HPB];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const IT* prow = row + (size_t)(p0 + j) * plane_stride;
+                const bool there = p0 + j < n_planes;
+#pragma unroll
+                for (int k = 0; k < ROPE_HPB; ++k) {
+                    const int h = h0 + k;
+                    tv[j][k] = (there && h < n_heads) ? bw::to_f32(prow[(size_t)h * hd + (h < nh + nkv ? sc : c)]) : 0.f;
+                    tw[j][k] = (there && h < nh + nkv && rot_c) ? bw::to_f32(prow[(size_t)h * hd + pc]) : 0.f;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int k = 0; k < ROPE_HPB; ++k) { v[k] += tv[j][k]; w[k] += tw[j][k]; }
+            }
         }
 #pragma unroll
         for (int k = 0; k < ROPE_HPB; ++k) {
@@ -263,6 +362,41 @@ BW_EXPORT int bw_rmsnorm(const float* x, const void* w, int w_type, const int* r
     return 0;
 }
 
+// x[n_rows or more, H] += the planes (float32, plane_stride floats apart), out = rmsnorm of the new x.
+// rows != null: out row i is the norm of x[rows[i]] + planes[.][rows[i]], and x is NOT changed.
+BW_EXPORT int bw_add_rmsnorm(float* x, const float* planes, int n_planes, long long plane_stride, const void* w,
+                             int w_type, const int* rows, void* out, int out_type, int n_rows, int H, float eps,
+                             void* stream) {
+    if (n_rows <= 0) return 0;
+    if (!planes || n_planes < 1 || plane_stride < 0) return BW_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool vec = H % 4 == 0 && plane_stride % 4 == 0 &&
+                     (((uintptr_t)x | (uintptr_t)planes | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    const int threads = vec ? (H >= 4096 ? 1024 : (H >= 1024 ? 256 : 128)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
+#define BW_ARMS(WT, OT) do { if (vec) bw::launch((add_rmsnorm_kernel<WT, OT, true>), dim3(n_rows), dim3(threads), 0, s, x, planes, n_planes, (size_t)plane_stride, cp<WT>(w), rows, mp<OT>(out), H, eps); \
+        else bw::launch((add_rmsnorm_kernel<WT, OT, false>), dim3(n_rows), dim3(threads), 0, s, x, planes, n_planes, (size_t)plane_stride, cp<WT>(w), rows, mp<OT>(out), H, eps); } while (0)
+    if (w_type == BW_F32 && out_type == BW_F32) BW_ARMS(float, float);
+    else if (w_type == BW_F32 && out_type == BW_BF16) BW_ARMS(float, bf16);
+    else if (w_type == BW_BF16 && out_type == BW_F32) BW_ARMS(bf16, float);
+    else if (w_type == BW_BF16 && out_type == BW_BF16) BW_ARMS(bf16, bf16);
+    else return BW_ERR_BAD_ARG;
+#undef BW_ARMS
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+// x[total] += the planes, added in plane order
+BW_EXPORT int bw_add_planes(float* x, const float* planes, int n_planes, long long plane_stride, long long total,
+                            void* stream) {
+    if (total <= 0 || n_planes <= 0) return 0;
+    if (!x || !planes || plane_stride < 0) return BW_ERR_BAD_ARG;
+    const long long want = (total + 255) / 256;
+    bw::launch(add_planes_kernel, dim3((unsigned)(want < 148 * 8 ? want : 148 * 8)), dim3(256), 0, (cudaStream_t)stream,
+               x, planes, n_planes, (size_t)plane_stride, (size_t)total);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
 BW_EXPORT int bw_swiglu(const void* gu, int in_type, void* out, int out_type, int T, int I, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
@@ -299,18 +433,20 @@ BW_EXPORT int bw_kv_slots(const int* positions, const int* req_of_token, const i
 
 // table: [T, rotary_dim] from bw_rope_table, or null to compute the angles here.  paired != 0: the
 // rotated channels of the q and k heads come as (channel j, channel j + rotary_dim / 2) pairs.
+// n_planes > 1: qkv is the sum of that many planes, plane_stride elements apart (bw_gemm_tc_planes).
 BW_EXPORT int bw_rope_append(const void* qkv, int in_type, const int* positions, const int* req_of_token,
                              const int* block_table, int max_blocks, const float* inv_freq, const float* table,
                              int rotary_dim, void* q_out, void* k_pages, void* v_pages, int out_type,
-                             int T, int nh, int nkv, int hd, int page_size, int num_pages, int paired, void* stream) {
+                             int T, int nh, int nkv, int hd, int page_size, int num_pages, int paired,
+                             int n_planes, long long plane_stride, void* stream) {
     if (T <= 0) return 0;
-    if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return BW_ERR_BAD_ARG;
+    if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1) || n_planes < 1 || (n_planes > 1 && plane_stride <= 0)) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hd >= 256 ? 256 : (hd >= 128 ? 128 : (hd >= 64 ? 64 : 32));
     const dim3 grid(T, (nh + 2 * nkv + ROPE_HPB - 1) / ROPE_HPB);
 #define BW_RA(IT, OT) bw::launch((rope_append_kernel<IT, OT>), dim3(grid), dim3(threads), 0, s, cp<IT>(qkv), positions, req_of_token, \
         block_table, max_blocks, inv_freq, table, rotary_dim, mp<OT>(q_out), mp<OT>(k_pages), mp<OT>(v_pages), \
-        nh, nkv, hd, page_size, num_pages, paired)
+        nh, nkv, hd, page_size, num_pages, paired, n_planes, (size_t)plane_stride)
     if (in_type == BW_F32 && out_type == BW_F32) BW_RA(float, float);
     else if (in_type == BW_F32 && out_type == BW_BF16) BW_RA(float, bf16);
     else if (in_type == BW_BF16 && out_type == BW_BF16) BW_RA(bf16, bf16);

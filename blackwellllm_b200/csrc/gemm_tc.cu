@@ -75,6 +75,7 @@ struct Epilogue {
     int rope_on;
     int tma_add;          // normal orientation, out += : 32 x 32 boxes go out through the tensor map tmC
     int stream;           // the k-blocks of all tiles, laid end to end, are cut into one equal range per CTA
+    int planes;           // split-K: the partial planes ARE the result (the bias in plane 0); whoever reads them adds them up
     RopeOut rope;
 };
 
@@ -183,9 +184,10 @@ template <int N, bool ROPE>
 __device__ __forceinline__ void emit(const Epilogue& ep, float* part, const float (&vals)[N], int token0,
                                      int nvalid, int feature, bool fvalid) {
     if (part) {
+        const float b = (ep.planes && part == ep.partial && fvalid) ? bias_at(ep, feature) : 0.f;
 #pragma unroll
         for (int c = 0; c < N; ++c)
-            if (c < nvalid && fvalid) part[(size_t)(token0 + c) * ep.features + feature] = vals[c];
+            if (c < nvalid && fvalid) part[(size_t)(token0 + c) * ep.features + feature] = vals[c] + b;
         return;
     }
     if (ep.swiglu) {
@@ -1114,8 +1116,14 @@ BW_EXPORT double bw_gemm_tc_pair_plan(int M, int N, int K, int force_splits, lon
 static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_type, void* out, int out_type,
                        int M, int N, int K, long long ldx, long long ldo, int accumulate, int swiglu,
                        float* workspace, long long workspace_elems, int* counters, long long n_counters,
-                       int force_splits, const RopeOut* rope, void* stream) {
+                       int force_splits, const RopeOut* rope, void* stream, int* planes_out = nullptr) {
     if (M <= 0 || N <= 0) return 0;
+    // planes_out: the product is left as *planes_out float32 planes [M, N] in `out` (row stride N, the bias
+    // in the first), to be added up by its reader; K is split as if the sums were made here.
+    const bool planes = planes_out != nullptr;
+    if (planes && (M > FUSED_REDUCE_MAX_TOKENS || out_type != BW_F32 || accumulate || swiglu || rope || ldo != N ||
+                   workspace != (float*)out))
+        return BW_ERR_BAD_ARG;
     const int NUM_SMS = bw::num_sms();
     if (!bw_gemm_tc_supported(x, w, K, ldx)) return BW_ERR_UNSUPPORTED;
     if (accumulate && out_type != BW_F32) return BW_ERR_BAD_ARG;
@@ -1124,7 +1132,8 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     if (rope && (swiglu || accumulate)) return BW_ERR_BAD_ARG;
     if (!swiglu && !rope && ldo < N) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool can_split = workspace && counters;
+    const bool can_split = workspace && (counters || planes);
+    if (planes) n_counters = 1LL << 40;   // no counters are used: nothing to run out of
     int tr, bn;
     int splits = bw_gemm_tc_plan(M, N, K, swiglu, can_split ? workspace_elems : 0, can_split ? n_counters : 0, &tr, &bn);
     if (!tr && bn < 128) return BW_ERR_BAD_ARG;   // only tiles of 128 columns or more have the normal orientation's staging
@@ -1168,10 +1177,12 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     // gate/up at batch 8 takes 43 us instead of 47.5.  (Two CTAs per SM on whole tiles took 38 us when
     // the block scheduler spread them and 48 us when it paired them on some SMs and left others idle.)
     const long long n_tiles = (long long)tiles_a * tiles_b;
-    const bool stream_k = tr && fused_reduce && can_split && force_splits <= 0 && splits == 1 && n_tiles > NUM_SMS &&
+    const bool stream_k = tr && fused_reduce && can_split && !planes && force_splits <= 0 && splits == 1 && n_tiles > NUM_SMS &&
                           n_tiles % NUM_SMS != 0 && 2LL * M * N <= workspace_elems && n_tiles * 4 <= n_counters;
     if (stream_k) splits = 2;   // at most two CTAs share a tile: two planes of partial sums
-    ep.out = out; ep.partial = splits > 1 ? workspace : nullptr; ep.counters = fused_reduce ? counters : nullptr;
+    ep.out = out; ep.partial = splits > 1 ? workspace : nullptr; ep.counters = (fused_reduce && !planes) ? counters : nullptr;
+    ep.planes = planes ? 1 : 0;
+    if (planes) *planes_out = splits;
     ep.bias = bias; ep.ldo = ldo;
     ep.out_type = out_type; ep.bias_type = bias_type; ep.accumulate = accumulate; ep.transposed = tr;
     ep.swiglu = swiglu; ep.tokens = M; ep.features = N; ep.splits = splits;
@@ -1209,7 +1220,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     if (rope) BW_GEMM_LAUNCH(true) else BW_GEMM_LAUNCH(false)
 #undef BW_GEMM_LAUNCH
     if (rc) return rc;
-    if (splits > 1 && !fused_reduce) {
+    if (splits > 1 && !fused_reduce && !planes) {
         const size_t total = (size_t)M * (swiglu ? N / 2 : N);
         const size_t want = (total + 255) / 256;
         const int blocks = (int)(want < (size_t)NUM_SMS * 8 ? want : (size_t)NUM_SMS * 8);
@@ -1225,6 +1236,19 @@ BW_EXPORT int bw_gemm_tc(const void* x, const void* w, const void* bias, int bia
                          int force_splits, void* stream) {
     return run_gemm_tc(x, w, bias, bias_type, out, out_type, M, N, K, ldx, ldo, accumulate, swiglu, workspace,
                        workspace_elems, counters, n_counters, force_splits, nullptr, stream);
+}
+
+// The product of up to 16 tokens as float32 planes: planes[p][m][n] for p < *n_planes add up to
+// x[M, K] . w[N, K]^T (+ bias, which is part of plane 0), in plane order.  K is split as bw_gemm_tc
+// would split it, but no CTA waits for another's partial sums: the kernel that reads the result adds
+// the planes (bw_add_rmsnorm, bw_add_planes, bw_rope_append).  planes_elems: room in `planes` (floats).
+BW_EXPORT int bw_gemm_tc_planes(const void* x, const void* w, const void* bias, int bias_type, float* planes,
+                                long long planes_elems, int M, int N, int K, long long ldx, int force_splits,
+                                int* n_planes, void* stream) {
+    if (!planes || !n_planes || planes_elems < (long long)M * N) return BW_ERR_BAD_ARG;
+    *n_planes = 1;
+    return run_gemm_tc(x, w, bias, bias_type, planes, BW_F32, M, N, K, ldx, N, 0, 0, planes, planes_elems, nullptr, 0,
+                       force_splits, nullptr, stream, n_planes);
 }
 
 // The fused q/k/v projection with rotary position encoding: x[M, K] . w[N, K]^T (+ bias), N =

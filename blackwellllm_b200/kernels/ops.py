@@ -6,6 +6,7 @@ implementation.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -50,6 +51,8 @@ def _stream():
 
 
 def _dev(t: torch.Tensor, name: str, dtype=None, contiguous=True):
+    if _pending is not None and t.dtype == torch.float32 and t.data_ptr() == _pending[0].data_ptr():
+        resolve_pending()   # an operand whose last matrix product is still in planes: add them first
     if not t.is_cuda:
         raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
     if dtype is not None and t.dtype != dtype:
@@ -131,8 +134,96 @@ def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: Optional[
     return logits
 
 
+# ------------------------------------------------------------------ sums left to the reader
+#
+# For up to GEMM_FUSED_REDUCE_MAX_TOKENS tokens a product that is ADDED to a float32 tensor (the
+# residual stream) can leave its K splits unsummed, as planes in a buffer of this module
+# (gemm_tc_deferred): no CTA then waits for another's partial sums.  The planes are added by
+# whichever kernel reads the tensor next: rmsnorm adds them while it normalises; every other
+# function of this module adds them with a kernel of its own first (through _dev); code that reads
+# the tensor by other means calls resolve_pending() before.  At most one sum is outstanding.
+
+DEFER_SUMS = os.environ.get("BW_DEFER_SUMS", "1") != "0"
+_pending = None          # (target tensor, planes [S, M, N]) or None
+_plane_buffers = {}
+_PLANE_BUFFER_ELEMS = 8 << 20
+
+
+def _plane_buffer(device: torch.device) -> torch.Tensor:
+    buf = _plane_buffers.get(device)
+    if buf is None:
+        buf = _plane_buffers[device] = torch.empty(_PLANE_BUFFER_ELEMS, dtype=torch.float32, device=device)
+    return buf
+
+
+def pending_target() -> Optional[torch.Tensor]:
+    """The tensor whose last product is still in planes (None: nothing is outstanding)."""
+    return None if _pending is None else _pending[0]
+
+
+def resolve_pending() -> None:
+    """Adds an outstanding sum into its tensor (a no-op when nothing is outstanding)."""
+    global _pending
+    if _pending is None:
+        return
+    target, planes = _pending
+    _pending = None
+    fn = _fn("elementwise", "bw_add_planes", [c_void_p, c_void_p, c_int, c_ll, c_ll, c_void_p])
+    _check(fn(_ptr(target), _ptr(planes), planes.shape[0], planes.stride(0), target.numel(), _stream()), "add_planes")
+
+
+def discard_pending(t: Optional[torch.Tensor] = None) -> None:
+    """Forgets an outstanding sum into ``t`` (None: into whatever tensor): it is not read again."""
+    global _pending
+    if _pending is not None and (t is None or _pending[0].data_ptr() == t.data_ptr()):
+        _pending = None
+
+
+def gemm_tc_planes(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                   force_splits: int = 0) -> torch.Tensor:
+    """x @ w.T (+ bias) for up to GEMM_FUSED_REDUCE_MAX_TOKENS tokens as float32 planes [S, M, N] that
+    add up to it (in plane order; the bias is in plane 0), in this module's plane buffer: valid until
+    the next call.  An outstanding sum is resolved first."""
+    resolve_pending()
+    _dev(x, "x", torch.bfloat16, contiguous=False); _dev(w, "w", torch.bfloat16)
+    M, K = x.shape
+    N = w.shape[0]
+    if not gemm_tc_supports(x, w) or w.shape[1] != K or M > GEMM_FUSED_REDUCE_MAX_TOKENS:
+        raise KernelError("gemm_tc_planes: bfloat16 operands the tensor-core product takes, at most "
+                          f"{GEMM_FUSED_REDUCE_MAX_TOKENS} tokens")
+    if bias is not None:
+        _dev(bias, "bias")
+        if bias.numel() != N:
+            raise KernelError("gemm: bias must have N entries")
+    buf = _plane_buffer(x.device)
+    n = c_int(0)
+    fn = _fn("gemm_tc", "bw_gemm_tc_planes", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int,
+                                               c_ll, c_int, ctypes.POINTER(c_int), c_void_p],
+             macros=_gemm_macros(), tag=f"planes{M}x{N}x{K}" if _timings is not None else None)
+    _check(fn(_ptr(x), _ptr(w), _ptr(bias), _code(bias, "bias") if bias is not None else 0, _ptr(buf), buf.numel(),
+              M, N, K, x.stride(0), int(force_splits), ctypes.byref(n), _stream()), "gemm_tc_planes")
+    return buf[:n.value * M * N].view(n.value, M, N)
+
+
+def gemm_tc_deferred(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out += x @ w.T (+ bias), the sum left to the next reader of ``out`` (float32 [M, N], contiguous)."""
+    global _pending
+    if out.dtype != torch.float32 or not out.is_contiguous() or out.shape != (x.shape[0], w.shape[0]):
+        raise KernelError("gemm_tc_deferred: out must be contiguous float32 [M, N]")
+    planes = gemm_tc_planes(x, w, bias)
+    _pending = (out, planes)
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype,
             rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    global _pending
+    planes = None
+    if _pending is not None and _pending[0].data_ptr() == x.data_ptr() and _pending[0].shape == x.shape:
+        planes = _pending[1]
+        if rows is None:
+            _pending = None       # x itself is brought up to date by the kernel below
+        else:
+            saved, _pending = _pending, None
     _dev(x, "x", torch.float32); _dev(w, "w")
     H = x.shape[-1]
     if w.numel() != H:
@@ -143,6 +234,14 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype
     if out is None:
         out = torch.empty((n, H), dtype=out_dtype, device=x.device)
     _dev(out, "out", out_dtype)
+    if planes is not None:
+        fn = _fn("elementwise", "bw_add_rmsnorm", [c_void_p, c_void_p, c_int, c_ll, c_void_p, c_int, c_void_p, c_void_p,
+                                                   c_int, c_int, c_int, c_float, c_void_p])
+        _check(fn(_ptr(x), _ptr(planes), planes.shape[0], planes.stride(0), _ptr(w), _code(w, "w"), _ptr(rows), _ptr(out),
+                  _code(out, "out"), n, H, float(eps), _stream()), "add_rmsnorm")
+        if rows is not None:
+            _pending = saved      # chosen rows only: x is unchanged and the sum stays outstanding
+        return out
     fn = _fn("elementwise", "bw_rmsnorm",
              [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
     _check(fn(_ptr(x), _ptr(w), _code(w, "w"), _ptr(rows), _ptr(out), _code(out, "out"), n, H,
@@ -194,7 +293,12 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, req_of_token: torch.
     """Rotates q and k heads of ``qkv`` [T, (nh+2nkv)*hd], returns q [T, nh*hd] in the
     pages' dtype, and writes rotated k and raw v to pages [num_pages, nkv, page, hd].
     ``table``: the step's cos/sin table from :func:`rope_table` (else computed here).
-    ``paired``: the q and k heads of ``qkv`` are in the order of :func:`rotary_row_order`."""
+    ``paired``: the q and k heads of ``qkv`` are in the order of :func:`rotary_row_order`.
+    ``qkv`` may be planes [S, T, width] from :func:`gemm_tc_planes`: they are added while they are read."""
+    n_planes, plane_stride = 1, 0
+    if qkv.dim() == 3:
+        n_planes, plane_stride = qkv.shape[0], qkv.stride(0)
+        qkv = qkv[0]
     _dev(qkv, "qkv"); _dev(positions, "positions", torch.int32)
     _dev(req_of_token, "req_of_token", torch.int32); _dev(block_table, "block_table", torch.int32)
     _dev(k_pages, "k_pages"); _dev(v_pages, "v_pages", k_pages.dtype)
@@ -217,10 +321,11 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, req_of_token: torch.
             raise KernelError("rope_append: the cos/sin table must be [T, rotary_dim]")
     fn = _fn("elementwise", "bw_rope_append",
              [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_ll, c_void_p])
     _check(fn(_ptr(qkv), _code(qkv, "qkv"), _ptr(positions), _ptr(req_of_token), _ptr(block_table),
               block_table.shape[1], _ptr(inv_freq), _ptr(table), rotary_dim, _ptr(q_out), _ptr(k_pages), _ptr(v_pages),
-              _code(k_pages, "pages"), T, nh, nkv, hd, page_size, num_pages if append else 0, int(paired), _stream()),
+              _code(k_pages, "pages"), T, nh, nkv, hd, page_size, num_pages if append else 0, int(paired),
+              n_planes, plane_stride, _stream()),
            "rope_append")
     return q_out
 

@@ -76,14 +76,22 @@ class DecoderModel:
         """Runs the batch's tokens through the schedule; returns float32 logits
         [len(batch.logit_rows), vocab] for the rows that were asked for."""
         c = self.config
+        ops.discard_pending()   # nothing of an earlier (failed) pass is added into this one's tensors
         h = ops.embed_gather(self.embed, batch.token_ids, scale=c.embedding_multiplier)
         for pos, e in enumerate(self.config.schedule):
             cache = caches[e.cache_of if e.cache_of is not None else pos]
-            self.blocks[e.layer].forward(h, batch, cache, owns_cache=e.cache_of is None)
+            blk = self.blocks[e.layer]
+            if not blk.takes_pending:
+                ops.resolve_pending()   # the block before may have left its last sum to the next reader
+            blk.forward(h, batch, cache, owns_cache=e.cache_of is None)
         n = batch.logit_rows.numel()
         if n == 0:
+            ops.discard_pending(h)
             return torch.empty((0, self.config.vocab_size), dtype=torch.float32, device=h.device)
+        if not self.final_norm.adds_pending:
+            ops.resolve_pending()
         x = self.final_norm.forward(h, rows=batch.logit_rows)
+        ops.discard_pending(h)          # the stream ends here: only the chosen rows were summed
         logits = self.head(x, out_dtype=torch.float32)
         if c.logit_scale != 1.0 or c.logit_softcap is not None:
             ops.logit_transform(logits, c.logit_scale, c.logit_softcap)

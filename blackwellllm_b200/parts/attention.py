@@ -69,7 +69,7 @@ class GQAAttention(Mixer):
             q = self.position.rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, append=owns_cache)
         o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, batch.block_tables[cache.group],
                                 self.nh, self.window, self.scale)
-        self.o(o, out=residual, accumulate=True)
+        self.o.add_to(o, residual)
 
 
 register_mixer("gqa_attention", GQAAttention)

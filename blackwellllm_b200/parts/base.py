@@ -80,6 +80,11 @@ class Part:
 
 
 class Norm(Part):
+    # True: forward() reads x only through ops.rmsnorm, which adds a sum that a matrix product left
+    # outstanding for x (ops.gemm_tc_deferred) while it normalises.  False: whoever calls forward()
+    # calls ops.resolve_pending() first.
+    adds_pending = False
+
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
@@ -115,6 +120,9 @@ class FeedForward(Part):
 
 class Block(Part):
     mixer: Mixer
+    # True: forward() may be entered, and may return, with a sum outstanding for the residual stream
+    # (ops.gemm_tc_deferred) and sees to it that no part reads the stream before the sum is made.
+    takes_pending = False
 
     def forward(self, residual, batch, cache, owns_cache: bool = True) -> None:
         raise NotImplementedError

@@ -2,7 +2,8 @@
 
 ``prenorm`` (src/core/engine.cpp:946-1024): the norm stands before each sublayer
 and reads the residual stream without changing it; each sublayer adds its output
-to the residual stream, which stays float32.
+to the residual stream, which stays float32.  A sublayer's last product may leave its sum to the
+next reader of the stream (``Linear.add_to``): the next norm, which adds it while it normalises.
 """
 from __future__ import annotations
 
@@ -10,6 +11,7 @@ from typing import Dict, List
 
 import torch
 
+from ..kernels import ops
 from .base import (Block, BuildContext, ParamSpec, build_ffn, build_mixer, build_norm,
                    register_block)
 
@@ -43,11 +45,21 @@ class PreNormBlock(Block):
         for prefix, part in self._children():
             part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
 
+    takes_pending = True
+
+    @staticmethod
+    def _normed(norm, residual):
+        # a sublayer may have left the sum of its last product to the stream's next reader: a norm
+        # that adds it while it normalises, or else a kernel of its own here
+        if not norm.adds_pending:
+            ops.resolve_pending()
+        return norm.forward(residual)
+
     def forward(self, residual, batch, cache, owns_cache: bool = True) -> None:
-        x = self.mixer_norm.forward(residual)
+        x = self._normed(self.mixer_norm, residual)
         self.mixer.forward(x, residual, batch, cache, owns_cache)
         if self.ffn is not None:
-            x = self.ffn_norm.forward(residual)
+            x = self._normed(self.ffn_norm, residual)
             self.ffn.forward(x, residual, batch)
 
 

@@ -32,3 +32,14 @@ class Linear:
         if w.dtype == torch.bfloat16 and ops.gemm_tc_supports(x, w):
             return ops.gemm_tc(x, w, self.bias, out=out, out_dtype=out_dtype, accumulate=accumulate)
         return ops.gemm_simt(x, w, self.bias, out=out, out_dtype=out_dtype, accumulate=accumulate)
+
+    def add_to(self, x: torch.Tensor, residual: torch.Tensor) -> None:
+        """``residual += x @ W.T (+ bias)`` (float32).  For a few tokens on the tensor-core path the sum
+        of the K splits is left to the next reader of ``residual`` (``ops.gemm_tc_deferred``)."""
+        w = self.weight
+        if (ops.DEFER_SUMS and w.dtype == torch.bfloat16 and x.dtype == w.dtype
+                and x.shape[0] <= ops.GEMM_FUSED_REDUCE_MAX_TOKENS and residual.dtype == torch.float32
+                and residual.is_contiguous() and ops.gemm_tc_supports(x, w)):
+            ops.gemm_tc_deferred(x, w, self.bias, residual)
+        else:
+            self(x, out=residual, accumulate=True)

@@ -48,7 +48,7 @@ class SwiGLU(FeedForward):
             a = ops.gemm_tc(x, self.gate_up.weight, swiglu=True)
         else:
             a = ops.swiglu(self.gate_up(x))
-        self.down(a, out=residual, accumulate=True)
+        self.down.add_to(a, residual)
 
 
 register_ffn("swiglu", SwiGLU)

@@ -16,6 +16,8 @@ from .base import BuildContext, Norm, ParamSpec, register_norm
 
 
 class RMSNorm(Norm):
+    adds_pending = True
+
     def __init__(self, spec, hidden_size: int, ctx: BuildContext):
         self.eps = float(spec.eps)
         self.hidden_size = hidden_size

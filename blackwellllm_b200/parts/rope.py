@@ -70,9 +70,10 @@ class RotaryEncoding(PositionEncoding):
 
         def project(x, batch, cache, append=True):
             if batch.T <= ops.GEMM_FUSED_REDUCE_MAX_TOKENS:
-                # few tokens: the product sums its K splits in its last warps, and the rotation on
-                # top of that was measured slower than a kernel of its own on the paired layout
-                qkv = ops.gemm_tc(x, w, b, out_dtype=torch.float32)
+                # few tokens: the product leaves its K splits as planes, which the rotation's kernel
+                # adds while it reads them (the rotation in the product's own epilogue, after a sum
+                # of the splits in its last warps, was measured slower than a kernel of its own)
+                qkv = ops.gemm_tc_planes(x, w, b) if ops.DEFER_SUMS else ops.gemm_tc(x, w, b, out_dtype=torch.float32)
                 return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
                                        self.inv_freq, self.rotary_dim, cache.k_pages, cache.v_pages, nh, nkv, hd,
                                        append=append, table=self._table(batch), paired=True)

@@ -73,6 +73,127 @@ def test_gemm_tc_split_k(ops, M, splits):
     assert torch.equal(out, again)  # split sums are added in a fixed order
 
 
+# ------------------------------------------------------------------ sums left to the reader
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16])
+@pytest.mark.parametrize("N,K,force", [(4096, 4096, 0), (1000, 2056, 0), (6144, 512, 0), (384, 14336, 0), (520, 2240, 3),
+                                       (128 * 149, 256, 0)])
+def test_gemm_tc_planes_add_up_to_the_product(ops, M, N, K, force):
+    x = rand(M, K, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rand(N, K, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    b = rand(N, seed=3).to(DEV)
+    ref = x.double() @ w.double().T + b.double()
+    planes = ops.gemm_tc_planes(x, w, b, force_splits=force)
+    assert planes.dtype == torch.float32 and planes.shape[1:] == (M, N) and planes.shape[0] >= 1
+    if force:
+        assert planes.shape[0] == force
+    if (N, K) == (384, 14336):
+        assert planes.shape[0] > 1                  # three tiles and a long K: the planner splits
+    if N == 128 * 149:
+        assert planes.shape[0] == 1                 # more tiles than SMs: one plane, written as the result
+    total = planes[0].clone()
+    for p in range(1, planes.shape[0]):
+        total += planes[p]                          # the order in which the readers add them
+    assert ops.gemm_tc_status() == 0
+    assert float((total.double() - ref).abs().max()) / float(ref.abs().max()) <= 1e-5
+    again = ops.gemm_tc_planes(x, w, b, force_splits=force).clone()
+    assert torch.equal(again, ops.gemm_tc_planes(x, w, b, force_splits=force))
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tc_planes(rand(17, K, dtype=torch.bfloat16).to(DEV), w)
+
+
+@pytest.mark.parametrize("H,K", [(4096, 4096), (1000, 2056), (72, 200), (130, 14336)])
+@pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32])
+def test_rmsnorm_adds_an_outstanding_sum(ops, H, K, odt):
+    M, eps = 7, 1e-5
+    x = rand(M, K, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rand(H, K, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    b = rand(H, seed=3).to(DEV)
+    gain = (1 + rand(H, seed=4, scale=0.1)).to(odt).to(DEV)
+    base = rand(M, H, seed=5).to(DEV)
+    summed = base.double() + x.double() @ w.double().T + b.double()
+    normed = summed * torch.rsqrt((summed * summed).mean(-1, keepdim=True) + eps) * gain.double()
+    tol = 2 ** -8 if odt == torch.bfloat16 else 1e-5
+
+    res = base.clone()
+    ops.gemm_tc_deferred(x, w, b, res)
+    assert ops.pending_target() is res and torch.equal(res, base)         # nothing was added yet
+    out = ops.rmsnorm(res, gain, eps, odt)
+    assert ops.pending_target() is None                                   # the norm added it and wrote the stream back
+    assert float((res.double() - summed).abs().max()) / float(summed.abs().max()) <= 1e-5
+    assert float((out.double() - normed).abs().max()) / float(normed.abs().max()) <= tol
+
+    # chosen rows (they may repeat): the stream is left as it was and the sum stays outstanding
+    res = base.clone()
+    ops.gemm_tc_deferred(x, w, b, res)
+    rows = torch.tensor([2, 0, 2, 6], dtype=torch.int32, device=DEV)
+    out = ops.rmsnorm(res, gain, eps, odt, rows=rows)
+    assert torch.equal(res, base) and ops.pending_target() is res
+    assert float((out.double() - normed[rows.long()]).abs().max()) / float(normed.abs().max()) <= tol
+    ops.resolve_pending()
+    assert ops.pending_target() is None
+    assert float((res.double() - summed).abs().max()) / float(summed.abs().max()) <= 1e-5
+
+
+def test_an_outstanding_sum_is_made_before_anything_else_reads_or_replaces_it(ops):
+    M, H, K = 5, 264, 520
+    x = rand(M, K, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rand(H, K, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    base = rand(M, H, seed=5).to(DEV)
+    summed = base.double() + x.double() @ w.double().T
+
+    def close(t, ref):
+        return float((t.double() - ref).abs().max()) / float(ref.abs().max()) <= 1e-5
+
+    # another kernel of the package takes the tensor as an operand: the sum is made first
+    res = base.clone()
+    ops.gemm_tc_deferred(x, w, None, res)
+    other = rand(M, H, seed=6).to(DEV)
+    ops.rmsnorm(other, torch.ones(H, device=DEV), 1e-5, torch.float32)      # a norm of ANOTHER tensor leaves it alone
+    assert ops.pending_target() is res
+    ops.logit_transform(res, 2.0)
+    assert ops.pending_target() is None and close(res, 2.0 * summed)
+
+    # a second product is left open while the first still is: the first is added before its planes are overwritten
+    res, res2 = base.clone(), base.clone()
+    ops.gemm_tc_deferred(x, w, None, res)
+    ops.gemm_tc_deferred(x, w, None, res2)
+    assert ops.pending_target() is res2 and close(res, summed) and torch.equal(res2, base)
+    ops.discard_pending(res)                      # not the outstanding one: nothing happens
+    assert ops.pending_target() is res2
+    ops.discard_pending(res2)
+    assert ops.pending_target() is None and torch.equal(res2, base)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rd,page", [(5, 1, 48, 32, 8), (4, 2, 64, 64, 16), (32, 8, 128, 128, 16)])
+@pytest.mark.parametrize("M,force", [(3, 0), (16, 3), (8, 5)])
+def test_rope_append_adds_planes(ops, nh, nkv, hd, rd, page, M, force):
+    """The q/k/v product left as planes and rotated from there equals the rotation of the summed product, bit for bit
+    where the sum is the same: compared with the same kernel on the planes added up beforehand in the same order."""
+    K = 1024 + 64 * 5
+    width = (nh + 2 * nkv) * hd
+    x = rand(M, K, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rand(width, K, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    b = rand(width, seed=3).to(DEV)
+    inv = (1e4 ** (-torch.arange(rd // 2, dtype=torch.float64) * 2 / rd)).float().to(DEV)
+    positions = torch.arange(100, 100 + M, dtype=torch.int32, device=DEV)
+    req = torch.zeros(M, dtype=torch.int32, device=DEV)
+    n_pages = (100 + M) // page + 2
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).flip(0).reshape(1, -1).contiguous()
+    pools = [torch.zeros(n_pages, nkv, page, hd, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
+    planes = ops.gemm_tc_planes(x, w, b, force_splits=force).clone()
+    if force:
+        assert planes.shape[0] == force
+    total = planes[0].clone()
+    for p in range(1, planes.shape[0]):
+        total += planes[p]
+    for paired in (False, True):
+        q1 = ops.rope_append(planes, positions, req, table, inv, rd, pools[0], pools[1], nh, nkv, hd, paired=paired)
+        q2 = ops.rope_append(total, positions, req, table, inv, rd, pools[2], pools[3], nh, nkv, hd, paired=paired)
+        assert torch.equal(q1, q2) and torch.equal(pools[0], pools[2]) and torch.equal(pools[1], pools[3])
+        assert float(pools[0].abs().max()) > 0
+
+
 @pytest.mark.parametrize("mode", ["bias_accumulate", "swiglu", "bf16"])
 @pytest.mark.parametrize("M,splits", [(300, 2), (700, 3), (1000, 4)])
 def test_gemm_tc_split_k_on_cta_pairs(ops, M, splits, mode):

@@ -6,6 +6,7 @@ from dataclasses import dataclass
 import pytest
 import torch
 
+from blackwellllm_b200.kernels import ops
 from plain_model import (plain_attention, plain_inv_freq, plain_linear, plain_rmsnorm, plain_rope, plain_swiglu)
 
 pytestmark = pytest.mark.gpu
@@ -195,6 +196,7 @@ def test_attention_mixer_alone(dtype, bias, window):
         x = torch.cat([xs[r][done[r]:done[r] + n] for r, n in step]).to(DEV)
         residual = torch.zeros(x.shape[0], H, device=DEV)
         mixer.forward(x, residual, batch, cache.views[0], True)
+        ops.resolve_pending()   # a few tokens: the output projection leaves its sum to the stream's next reader
         at = 0
         for r, n in step:
             got[r].append(residual[at:at + n].double().cpu())
@@ -223,6 +225,8 @@ def test_swiglu_part_and_block(dtype):
     x = rnd(11, H, seed=4).to(dtype)
     res = torch.ones(11, H, device=DEV)
     ffn.forward(x.to(DEV), res, None)
+    assert (ops.pending_target() is res) == (dtype == torch.bfloat16)   # 11 tokens: the down projection's sum is left open
+    ops.resolve_pending()
     xd = x.double()
     ref = 1.0 + plain_linear(plain_swiglu(plain_linear(xd, Wf["gate_proj.weight"].double()),
                                           plain_linear(xd, Wf["up_proj.weight"].double())), Wf["down_proj.weight"].double())
@@ -244,6 +248,7 @@ def test_swiglu_part_and_block(dtype):
     h0 = rnd(T, H, seed=5)
     h = h0.clone().to(DEV)
     block.forward(h, make_batch(cache, [("a", T)]), cache.views[0], True)
+    ops.resolve_pending()
     hd_ = h0.double()
     n1 = plain_rmsnorm(hd_, g1.double(), 1e-5)
     Wd = {k: v.double() for k, v in Wa.items()}
@@ -256,6 +261,82 @@ def test_swiglu_part_and_block(dtype):
     hd_ = hd_ + plain_linear(plain_swiglu(plain_linear(n2, Wf["gate_proj.weight"].double()),
                                           plain_linear(n2, Wf["up_proj.weight"].double())), Wf["down_proj.weight"].double())
     assert float((h.double().cpu() - hd_).abs().max()) <= TOL[dtype] * float(hd_.abs().max())
+
+
+@dataclass(frozen=True)
+class ToyScaleNormSpec:
+    kind: str = "toy_scalenorm"
+
+
+def register_toy_scalenorm():
+    from blackwellllm_b200.parts import Norm, ParamSpec, register_norm
+
+    class ToyScaleNorm(Norm):
+        """y = x * w / (1 + mean |x|), computed with torch on the stream itself: it knows nothing of sums that a
+        product left open, so the block has to make them before it calls this."""
+        def __init__(self, spec, hidden_size, ctx):
+            self.hidden_size, self.ctx, self.weight = hidden_size, ctx, None
+
+        def param_specs(self):
+            return [ParamSpec("weight", (self.hidden_size,), role="gain", init="ones")]
+
+        def bind(self, tensors):
+            self.weight = tensors["weight"].float()
+
+        def forward(self, x, rows=None):
+            if rows is not None:
+                x = x[rows.long()]
+            return (x * self.weight / (1 + x.abs().mean(-1, keepdim=True))).to(self.ctx.dtype)
+
+    register_norm("toy_scalenorm", ToyScaleNorm)
+
+
+@pytest.mark.parametrize("norm", ["rmsnorm", "toy_scalenorm"])
+@pytest.mark.parametrize("T", [1, 5, 16])
+def test_block_on_few_tokens_where_products_leave_their_sums_open(norm, T):
+    """Up to 16 tokens the output and the down projection leave the sums of their K splits to the next reader of the
+    stream: an RMSNorm adds them while it normalises, before any other norm the block adds them itself."""
+    from blackwellllm_b200.cache.manager import CacheManager
+    from blackwellllm_b200.config.specs import AttentionSpec, LayerSpec, RMSNormSpec, RopeSpec, SwiGLUSpec
+    from blackwellllm_b200.parts import BuildContext, build_block
+    register_toy_scalenorm()
+    dtype = torch.bfloat16
+    H, I, nh, nkv, hd = 136, 208, 6, 3, 16
+    ctx = BuildContext(DEV, dtype)
+    nspec = RMSNormSpec(1e-5) if norm == "rmsnorm" else ToyScaleNormSpec()
+    block = build_block(LayerSpec(AttentionSpec(nh, nkv, hd, True, RopeSpec(1e4, hd)), SwiGLUSpec(I), nspec, nspec), H, ctx)
+    Wa = attention_weights(H, nh, nkv, hd, True, dtype, 20)
+    Wf = {"gate_proj.weight": rnd(I, H, seed=1, scale=0.1).to(dtype), "up_proj.weight": rnd(I, H, seed=2, scale=0.1).to(dtype),
+          "down_proj.weight": rnd(H, I, seed=3, scale=0.1).to(dtype)}
+    g1, g2 = (1 + rnd(H, seed=30, scale=0.1)).to(dtype), (1 + rnd(H, seed=31, scale=0.1)).to(dtype)
+    tensors = {"self_attn." + k: v for k, v in Wa.items()}
+    tensors.update({"mlp." + k: v for k, v in Wf.items()})
+    tensors.update({"input_layernorm.weight": g1, "post_attention_layernorm.weight": g2})
+    block.bind({k: v.to(DEV) for k, v in tensors.items()})
+    cache = CacheManager([block.mixer.cache_request()], 8, 16, 2, dtype=dtype, device=DEV)
+    h0 = rnd(T, H, seed=5)
+    h = h0.clone().to(DEV)
+    block.forward(h, make_batch(cache, [("a", T)]), cache.views[0], True)
+    assert ops.pending_target() is h          # the down projection's sum is still open when the block returns
+    ops.resolve_pending()
+
+    def plain_norm(x, g):
+        if norm == "rmsnorm":
+            return plain_rmsnorm(x, g.double(), 1e-5)
+        return x * g.double() / (1 + x.abs().mean(-1, keepdim=True))
+
+    x = h0.double()
+    n1 = plain_norm(x, g1)
+    Wd = {k: v.double() for k, v in Wa.items()}
+    pos, inv = torch.arange(T), plain_inv_freq(hd, 1e4, None)
+    q = plain_rope(plain_linear(n1, Wd["q_proj.weight"], Wd["q_proj.bias"]).view(T, nh, hd), pos, inv)
+    k = plain_rope(plain_linear(n1, Wd["k_proj.weight"], Wd["k_proj.bias"]).view(T, nkv, hd), pos, inv)
+    v = plain_linear(n1, Wd["v_proj.weight"], Wd["v_proj.bias"]).view(T, nkv, hd)
+    x = x + plain_linear(plain_attention(q, k, v).reshape(T, nh * hd), Wd["o_proj.weight"])
+    n2 = plain_norm(x, g2)
+    x = x + plain_linear(plain_swiglu(plain_linear(n2, Wf["gate_proj.weight"].double()),
+                                      plain_linear(n2, Wf["up_proj.weight"].double())), Wf["down_proj.weight"].double())
+    assert float((h.double().cpu() - x).abs().max()) <= TOL[dtype] * float(x.abs().max())
 
 
 # ---------------------------------------------------------------------------------------------
