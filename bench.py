@@ -251,8 +251,8 @@ def name_launchers(cfg):
 
     def rename(tag):
         fn, _, shape = tag.partition(" ")
-        if fn in ("bw_gemm_tc", "bw_gemm_tc_rope") and shape:
-            dims = shape.replace("rope", "").split("x")
+        if fn in ("bw_gemm_tc", "bw_gemm_tc_rope", "bw_gemm_tc_planes") and shape:
+            dims = shape.replace("rope", "").replace("planes", "").split("x")
             N, K = int(dims[1]), int(dims[2])
             if fn == "bw_gemm_tc_rope" or (N, K) == (qkv, H):
                 return "gemm_qkv" + ("+rope+append" if fn == "bw_gemm_tc_rope" else "")
@@ -265,7 +265,7 @@ def name_launchers(cfg):
             if (N, K) == (V, H):
                 return "gemm_lm_head"
         return {"bw_attention_tc": "attention_prefill_tcgen05", "bw_attention_mma": "attention_decode_mma",
-                "bw_rmsnorm": "rmsnorm", "bw_rope_table": "rope_table", "bw_kv_slots": "kv_slots",
+                "bw_rmsnorm": "rmsnorm", "bw_add_rmsnorm": "rmsnorm", "bw_rope_table": "rope_table", "bw_kv_slots": "kv_slots",
                 "bw_rope_append": "rope_append", "bw_embed_gather": "embed_gather"}.get(fn, fn)
     return rename
 

@@ -372,7 +372,10 @@ BW_EXPORT int bw_add_rmsnorm(float* x, const float* planes, int n_planes, long l
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = H % 4 == 0 && plane_stride % 4 == 0 &&
                      (((uintptr_t)x | (uintptr_t)planes | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
-    const int threads = vec ? (H >= 4096 ? 1024 : (H >= 1024 ? 256 : 128)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
+    // one pass over the row: a thread per four elements (up to 1,024 threads), so that the loads of
+    // the stream and of all planes are in flight at once
+    const int quads = (H / 4 + 31) / 32 * 32;
+    const int threads = vec ? (quads > 1024 ? 1024 : (quads < 128 ? 128 : quads)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
 #define BW_ARMS(WT, OT) do { if (vec) bw::launch((add_rmsnorm_kernel<WT, OT, true>), dim3(n_rows), dim3(threads), 0, s, x, planes, n_planes, (size_t)plane_stride, cp<WT>(w), rows, mp<OT>(out), H, eps); \
         else bw::launch((add_rmsnorm_kernel<WT, OT, false>), dim3(n_rows), dim3(threads), 0, s, x, planes, n_planes, (size_t)plane_stride, cp<WT>(w), rows, mp<OT>(out), H, eps); } while (0)
     if (w_type == BW_F32 && out_type == BW_F32) BW_ARMS(float, float);
