@@ -1107,6 +1107,8 @@ BW_EXPORT double bw_gemm_tc_pair_plan(int M, int N, int K, int force_splits, lon
     return best;
 }
 
+constexpr int PLANES_MAX_TOKENS = 256;   // bw_gemm_tc_planes: the orientation with the features in the 128-row dimension
+
 // out[M, N] (=|+=) x[M, K] . w[N, K]^T (+ bias[N]).  x, w bf16; out float32 or bf16
 // (accumulate: float32).  swiglu != 0: w holds gate and up rows interleaved in blocks of 16
 // (16 gate rows, the 16 up rows of the same features, ...), N = 2 I with I a multiple of 16,
@@ -1121,7 +1123,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     // planes_out: the product is left as *planes_out float32 planes [M, N] in `out` (row stride N, the bias
     // in the first), to be added up by its reader; K is split as if the sums were made here.
     const bool planes = planes_out != nullptr;
-    if (planes && (M > FUSED_REDUCE_MAX_TOKENS || out_type != BW_F32 || accumulate || swiglu || rope || ldo != N ||
+    if (planes && (M > PLANES_MAX_TOKENS || out_type != BW_F32 || accumulate || swiglu || rope || ldo != N ||
                    workspace != (float*)out))
         return BW_ERR_BAD_ARG;
     const int NUM_SMS = bw::num_sms();
@@ -1238,7 +1240,7 @@ BW_EXPORT int bw_gemm_tc(const void* x, const void* w, const void* bias, int bia
                        workspace_elems, counters, n_counters, force_splits, nullptr, stream);
 }
 
-// The product of up to 16 tokens as float32 planes: planes[p][m][n] for p < *n_planes add up to
+// The product of up to 256 tokens as float32 planes: planes[p][m][n] for p < *n_planes add up to
 // x[M, K] . w[N, K]^T (+ bias, which is part of plane 0), in plane order.  K is split as bw_gemm_tc
 // would split it, but no CTA waits for another's partial sums: the kernel that reads the result adds
 // the planes (bw_add_rmsnorm, bw_add_planes, bw_rope_append).  planes_elems: room in `planes` (floats).

@@ -38,7 +38,7 @@ class Linear:
         of the K splits is left to the next reader of ``residual`` (``ops.gemm_tc_deferred``)."""
         w = self.weight
         if (ops.DEFER_SUMS and w.dtype == torch.bfloat16 and x.dtype == w.dtype
-                and x.shape[0] <= ops.GEMM_FUSED_REDUCE_MAX_TOKENS and residual.dtype == torch.float32
+                and x.shape[0] <= ops.DEFER_MAX_TOKENS and residual.dtype == torch.float32
                 and residual.is_contiguous() and ops.gemm_tc_supports(x, w)):
             ops.gemm_tc_deferred(x, w, self.bias, residual)
         else:

@@ -75,7 +75,7 @@ def test_gemm_tc_split_k(ops, M, splits):
 
 # ------------------------------------------------------------------ sums left to the reader
 
-@pytest.mark.parametrize("M", [1, 3, 8, 16])
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 64, 100, 256])
 @pytest.mark.parametrize("N,K,force", [(4096, 4096, 0), (1000, 2056, 0), (6144, 512, 0), (384, 14336, 0), (520, 2240, 3),
                                        (128 * 149, 256, 0)])
 def test_gemm_tc_planes_add_up_to_the_product(ops, M, N, K, force):
@@ -89,7 +89,7 @@ def test_gemm_tc_planes_add_up_to_the_product(ops, M, N, K, force):
         assert planes.shape[0] == force
     if (N, K) == (384, 14336):
         assert planes.shape[0] > 1                  # three tiles and a long K: the planner splits
-    if N == 128 * 149:
+    if N == 128 * 149 and M <= 16:
         assert planes.shape[0] == 1                 # more tiles than SMs: one plane, written as the result
     total = planes[0].clone()
     for p in range(1, planes.shape[0]):
@@ -99,7 +99,7 @@ def test_gemm_tc_planes_add_up_to_the_product(ops, M, N, K, force):
     again = ops.gemm_tc_planes(x, w, b, force_splits=force).clone()
     assert torch.equal(again, ops.gemm_tc_planes(x, w, b, force_splits=force))
     with pytest.raises(ops.KernelError):
-        ops.gemm_tc_planes(rand(17, K, dtype=torch.bfloat16).to(DEV), w)
+        ops.gemm_tc_planes(rand(257, K, dtype=torch.bfloat16).to(DEV), w)
 
 
 @pytest.mark.parametrize("H,K", [(4096, 4096), (1000, 2056), (72, 200), (130, 14336)])
