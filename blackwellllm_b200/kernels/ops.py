@@ -149,13 +149,13 @@ DEFER_SUMS = os.environ.get("BW_DEFER_SUMS", "1") != "0"
 DEFER_MAX_TOKENS = int(os.environ.get("BW_DEFER_MAX_TOKENS", "128"))
 _pending = None          # (target tensor, planes [S, M, N]) or None
 _plane_buffers = {}
-_PLANE_BUFFER_ELEMS = 8 << 20
+PLANE_BUFFER_ELEMS = 8 << 20
 
 
 def _plane_buffer(device: torch.device) -> torch.Tensor:
     buf = _plane_buffers.get(device)
     if buf is None:
-        buf = _plane_buffers[device] = torch.empty(_PLANE_BUFFER_ELEMS, dtype=torch.float32, device=device)
+        buf = _plane_buffers[device] = torch.empty(PLANE_BUFFER_ELEMS, dtype=torch.float32, device=device)
     return buf
 
 

@@ -37,8 +37,9 @@ class Linear:
         """``residual += x @ W.T (+ bias)`` (float32).  For a few tokens on the tensor-core path the sum
         of the K splits is left to the next reader of ``residual`` (``ops.gemm_tc_deferred``)."""
         w = self.weight
-        if (ops.DEFER_SUMS and w.dtype == torch.bfloat16 and x.dtype == w.dtype
-                and x.shape[0] <= ops.DEFER_MAX_TOKENS and residual.dtype == torch.float32
+        T = x.shape[0]
+        if (ops.DEFER_SUMS and w.dtype == torch.bfloat16 and x.dtype == w.dtype and T <= ops.DEFER_MAX_TOKENS
+                and T * w.shape[0] <= ops.PLANE_BUFFER_ELEMS and residual.dtype == torch.float32
                 and residual.is_contiguous() and ops.gemm_tc_supports(x, w)):
             ops.gemm_tc_deferred(x, w, self.bias, residual)
         else:
