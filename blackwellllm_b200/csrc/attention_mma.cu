@@ -43,6 +43,13 @@ struct Params {
     float* part_o; float* part_ml; // slices' partial results (attn_keys_kernel)
     int max_blocks, nh, nkv, G, page_size, num_pages, window;
     float scale_log2;
+    // Decode rows straight from the q/k/v product (attn_keys_tma_kernel only; null: q holds the queries and
+    // the cache this step's keys and values): qkv is float32 [planes][tokens][(nh + 2 nkv) * HD] to be added
+    // up in plane order, the rotated channels of the q and k heads as (channel j, channel j + rd / 2) pairs;
+    // rope_table is [tokens][rd] (cosines, then sines); append != 0: the CTA whose slice holds the token's
+    // own position writes the rotated key and the value to the cache.  Every request has one token.
+    const float* qkv; long long qkv_plane_stride; const float* rope_table;
+    int qkv_planes, rd, append;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -525,8 +532,84 @@ __device__ __forceinline__ void process_keys_swz(const uint32_t (&qf)[KSTEPS][4]
 }
 
 constexpr int KEYS_TMA_TILES = 4 * TMA_TILE;                      // 2 stages of K and V
-constexpr int KEYS_TMA_LOOP = KEYS_TMA_TILES + 16 * ROW_BYTES + 64 + 1024;   // + query rows + barriers + alignment slack
+constexpr int KEYS_TMA_LOOP = KEYS_TMA_TILES + 16 * ROW_BYTES + 64 + 4 * HD + 1024;   // + query rows + barriers + the token's own key and value + alignment slack
 constexpr int SMEM_KEYS_TMA = KEYS_TMA_LOOP > SMEM_KEYS_MERGE_BYTES + 1024 ? KEYS_TMA_LOOP : SMEM_KEYS_MERGE_BYTES + 1024;
+
+// The decode token's query rows (the G heads of kv head g) from the unsummed q/k/v product, rotated, into
+// the 16 padded rows of q_tile (the other rows zero); with want_kv also the token's rotated key and its value
+// into kv_new [2][HD] (shared memory) and, if the token's page exists, into the cache.  A unit of work
+// is two neighbouring floats of a head: a (channel j, channel j + rd / 2) pair of a q or k head, two
+// channels in place elsewhere; four units a thread and four planes at a time are in flight together.
+__device__ __forceinline__ void rows_from_qkv(const Params& p, int tok, int g, int pos, const int* bt,
+                                              uint8_t* q_tile, bf16* kv_new, bool want_kv) {
+    const int half = p.rd >> 1;
+    const size_t width = (size_t)(p.nh + 2 * p.nkv) * HD;
+    const float* row = p.qkv + (size_t)tok * width;
+    const float* tab = p.rope_table + (size_t)tok * p.rd;
+    const int units = (p.G + (want_kv ? 2 : 0)) * (HD / 2);
+    bf16* k_dst = nullptr; bf16* v_dst = nullptr;
+    if (want_kv) {
+        const int page = bt[pos / p.page_size];
+        if (page >= 0 && page < p.num_pages) {
+            const size_t at = (((size_t)page * p.nkv + g) * p.page_size + pos % p.page_size) * HD;
+            k_dst = const_cast<bf16*>(p.k_pages) + at; v_dst = const_cast<bf16*>(p.v_pages) + at;
+        }
+    }
+    for (int idx = threadIdx.x; idx < (16 - p.G) * CPR; idx += THREADS)   // rows that hold no query
+        *reinterpret_cast<uint4*>(q_tile + (p.G + idx / CPR) * ROW_BYTES + (idx % CPR) * 16) = make_uint4(0, 0, 0, 0);
+    for (int u0 = threadIdx.x; u0 < units; u0 += 4 * THREADS) {
+        const float* src[4];
+        float2 acc[4];
+        float cs[4], sn[4];
+        int hs[4], j[4];
+        bool rot[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int u = u0 + i * THREADS;
+            hs[i] = u < units ? u / (HD / 2) : -1;
+            j[i] = u - (u / (HD / 2)) * (HD / 2);
+            const int head = hs[i] < p.G ? g * p.G + hs[i] : (hs[i] == p.G ? p.nh + g : p.nh + p.nkv + g);
+            src[i] = row + (size_t)head * HD + 2 * j[i];
+            rot[i] = hs[i] >= 0 && hs[i] <= p.G && 2 * j[i] < p.rd;      // a q or k head's rotated pair
+            acc[i] = make_float2(0.f, 0.f);
+            cs[i] = rot[i] ? tab[j[i]] : 1.f;
+            sn[i] = rot[i] ? tab[half + j[i]] : 0.f;
+        }
+        for (int p0 = 0; p0 < p.qkv_planes; p0 += 4) {
+            float2 t[4][4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    t[q][i] = (hs[i] >= 0 && p0 + q < p.qkv_planes)
+                        ? *reinterpret_cast<const float2*>(src[i] + (size_t)(p0 + q) * p.qkv_plane_stride) : make_float2(0.f, 0.f);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { acc[i].x += t[q][i].x; acc[i].y += t[q][i].y; }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (hs[i] < 0) continue;
+            // x cos - partner sin for the first half's channel, x cos + partner sin for the second's
+            const float a = rot[i] ? acc[i].x * cs[i] + acc[i].y * -sn[i] : acc[i].x;
+            const float b = rot[i] ? acc[i].y * cs[i] + acc[i].x * sn[i] : acc[i].y;
+            const int c0 = rot[i] ? j[i] : 2 * j[i], c1 = rot[i] ? j[i] + half : 2 * j[i] + 1;
+            const bf16 va = __float2bfloat16_rn(a), vb = __float2bfloat16_rn(b);
+            if (hs[i] < p.G) {
+                bf16* qr = reinterpret_cast<bf16*>(q_tile + hs[i] * ROW_BYTES);
+                qr[c0] = va; qr[c1] = vb;
+            } else {
+                bf16* st = kv_new + (hs[i] - p.G) * HD;
+                st[c0] = va; st[c1] = vb;
+                bf16* dst = hs[i] == p.G ? k_dst : v_dst;
+                if (dst) { dst[c0] = va; dst[c1] = vb; }
+            }
+        }
+    }
+}
 
 // Warp 0 issues the boxes of the next tile while all four warps work on the current one.  (A
 // separate producer warp with deeper stages was measured slower: its registers cost the third
@@ -539,6 +622,7 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     uint8_t* kv = smem;                           // [2 stages][K tile, V tile], each 1024-aligned (swizzle)
     uint8_t* q_tile = smem + KEYS_TMA_TILES;      // 16 padded rows
     uint64_t* bars = reinterpret_cast<uint64_t*>(q_tile + 16 * ROW_BYTES);
+    bf16* kv_new = reinterpret_cast<bf16*>(q_tile + 16 * ROW_BYTES + 64);   // [2][HD]: the token's own key and value
     const uint32_t full0 = smem_u32(bars);
     if (threadIdx.x == 0) {
         bw::mbar_init(full0, 1); bw::mbar_init(full0 + 8, 1);
@@ -601,11 +685,19 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const bool early = t_lo <= t_hi && t_lo * BN + BN <= q_pos0;
     if (early && warp == 0) { lookup(t_lo); issue_tile(0); lookup(t_lo + 1); }
     BW_PDL_WAIT();
+    // from the unsummed q/k/v product: the slice that holds the token's own position (one per request and
+    // kv head, never empty) also makes the token's key and value and puts them into its tile below
+    const int t_own = last_pos / BN;
+    const bool own = p.qkv != nullptr && p.append && t_lo <= t_own && t_own <= t_hi;
     if (t_lo <= t_hi) {
         if (!early && warp == 0) { lookup(t_lo); issue_tile(0); lookup(t_lo + 1); }
-        load_q_rows(p, p.cu_q[r], g, 0, n_rows, q_tile, 16);
-        cp_async_commit();
-        cp_async_wait<0>();
+        if (p.qkv) {
+            rows_from_qkv(p, p.cu_q[r], g, last_pos, bt, q_tile, kv_new, own);
+        } else {
+            load_q_rows(p, p.cu_q[r], g, 0, n_rows, q_tile, 16);
+            cp_async_commit();
+            cp_async_wait<0>();
+        }
         __syncthreads();
         uint32_t qf[KSTEPS][4];
         load_q_frags(q_tile, qf);
@@ -616,6 +708,18 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             uint8_t* v_tile = k_tile + TMA_TILE;
             if (warp == 0 && t < t_hi) { issue_tile(stage ^ 1); lookup(t + 2); }
             ok = bw::mbar_wait(full0 + 8 * stage, (i >> 1) & 1, &g_tma_status, 21);
+            if (own && t == t_own) {
+                // the cache's row of the token's own position was loaded as it was before this step: the
+                // key and value made above take its place (swizzled like the boxes around it)
+                const int rk = last_pos - t * BN;
+                for (int idx = threadIdx.x; idx < 2 * CPR; idx += THREADS) {
+                    const int which = idx / CPR, ch = idx - which * CPR;
+                    uint8_t* tile = which ? v_tile : k_tile;
+                    *reinterpret_cast<uint4*>(tile + (ch >> 3) * SLICE_BYTES + rk * 128 + (((ch & 7) ^ (rk & 7)) << 4)) =
+                        *reinterpret_cast<const uint4*>(kv_new + which * HD + ch * 8);
+                }
+                __syncthreads();
+            }
             // Rows of keys that do not exist hold whatever was there: values times a probability of
             // 0 must still be 0, so those rows of V are cleared (only in a request's last tile or at
             // a window's edge).
@@ -728,14 +832,30 @@ BW_EXPORT int bw_attention_head_dim() { return HD; }
 // keys_work: n_keys_items int4 (request, slice, slices, item) for the others; merge_work: one int4 per
 // item that has more than one slice.  part_o / part_ml: float32 scratch for
 // [items, nkv, slices, 16, HD] and [.., 2].  window <= 0: all keys.
+// qkv != null (q may be null then): every request has ONE token, and its queries, key and value come from
+// the q/k/v product itself: float32 [qkv_planes][tokens][(nh + 2 nkv) * HD], the planes qkv_plane_stride
+// floats apart and added in order, the rotated channels of the q and k heads as (j, j + rd / 2) pairs;
+// rope_table float32 [tokens][rd] (cosines, then sines); append != 0: key and value also go to the cache.
+// Only where the TMA key-slice kernel runs (head size a multiple of 64, pages of 8 to 64 tokens);
+// BW_ERR_UNSUPPORTED otherwise, and nothing was launched.
 BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
                                const int* q_start, const int* kv_len, const int* block_table, int max_blocks,
                                const int* rows_work, int n_rows_items, const int* keys_work, int n_keys_items,
                                const int* merge_work, int n_merge_items, float* part_o, float* part_ml, int nh,
-                               int nkv, int page_size, int num_pages, int window, float scale, void* stream) {
+                               int nkv, int page_size, int num_pages, int window, float scale,
+                               const float* qkv, int qkv_planes, long long qkv_plane_stride, const float* rope_table,
+                               int rd, int append, void* stream) {
     if (nkv <= 0 || nh % nkv != 0) return BW_ERR_BAD_ARG;
     const int G = nh / nkv;
     if (G > 16) return BW_ERR_UNSUPPORTED;
+    const bool tma_keys = HD % 64 == 0 && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
+                          (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
+    if (qkv) {
+        if (!tma_keys) return BW_ERR_UNSUPPORTED;
+        if (n_rows_items > 0 || qkv_planes < 1 || rd < 0 || rd > HD || (rd & 1) || (rd > 0 && !rope_table) ||
+            (((uintptr_t)qkv | (uintptr_t)(qkv_plane_stride * 4)) & 7))
+            return BW_ERR_BAD_ARG;
+    } else if (!q) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     static bool rows_attr_done[bw::MAX_DEVICES], keys_attr_done[bw::MAX_DEVICES];
     if (cudaError_t e = bw::allow_dynamic_smem(attn_rows_kernel, SMEM_ROWS, rows_attr_done); e != cudaSuccess) return (int)e;
@@ -747,6 +867,8 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
     p.max_blocks = max_blocks; p.nh = nh; p.nkv = nkv; p.G = G; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window > 0 ? window : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.qkv = qkv; p.qkv_plane_stride = qkv_plane_stride; p.rope_table = rope_table;
+    p.qkv_planes = qkv_planes; p.rd = rd; p.append = append;
     if (n_rows_items > 0) {
         p.work = rows_work;
         bw::launch((attn_rows_kernel), dim3(dim3(n_rows_items, nkv)), dim3(THREADS), SMEM_ROWS, s, p, 64 / G);
@@ -756,8 +878,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
         p.work = keys_work;
         bool launched = false;
 #if HEAD_DIM % 64 == 0
-        if ((page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
-            (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0) {
+        if (tma_keys) {
             static bool tma_attr_done[bw::MAX_DEVICES];
             if (cudaError_t e = bw::allow_dynamic_smem(attn_keys_tma_kernel, SMEM_KEYS_TMA, tma_attr_done); e != cudaSuccess) return (int)e;
             CUtensorMap tk, tv;

@@ -628,11 +628,32 @@ def check_attention_supported(dtype: torch.dtype, head_dim: int, group: int = 1)
                           f"{MAX_GROUP_BF16}")
 
 
-def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
+class UnrotatedQKV:
+    """The q/k/v product of a step in which every request has ONE token, left as float32 planes
+    (:func:`gemm_tc_planes`, rows in the order of :func:`rotary_row_order`), with what the rotation needs:
+    :func:`paged_attention` rotates the queries, and rotates and appends the keys and values, inside its
+    key-slice kernel where that kernel runs; ``materialise()`` does it with :func:`rope_append` elsewhere."""
+
+    def __init__(self, planes: torch.Tensor, table: Optional[torch.Tensor], rotary_dim: int, append: bool, materialise):
+        self.planes, self.table, self.rotary_dim, self.append, self.materialise = planes, table, rotary_dim, append, materialise
+
+
+def attention_takes_unrotated(hd: int, page_size: int) -> bool:
+    """Whether the decode attention can rotate and append by itself (:class:`UnrotatedQKV`): the TMA
+    key-slice kernel's sizes.  BW_ATTN_FUSED_ROPE=0 in the environment says no."""
+    return (os.environ.get("BW_ATTN_FUSED_ROPE", "1") != "0" and hd % 64 == 0 and hd <= 256
+            and page_size in (8, 16, 32, 64))
+
+
+def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
                     block_table: torch.Tensor, nh: int, window: Optional[int], scale: float) -> torch.Tensor:
     """Causal attention of the batch's tokens over the paged cache (which already
-    holds this step's keys and values).  float32: the CUDA-core kernel; bfloat16:
-    the tensor-core kernel built for this head size."""
+    holds this step's keys and values, unless ``q`` is an :class:`UnrotatedQKV`).  float32: the
+    CUDA-core kernel; bfloat16: the tensor-core kernel built for this head size."""
+    if isinstance(q, UnrotatedQKV):
+        if batch.T == batch.R and attention_takes_unrotated(k_pages.shape[3], k_pages.shape[2]):
+            return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale)
+        q = q.materialise()
     if q.dtype == torch.float32:
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
                               window, scale)
@@ -640,7 +661,8 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
 
 
 _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                   c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+                                   c_int, c_int, c_int, c_int, c_int, c_float,
+                                   c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_void_p]
 
 
 _sm_counts = {}
@@ -725,24 +747,41 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
     return work
 
 
-def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_table: torch.Tensor,
+def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_table: torch.Tensor,
                   nh: int, window: Optional[int], scale: float) -> torch.Tensor:
-    _dev(q, "q", torch.bfloat16); _dev(k_pages, "k_pages", torch.bfloat16); _dev(v_pages, "v_pages", torch.bfloat16)
+    _dev(k_pages, "k_pages", torch.bfloat16); _dev(v_pages, "v_pages", torch.bfloat16)
     _dev(block_table, "block_table", torch.int32)
     num_pages, nkv, page_size, hd = k_pages.shape
-    if q.shape[1] != nh * hd or nh % nkv:
-        raise KernelError("attention: q must be [T, nh * head_dim] with nh a multiple of the kv heads")
+    raw = q if isinstance(q, UnrotatedQKV) else None
+    if raw is not None:
+        planes = _dev(raw.planes, "qkv planes", torch.float32)
+        if batch.T != batch.R:
+            raise KernelError("attention: unrotated q/k/v only with one token per request")
+        if planes.dim() != 3 or planes.shape[2] != (nh + 2 * nkv) * hd or nh % nkv or planes.shape[1] != batch.R:
+            raise KernelError("attention: unrotated q/k/v must be planes [S, requests, (nh + 2 nkv) * head_dim]")
+        if raw.rotary_dim:
+            _dev(raw.table, "table", torch.float32)
+            if tuple(raw.table.shape) != (planes.shape[1], raw.rotary_dim):
+                raise KernelError("attention: the cos/sin table must be [T, rotary_dim]")
+        q = None
+        out = torch.empty((planes.shape[1], nh * hd), dtype=torch.bfloat16, device=planes.device)
+    else:
+        _dev(q, "q", torch.bfloat16)
+        if q.shape[1] != nh * hd or nh % nkv:
+            raise KernelError("attention: q must be [T, nh * head_dim] with nh a multiple of the kv heads")
+        out = torch.empty_like(q)
     G = nh // nkv
     check_attention_supported(torch.bfloat16, hd, G)
     # prompt portions: the tcgen05 kernel (128-row tiles) where it takes the geometry, else mma.sync (64-row tiles)
     use_tc = attention_tc_supports(hd, G, page_size)
     rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices = attention_work(
         batch, G, nkv, window, hd, rows_tile=128 if use_tc else 64, page_size=page_size)
-    out = torch.empty_like(q)
     part_o = part_ml = None
     if n_merge:
-        part_o = torch.empty((slices * nkv * 16, hd), dtype=torch.float32, device=q.device)
-        part_ml = torch.empty((slices * nkv * 16, 2), dtype=torch.float32, device=q.device)
+        part_o = torch.empty((slices * nkv * 16, hd), dtype=torch.float32, device=out.device)
+        part_ml = torch.empty((slices * nkv * 16, 2), dtype=torch.float32, device=out.device)
+    if raw is not None and n_rows:
+        raise KernelError("attention: unrotated q/k/v only with one token per request")
     if use_tc and n_rows:
         tc = _fn("attention_tc", "bw_attention_tc", _ATTN_TC_ARGS, macros=attention_tc_macros(hd))
         _check(tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
@@ -755,7 +794,10 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
               _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, _ptr(keys_w),
               n_keys, _ptr(merge_w), n_merge, _ptr(part_o), _ptr(part_ml), nh, nkv, page_size, num_pages,
-              int(window or 0), float(scale), _stream()), "attention_mma")
+              int(window or 0), float(scale),
+              _ptr(raw.planes if raw is not None else None), raw.planes.shape[0] if raw is not None else 0,
+              raw.planes.stride(0) if raw is not None else 0, _ptr(raw.table if raw is not None else None),
+              raw.rotary_dim if raw is not None else 0, int(raw.append) if raw is not None else 0, _stream()), "attention_mma")
     return out
 
 

@@ -74,9 +74,17 @@ class RotaryEncoding(PositionEncoding):
                 # adds while it reads them (the rotation in the product's own epilogue, after a sum
                 # of the splits in its last warps, was measured slower than a kernel of its own)
                 qkv = ops.gemm_tc_planes(x, w, b) if ops.DEFER_SUMS else ops.gemm_tc(x, w, b, out_dtype=torch.float32)
-                return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
-                                       self.inv_freq, self.rotary_dim, cache.k_pages, cache.v_pages, nh, nkv, hd,
-                                       append=append, table=self._table(batch), paired=True)
+                table = self._table(batch)
+
+                def rotate():
+                    return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
+                                           self.inv_freq, self.rotary_dim, cache.k_pages, cache.v_pages, nh, nkv, hd,
+                                           append=append, table=table, paired=True)
+                if (qkv.dim() == 3 and batch.T == batch.R
+                        and ops.attention_takes_unrotated(hd, cache.k_pages.shape[2])):
+                    # one token per request: the attention's key-slice kernel rotates and appends by itself
+                    return ops.UnrotatedQKV(qkv, table, self.rotary_dim, append, rotate)
+                return rotate()
             slots = None
             if append:   # where the step's tokens go in this cache group: the same for all its layers
                 key = ("kv_slots", cache.group)

@@ -530,6 +530,53 @@ def test_attention_far_key_and_window_edge(ops, dtype):
         assert float((o_out.double().cpu() - ref).abs().max()) <= ATT_TOL[dtype] * float(ref.abs().max())
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rd,page", [(8, 2, 128, 128, 16), (4, 4, 64, 64, 8), (16, 1, 192, 64, 32), (6, 2, 128, 0, 64)])
+@pytest.mark.parametrize("window,append", [(None, True), (100, True), (None, False)])
+def test_decode_attention_rotates_and_appends_from_the_unsummed_product(ops, nh, nkv, hd, rd, page, window, append):
+    """One token per request: the key-slice kernel makes the rotated queries, and the token's rotated key and its
+    value, from the planes of the q/k/v product itself and writes key and value to the cache.  Compared with the
+    rotation kernel followed by the same attention on a cache of its own: the same output and the same pages
+    (up to the last bit of a bfloat16: the two kernels' products may be contracted differently).  The tokens'
+    positions sit in the middle of a tile, at a tile's and a page's first and last key, and alone in a cache."""
+    kv_lens = [1, 17, 64, 65, 200, 1000, 3000, 128, 4 * page + 1]
+    R = len(kv_lens)
+    q_lens = [1] * R
+    K = 1024 + 64 * 3
+    width = (nh + 2 * nkv) * hd
+    x = rand(R, K, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rand(width, K, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    b = rand(width, seed=3, scale=0.3).to(DEV)
+    _, kp, vp, table, _ = paged_case(q_lens, kv_lens, nh, nkv, hd, page, torch.bfloat16, seed=7)
+    # the cache's rows of the tokens' own positions hold what an earlier user of the page left: NaN
+    batch = FakeBatch(q_lens, kv_lens)
+    for r, L in enumerate(kv_lens):
+        pid, slot = int(table[r, (L - 1) // page]), (L - 1) % page
+        if append:
+            kp[pid, :, slot] = float("nan"); vp[pid, :, slot] = float("nan")
+    inv = (1e4 ** (-torch.arange(rd // 2, dtype=torch.float64) * 2 / max(rd, 1))).float().to(DEV)
+    tab = ops.rope_table(batch.positions, inv, rd) if rd else None
+    planes = ops.gemm_tc_planes(x, w, b, force_splits=3).clone()
+    caches = [(kp.clone(), vp.clone()) for _ in range(2)]
+    q = ops.rope_append(planes, batch.positions, batch.req_of_token, table, inv if rd else None, rd, caches[0][0], caches[0][1],
+                        nh, nkv, hd, append=append, table=tab, paired=True)
+    ref = ops.attention_mma(q, caches[0][0], caches[0][1], batch, table, nh, window, hd ** -0.5)
+    raw = ops.UnrotatedQKV(planes, tab, rd, append, None)
+    out = ops.attention_mma(raw, caches[1][0], caches[1][1], FakeBatch(q_lens, kv_lens), table, nh, window, hd ** -0.5)
+    assert not torch.isnan(out).any() and not torch.isnan(ref).any()
+    assert float((out.float() - ref.float()).abs().max()) <= ATT_TOL[torch.bfloat16] * float(ref.float().abs().max())
+    for mine, theirs in zip(caches[1], caches[0]):
+        same_nan = torch.isnan(mine) == torch.isnan(theirs)
+        assert bool(same_nan.all())                                    # exactly the same rows were written
+        a, c = torch.nan_to_num(mine.float()), torch.nan_to_num(theirs.float())
+        assert float((a - c).abs().max()) <= 2 ** -7 * float(c.abs().max())
+    if append:
+        for r, L in enumerate(kv_lens):                                # and they were written: no NaN is left there
+            pid, slot = int(table[r, (L - 1) // page]), (L - 1) % page
+            assert not torch.isnan(caches[1][0][pid, :, slot]).any() and not torch.isnan(caches[1][1][pid, :, slot]).any()
+    with pytest.raises(ops.KernelError):                               # a request with two tokens: refused
+        ops.attention_mma(raw, caches[1][0], caches[1][1], FakeBatch([1] * (R - 1) + [2], kv_lens), table, nh, window, hd ** -0.5)
+
+
 def test_attention_decode_slices_and_static_bound(ops):
     """Long decode rows are cut into key slices; a graph-style static bound changes
     the number of slices but not the result beyond rounding."""
