@@ -76,7 +76,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu_id, f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -517,9 +517,9 @@ def main():
     sampler.start()
     B = args.batch
     ms_step, launches = decode_device(B, args.steps, args.warmup)
-    clocks = sampler.stop()
     e2e_ms = decode_e2e(B, args.steps, args.warmup)
     e2e_pipe_ms = decode_e2e_pipelined(B, args.steps, args.warmup)
+    clocks = sampler.stop()      # over the three timed decode regions (device, end to end, pipelined)
     graph_launches = getattr(eng, "graph_kernel_count", lambda n: 0)(B)
     if graph_launches:
         launches = graph_launches * args.steps
