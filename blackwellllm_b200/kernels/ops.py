@@ -150,6 +150,7 @@ DEFER_MAX_TOKENS = int(os.environ.get("BW_DEFER_MAX_TOKENS", "128"))
 _pending = None          # (target tensor, planes [S, M, N]) or None
 _plane_buffers = {}
 PLANE_BUFFER_ELEMS = 8 << 20
+_plane_generation = 0    # counts the products that left planes: whoever keeps planes for later checks that they are still the last
 
 
 def _plane_buffer(device: torch.device) -> torch.Tensor:
@@ -203,9 +204,16 @@ def gemm_tc_planes(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
     fn = _fn("gemm_tc", "bw_gemm_tc_planes", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int,
                                                c_ll, c_int, ctypes.POINTER(c_int), c_void_p],
              macros=_gemm_macros(), tag=f"planes{M}x{N}x{K}" if _timings is not None else None)
+    global _plane_generation
+    _plane_generation += 1
     _check(fn(_ptr(x), _ptr(w), _ptr(bias), _code(bias, "bias") if bias is not None else 0, _ptr(buf), buf.numel(),
               M, N, K, x.stride(0), int(force_splits), ctypes.byref(n), _stream()), "gemm_tc_planes")
     return buf[:n.value * M * N].view(n.value, M, N)
+
+
+def planes_generation() -> int:
+    """A number that changes with every product that leaves planes in this module's buffer."""
+    return _plane_generation
 
 
 def gemm_tc_deferred(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
@@ -220,13 +228,20 @@ def gemm_tc_deferred(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype,
             rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     global _pending
-    planes = None
+    mine = None              # an outstanding sum into x: added by the kernel below instead of one of its own
     if _pending is not None and _pending[0].data_ptr() == x.data_ptr() and _pending[0].shape == x.shape:
-        planes = _pending[1]
-        if rows is None:
-            _pending = None       # x itself is brought up to date by the kernel below
-        else:
-            saved, _pending = _pending, None
+        mine, _pending = _pending, None
+    keep = mine is not None  # the sum stays outstanding unless the kernel below adds it into x
+    try:
+        out = _rmsnorm(x, w, eps, out_dtype, rows, out, None if mine is None else mine[1])
+        keep = keep and rows is not None     # with chosen rows x is left as it is
+        return out
+    finally:
+        if keep:
+            _pending = mine
+
+
+def _rmsnorm(x, w, eps, out_dtype, rows, out, planes):
     _dev(x, "x", torch.float32); _dev(w, "w")
     H = x.shape[-1]
     if w.numel() != H:
@@ -242,8 +257,6 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype
                                                    c_int, c_int, c_int, c_float, c_void_p])
         _check(fn(_ptr(x), _ptr(planes), planes.shape[0], planes.stride(0), _ptr(w), _code(w, "w"), _ptr(rows), _ptr(out),
                   _code(out, "out"), n, H, float(eps), _stream()), "add_rmsnorm")
-        if rows is not None:
-            _pending = saved      # chosen rows only: x is unchanged and the sum stays outstanding
         return out
     fn = _fn("elementwise", "bw_rmsnorm",
              [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
@@ -636,6 +649,7 @@ class UnrotatedQKV:
 
     def __init__(self, planes: torch.Tensor, table: Optional[torch.Tensor], rotary_dim: int, append: bool, materialise):
         self.planes, self.table, self.rotary_dim, self.append, self.materialise = planes, table, rotary_dim, append, materialise
+        self.generation = _plane_generation    # the planes are this module's buffer: good until the next such product
 
 
 def attention_takes_unrotated(hd: int, page_size: int) -> bool:
@@ -755,6 +769,8 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
     raw = q if isinstance(q, UnrotatedQKV) else None
     if raw is not None:
         planes = _dev(raw.planes, "qkv planes", torch.float32)
+        if raw.generation != _plane_generation:
+            raise KernelError("attention: the unrotated q/k/v planes were overwritten by a later product")
         if batch.T != batch.R:
             raise KernelError("attention: unrotated q/k/v only with one token per request")
         if planes.dim() != 3 or planes.shape[2] != (nh + 2 * nkv) * hd or nh % nkv or planes.shape[1] != batch.R:

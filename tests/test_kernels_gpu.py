@@ -134,6 +134,15 @@ def test_rmsnorm_adds_an_outstanding_sum(ops, H, K, odt):
     assert ops.pending_target() is None
     assert float((res.double() - summed).abs().max()) / float(summed.abs().max()) <= 1e-5
 
+    # a norm that is refused (a gain of the wrong length) adds nothing: the sum stays outstanding
+    res = base.clone()
+    ops.gemm_tc_deferred(x, w, b, res)
+    with pytest.raises(ops.KernelError):
+        ops.rmsnorm(res, gain[:-1].contiguous(), eps, odt)
+    assert ops.pending_target() is res and torch.equal(res, base)
+    ops.resolve_pending()
+    assert float((res.double() - summed).abs().max()) / float(summed.abs().max()) <= 1e-5
+
 
 def test_an_outstanding_sum_is_made_before_anything_else_reads_or_replaces_it(ops):
     M, H, K = 5, 264, 520
@@ -575,6 +584,10 @@ def test_decode_attention_rotates_and_appends_from_the_unsummed_product(ops, nh,
             assert not torch.isnan(caches[1][0][pid, :, slot]).any() and not torch.isnan(caches[1][1][pid, :, slot]).any()
     with pytest.raises(ops.KernelError):                               # a request with two tokens: refused
         ops.attention_mma(raw, caches[1][0], caches[1][1], FakeBatch([1] * (R - 1) + [2], kv_lens), table, nh, window, hd ** -0.5)
+    live = ops.UnrotatedQKV(ops.gemm_tc_planes(x, w, b), tab, rd, append, None)
+    ops.gemm_tc_planes(x, w, b)                                        # a later product takes the plane buffer
+    with pytest.raises(ops.KernelError, match="overwritten"):
+        ops.attention_mma(live, caches[1][0], caches[1][1], FakeBatch(q_lens, kv_lens), table, nh, window, hd ** -0.5)
 
 
 def test_attention_decode_slices_and_static_bound(ops):
