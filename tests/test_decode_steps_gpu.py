@@ -39,6 +39,21 @@ def random_case(case):
 
 @pytest.mark.parametrize("case", range(24))
 def test_decode_only_steps_against_the_plain_model(case):
+    run_case(case)
+
+
+@pytest.mark.parametrize("sums_open,own_rotation", [(False, False), (False, True), (True, False)])
+@pytest.mark.parametrize("case", [1, 4, 9, 16])
+def test_decode_only_steps_with_the_switches_off(case, sums_open, own_rotation, monkeypatch):
+    """The paths behind the switches stay alive: every product sums its own K splits (BW_DEFER_SUMS=0) and / or
+    the rotation kernel runs in decode-only steps too (BW_ATTN_FUSED_ROPE=0)."""
+    from blackwellllm_b200.kernels import ops
+    monkeypatch.setattr(ops, "DEFER_SUMS", sums_open)
+    monkeypatch.setenv("BW_ATTN_FUSED_ROPE", "1" if own_rotation else "0")
+    run_case(case)
+
+
+def run_case(case):
     from blackwellllm_b200 import Engine, StepEntry
     from blackwellllm_b200.kernels import ops
     from blackwellllm_b200.weights.random_init import model_param_specs, random_tensors
