@@ -819,6 +819,46 @@ attn_merge_kernel(Params p, const int* merge_items) {
     }
 }
 
+// The same for items of at most MERGE_FEW slices (decode batches, where the slices are few): one CTA per
+// (item, kv head), a thread per row and four channels; every thread fetches the maxima and sums of its
+// row's slices itself, so all its loads are in flight together and nothing waits at a barrier.
+constexpr int MERGE_FEW = 8;
+__global__ void __launch_bounds__(16 * MERGE_QUADS)
+attn_merge_few_kernel(Params p, const int* merge_items) {
+    BW_PDL_TRIGGER();
+    const int4 w = reinterpret_cast<const int4*>(merge_items)[blockIdx.x];
+    const int r = w.x, n_slices = w.z, item = w.w, g = blockIdx.y;
+    const int row = threadIdx.x / MERGE_QUADS, quad = threadIdx.x - row * MERGE_QUADS;
+    BW_PDL_WAIT();
+    const int n_rows = (p.cu_q[r + 1] - p.cu_q[r]) * p.G;
+    if (row >= n_rows) return;
+    const size_t base0 = ((size_t)item * p.nkv + (size_t)g * n_slices) * 16 + row;
+    float4 part[MERGE_FEW];
+    float2 ml[MERGE_FEW];
+#pragma unroll
+    for (int sl = 0; sl < MERGE_FEW; ++sl) {
+        const bool there = sl < n_slices;
+        ml[sl] = there ? reinterpret_cast<const float2*>(p.part_ml)[base0 + (size_t)sl * 16] : make_float2(-INFINITY, 0.f);
+        part[sl] = there ? reinterpret_cast<const float4*>(p.part_o + (base0 + (size_t)sl * 16) * HD)[quad]
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int sl = 0; sl < MERGE_FEW; ++sl) M = fmaxf(M, ml[sl].x);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float L = 0.f;
+#pragma unroll
+    for (int sl = 0; sl < MERGE_FEW; ++sl) {
+        const float f = ml[sl].x == -INFINITY ? 0.f : exp2f(ml[sl].x - M);
+        acc.x += part[sl].x * f; acc.y += part[sl].y * f; acc.z += part[sl].z * f; acc.w += part[sl].w * f;
+        L += ml[sl].y * f;
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const int tok = row / p.G, hg = row - tok * p.G;
+    bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + quad * 4;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+}
+
 constexpr int SMEM_ROWS = (BN + 4 * BN) * ROW_BYTES;     // q tile of 64 rows + 2 stages of K and V
 constexpr int SMEM_KEYS_LOOP = (16 + 4 * BN) * ROW_BYTES;
 constexpr int SMEM_KEYS_MERGE = SMEM_KEYS_MERGE_BYTES;
@@ -830,7 +870,8 @@ BW_EXPORT int bw_attention_head_dim() { return HD; }
 
 // rows_work: n_rows_items int4 (request, first token, 0, 0) for segments of more than 16 stacked rows.
 // keys_work: n_keys_items int4 (request, slice, slices, item) for the others; merge_work: one int4 per
-// item that has more than one slice.  part_o / part_ml: float32 scratch for
+// item that has more than one slice (merge_max_slices: the most slices any of them has, 0: unknown).
+// part_o / part_ml: float32 scratch for
 // [items, nkv, slices, 16, HD] and [.., 2].  window <= 0: all keys.
 // qkv != null (q may be null then): every request has ONE token, and its queries, key and value come from
 // the q/k/v product itself: float32 [qkv_planes][tokens][(nh + 2 nkv) * HD], the planes qkv_plane_stride
@@ -844,7 +885,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
                                const int* merge_work, int n_merge_items, float* part_o, float* part_ml, int nh,
                                int nkv, int page_size, int num_pages, int window, float scale,
                                const float* qkv, int qkv_planes, long long qkv_plane_stride, const float* rope_table,
-                               int rd, int append, void* stream) {
+                               int rd, int append, int merge_max_slices, void* stream) {
     if (nkv <= 0 || nh % nkv != 0) return BW_ERR_BAD_ARG;
     const int G = nh / nkv;
     if (G > 16) return BW_ERR_UNSUPPORTED;
@@ -898,7 +939,11 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
             BW_LAUNCH_CHECK();
         }
         if (n_merge_items > 0) {
-            bw::launch((attn_merge_kernel), dim3(n_merge_items, nkv, 16), dim3(MERGE_THREADS), 0, s, p, merge_work);
+            // merge_max_slices: the most slices of any merge item (0: unknown)
+            if (merge_max_slices > 0 && merge_max_slices <= MERGE_FEW && 16 * MERGE_QUADS <= 1024)
+                bw::launch((attn_merge_few_kernel), dim3(n_merge_items, nkv), dim3(16 * MERGE_QUADS), 0, s, p, merge_work);
+            else
+                bw::launch((attn_merge_kernel), dim3(n_merge_items, nkv, 16), dim3(MERGE_THREADS), 0, s, p, merge_work);
             BW_LAUNCH_CHECK();
         }
     }

@@ -676,7 +676,7 @@ def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
 
 _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_int, c_int, c_float,
-                                   c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_void_p]
+                                   c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_int, c_void_p]
 
 
 _sm_counts = {}
@@ -756,7 +756,7 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
         return torch.tensor(items, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
 
     work = (up(rows_items), len(rows_items), up(keys_items), len(keys_items), up(merge_items),
-            len(merge_items), total_slices if merge_items else 0)
+            len(merge_items), total_slices if merge_items else 0, max((m[2] for m in merge_items), default=0))
     batch.static_extras[key] = work
     return work
 
@@ -790,7 +790,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
     check_attention_supported(torch.bfloat16, hd, G)
     # prompt portions: the tcgen05 kernel (128-row tiles) where it takes the geometry, else mma.sync (64-row tiles)
     use_tc = attention_tc_supports(hd, G, page_size)
-    rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices = attention_work(
+    rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices, merge_max = attention_work(
         batch, G, nkv, window, hd, rows_tile=128 if use_tc else 64, page_size=page_size)
     part_o = part_ml = None
     if n_merge:
@@ -813,7 +813,8 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
               int(window or 0), float(scale),
               _ptr(raw.planes if raw is not None else None), raw.planes.shape[0] if raw is not None else 0,
               raw.planes.stride(0) if raw is not None else 0, _ptr(raw.table if raw is not None else None),
-              raw.rotary_dim if raw is not None else 0, int(raw.append) if raw is not None else 0, _stream()), "attention_mma")
+              raw.rotary_dim if raw is not None else 0, int(raw.append) if raw is not None else 0, merge_max,
+              _stream()), "attention_mma")
     return out
 
 
