@@ -819,10 +819,13 @@ attn_merge_kernel(Params p, const int* merge_items) {
     }
 }
 
-// The same for items of at most MERGE_FEW slices (decode batches, where the slices are few): one CTA per
+// The same for items of at most MERGE_FEW slices (decode batches of several requests, where the slices are few): one CTA per
 // (item, kv head), a thread per row and four channels; every thread fetches the maxima and sums of its
 // row's slices itself, so all its loads are in flight together and nothing waits at a barrier.
-constexpr int MERGE_FEW = 8;
+#ifndef ATTN_MERGE_FEW
+#define ATTN_MERGE_FEW 8   // measured: 1 % of a decode step at batch 8 (6 slices); 16 gains nothing at 6 and loses at 13 slices
+#endif
+constexpr int MERGE_FEW = ATTN_MERGE_FEW;
 __global__ void __launch_bounds__(16 * MERGE_QUADS)
 attn_merge_few_kernel(Params p, const int* merge_items) {
     BW_PDL_TRIGGER();

@@ -806,7 +806,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
         n_rows = 0
         if not n_keys:
             return out
-    fn = _fn("attention_mma", "bw_attention_mma", _ATTN_MMA_ARGS, macros={"HEAD_DIM": hd})
+    fn = _fn("attention_mma", "bw_attention_mma", _ATTN_MMA_ARGS, macros=attention_mma_macros(hd))
     _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
               _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, _ptr(keys_w),
               n_keys, _ptr(merge_w), n_merge, _ptr(part_o), _ptr(part_ml), nh, nkv, page_size, num_pages,
@@ -828,6 +828,15 @@ def attention_tc_supports(hd: int, G: int, page_size: int) -> bool:
     if os.environ.get("BW_ATTN_TC", "1") == "0":
         return False
     return hd % 64 == 0 and hd <= 256 and G <= 128 and page_size in (8, 16, 32, 64)
+
+
+def attention_mma_macros(hd: int) -> dict:
+    """The build of the mma.sync attention for this head size.  BW_ATTN_MERGE_FEW=n in the environment sets up
+    to how many slices the slice merge without barriers takes (for measurements; default: the source's)."""
+    macros = {"HEAD_DIM": hd}
+    if os.environ.get("BW_ATTN_MERGE_FEW"):
+        macros["ATTN_MERGE_FEW"] = int(os.environ["BW_ATTN_MERGE_FEW"])
+    return macros
 
 
 def attention_tc_macros(hd: int) -> dict:
