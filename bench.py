@@ -359,6 +359,7 @@ def main():
                           num_pages=num_pages, max_batch_tokens=max(args.prefill_tokens, max_b), seed=0,
                           cuda_graphs=not args.no_graphs)
     eng = llm.engine
+    eng.options.graph_after = 1   # the decode measurements' batch sizes are recorded in their first warm-up step
     V = cfg["vocab_size"]
     gen = torch.Generator().manual_seed(1234)
     per_layer, weight_elems, kv_per_token = model_bytes_and_flops(cfg, args.layers)

@@ -51,6 +51,8 @@ class EngineOptions:
     max_context: Optional[int] = None  # longest request; None: what the pool holds
     ignore_unexpected: bool = False  # tensors of a checkpoint that the model does not use: pass over, no error
     cuda_graphs: bool = True         # replay decode-only steps from a CUDA graph per batch size
+    graph_after: int = 4             # a batch size is recorded at its n-th decode-only step (a recording costs about
+                                     # four uncaptured steps; batch sizes that pass by once or twice never pay it)
     native_decode: bool = True       # greedy decode-only steps of live requests go through the C entry point
     max_graph_batch: int = 256
     device: str = "cuda:0"
@@ -86,6 +88,7 @@ class Engine:
                                   dtype=self.dtype, device=self.device)
         self._builder = BatchBuilder(self.device)
         self._graphs: Dict[int, dict] = {}
+        self._graph_uses: Dict[int, int] = {}   # decode-only steps seen per batch size that has no graph yet
         self._grown = None
         longest = options.max_context or num_pages * options.page_size
         self._graph_width = -(-longest // options.page_size)
@@ -275,6 +278,16 @@ class Engine:
                 return None
         return len(entries)
 
+    def _graph_due(self, R: int) -> bool:
+        """Whether this decode-only step of batch size R runs from (or records) the graph: yes once the
+        graph exists, and at the ``graph_after``-th such step; the steps before run uncaptured."""
+        slot = self._graphs.get(R)
+        if slot is not None and slot["graph"] is not None:
+            return True
+        n = self._graph_uses.get(R, 0) + 1
+        self._graph_uses[R] = n
+        return n >= self.options.graph_after
+
     def _step_graph(self, entries: Sequence[StepEntry], R: int, token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         width = self._graph_width
         slot = self._graphs.get(R)
@@ -418,6 +431,8 @@ class Engine:
         try:
             with torch.cuda.device(self.device):
                 R = self._graph_key(entries)
+                if R is not None and not self._graph_due(R):
+                    R = None
                 if R is not None:
                     logits = self._step_graph(entries, R, token_source)
                     T = R

@@ -281,6 +281,7 @@ def test_forward_batch_async_feeds_the_sampled_tokens_on_the_device(folders, dty
     raw, _, page = tiny.CONFIGS["qwen"]
     folder = folders[("qwen", dtype)]
     llm = make(folder, dtype, page_size=page)
+    llm.engine.options.graph_after = 1       # the batch size is recorded at its first decode step
     prompts = {0: tiny.prompt(20, raw["vocab_size"], 3), 2: tiny.prompt(11, raw["vocab_size"], 4), 5: tiny.prompt(33, raw["vocab_size"], 6)}
 
     def decode(pipelined, steps=7):

@@ -224,7 +224,7 @@ def test_the_first_step_of_a_decode_batch_size_runs_the_model_once(monkeypatch):
     cfg = parse_config(tiny.CONFIGS["llama"][0])
     model = StatefulModel(cfg.vocab_size)
     eng = Engine(cfg, model, EngineOptions(dtype="float32", page_size=8, num_pages=12, max_requests=3,
-                                           max_batch_tokens=64, cuda_graphs=True, device="cpu"))
+                                           max_batch_tokens=64, cuda_graphs=True, graph_after=1, device="cpu"))
     eng.step([StepEntry("a", [1, 2, 3], []), StepEntry("b", [4], [])])      # prompts: not a decode-only step
     assert model.runs == 1 and eng.graph_kernel_count(2) == 0
     slot_a, slot_b = eng.cache.slot("a"), eng.cache.slot("b")
@@ -398,6 +398,7 @@ def test_decode_steps_prepared_ahead_give_the_same_tokens_and_are_taken_back_on_
         e = BlackwellEngine(None, InferenceConfig(max_context_length=96, max_batch_size=3), config=raw, page_size=8,
                             max_batch_tokens=32, cuda_graphs=True)
         e.pipeline = pipeline
+        e.engine.options.graph_after = 1     # every batch size is recorded at its first decode step
         launched = {"ahead": 0, "cancelled": 0}
         real_launch, real_cancel = e.engine.launch_prepared, e.engine.cancel_prepared
 

@@ -664,7 +664,8 @@ def test_graph_safe_stateful_mixer_is_advanced_once_by_the_step_that_records_the
     W = random_tensors(model_param_specs(raw), seed=2, std=0.3, dtype=torch.float32)
 
     def run(graphs):
-        eng = Engine.from_tensors(raw, W, dtype="float32", page_size=8, max_tokens=64, max_requests=2, cuda_graphs=graphs)
+        eng = Engine.from_tensors(raw, W, dtype="float32", page_size=8, max_tokens=64, max_requests=2, cuda_graphs=graphs,
+                                  graph_after=1)
         outs = [eng.step([StepEntry("a", [1, 2, 3], [2]), StepEntry("b", [4], [0])]).clone()]
         for t in (5, 6, 7):                       # decode-only steps of batch size 2: recorded at the first, replayed after
             outs.append(eng.step([StepEntry("a", [t], [0]), StepEntry("b", [t + 10], [0])]).clone())
