@@ -14,6 +14,8 @@ src/core/engine_prefill_coordinator.cpp:160-169).
 """
 from __future__ import annotations
 
+import contextlib
+
 from dataclasses import dataclass
 from typing import Dict, Mapping, Optional, Sequence
 
@@ -51,8 +53,8 @@ class EngineOptions:
     max_context: Optional[int] = None  # longest request; None: what the pool holds
     ignore_unexpected: bool = False  # tensors of a checkpoint that the model does not use: pass over, no error
     cuda_graphs: bool = True         # replay decode-only steps from a CUDA graph per batch size
-    graph_after: int = 4             # a batch size is recorded at its n-th decode-only step (a recording costs about
-                                     # four uncaptured steps; batch sizes that pass by once or twice never pay it)
+    graph_after: int = 3             # a batch size is recorded at its n-th decode-only step (a recording costs about
+                                     # two uncaptured steps; batch sizes that pass by once or twice never pay it)
     native_decode: bool = True       # greedy decode-only steps of live requests go through the C entry point
     max_graph_batch: int = 256
     device: str = "cuda:0"
@@ -89,6 +91,7 @@ class Engine:
         self._builder = BatchBuilder(self.device)
         self._graphs: Dict[int, dict] = {}
         self._graph_uses: Dict[int, int] = {}   # decode-only steps seen per batch size that has no graph yet
+        self._capture_stream = None
         self._grown = None
         longest = options.max_context or num_pages * options.page_size
         self._graph_width = -(-longest // options.page_size)
@@ -278,15 +281,26 @@ class Engine:
                 return None
         return len(entries)
 
-    def _graph_due(self, R: int) -> bool:
-        """Whether this decode-only step of batch size R runs from (or records) the graph: yes once the
-        graph exists, and at the ``graph_after``-th such step; the steps before run uncaptured."""
-        slot = self._graphs.get(R)
-        if slot is not None and slot["graph"] is not None:
-            return True
-        n = self._graph_uses.get(R, 0) + 1
-        self._graph_uses[R] = n
-        return n >= self.options.graph_after
+    @contextlib.contextmanager
+    def _capture(self, graph):
+        """Records what runs inside into ``graph`` on a stream of its own.  (``torch.cuda.graph`` does the same
+        after a full garbage collection, 25 to 40 ms with a model's worth of Python objects: more than the
+        recording itself.)"""
+        if not hasattr(graph, "capture_begin"):          # a stand-in graph of the tests
+            with torch.cuda.graph(graph):
+                yield
+            return
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(self.device)
+        side = self._capture_stream
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            graph.capture_begin()
+            try:
+                yield
+            finally:
+                graph.capture_end()
+        torch.cuda.current_stream(self.device).wait_stream(side)
 
     def _step_graph(self, entries: Sequence[StepEntry], R: int, token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         width = self._graph_width
@@ -303,26 +317,42 @@ class Engine:
                 slot["buf"][:R].copy_(token_source)     # the token ids lead the packed layout
             slot["graph"].replay()
             return slot["logits"]
-        # The first step of this batch size: the model runs ONCE, uncaptured, and that run is the
-        # step's result (a mixer with state of its own must not see the step twice).  Then the same
-        # launches are recorded (a capture executes nothing) for the later steps of this size.
+        # No graph of this batch size yet.  Its first ``graph_after`` - 1 decode-only steps run uncaptured, on
+        # the batch as a replay would see it (block tables of the graph's width, the key bound of the graph), so
+        # that every kernel and buffer of the graph has been used once; the next one records.  Whichever way,
+        # the model runs ONCE for the step (a mixer with state of its own must not see a step twice): the
+        # step that records after uncaptured ones captures (a capture executes nothing) and replays; a step
+        # that records as the very first of its size runs uncaptured, which is its result, and then captures.
+        uses = self._graph_uses.get(R, 0) + 1
+        self._graph_uses[R] = uses
         batch = self.prepare(entries, min_blocks=width, into=slot["buf"])
         if any(t.shape[1] != width for t in batch.block_tables.values()):
             raise EngineError("a request outgrew max_context: its block table no longer fits the graph")
         batch.static_bound = width * self.cache.page_size
+        # what the host derives from the batch's shape and the bound alone (attention work lists) is made by the
+        # first of these steps and shared by the later ones and the graph: nothing is copied to the device inside a capture
+        batch.static_extras = slot.setdefault("static_extras", {})
         if token_source is not None:
             batch.token_ids.copy_(token_source)
         from ..kernels import ops
-        logits = self.model.forward(batch, self.cache.views)
-        torch.cuda.synchronize(self.device)
-        batch.extras.clear()   # what depends on this step's values is recomputed inside the graph
+        record = uses >= self.options.graph_after
+        logits = None
+        if not record or uses == 1:
+            logits = self.model.forward(batch, self.cache.views)
+            if not record:
+                return logits
+            torch.cuda.synchronize(self.device)
+            batch.extras.clear()   # what depends on this step's values is recomputed inside the graph
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
-        with torch.cuda.graph(graph):
+        with self._capture(graph):
             slot["logits"] = self.model.forward(batch, self.cache.views)
         slot["kernels"] = ops.launches - before
         slot["graph"] = graph
         slot["batch"] = batch   # keeps the per-step tensors that the captured kernels read alive
+        if logits is None:
+            graph.replay()
+            logits = slot["logits"]
         return logits
 
     def graph_kernel_count(self, batch_size: int) -> int:
@@ -431,8 +461,6 @@ class Engine:
         try:
             with torch.cuda.device(self.device):
                 R = self._graph_key(entries)
-                if R is not None and not self._graph_due(R):
-                    R = None
                 if R is not None:
                     logits = self._step_graph(entries, R, token_source)
                     T = R
