@@ -236,6 +236,19 @@ def test_the_first_step_of_a_decode_batch_size_runs_the_model_once(monkeypatch):
     assert model.runs == 3 and model.seen[slot_a] == 5 and model.seen[slot_b] == 3
     assert lg[:, :2].tolist() == [[9, 2], [6, 4]]
 
+    # A batch size recorded at its third decode-only step: two uncaptured steps, then a step that captures (which
+    # runs nothing) and replays, then replays.  Every step runs the model once.
+    model = StatefulModel(cfg.vocab_size)
+    eng = Engine(cfg, model, EngineOptions(dtype="float32", page_size=8, num_pages=12, max_requests=3,
+                                           max_batch_tokens=64, cuda_graphs=True, graph_after=3, device="cpu"))
+    eng.step([StepEntry("a", [1, 2, 3], []), StepEntry("b", [4], [])])
+    slot_a, slot_b = eng.cache.slot("a"), eng.cache.slot("b")
+    for k, (ta, tb) in enumerate([(7, 8), (9, 6), (5, 4), (3, 2)]):
+        lg = eng.step([StepEntry("a", [ta], [0]), StepEntry("b", [tb], [0])])
+        assert model.runs == 2 + k and model.seen[slot_a] == 4 + k and model.seen[slot_b] == 2 + k
+        assert lg[:, :2].tolist() == [[ta, 3 + k], [tb, 1 + k]]
+        assert (eng.graph_kernel_count(2) > 0 or eng._graphs[2]["graph"] is not None) == (k >= 2)
+
 
 def test_no_device_no_engine():
     cfg = tiny.CONFIGS["llama"][0]
