@@ -47,7 +47,9 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of the current stream of the current device (torch.cuda.current_stream() builds a
+    # Stream object around the same number, several microseconds a call)
+    return c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 def _dev(t: torch.Tensor, name: str, dtype=None, contiguous=True):
@@ -83,14 +85,20 @@ def timing_report() -> dict:
     return {k: tuple(v) for k, v in (_timings or {}).items()}
 
 
+_fns = {}   # (library, function, macros) -> the ctypes function with its signature set
+
+
 def _fn(lib_name: str, fn_name: str, argtypes, macros=None, extra_flags=(), tag=None):
-    lib = load_library(lib_name, macros, extra_flags)
-    fn = getattr(lib, fn_name)
-    key = (id(lib), fn_name)
-    if key not in _sigs_done:
-        fn.argtypes = argtypes
-        fn.restype = c_int
-        _sigs_done.add(key)
+    key = (lib_name, fn_name, tuple(sorted(macros.items())) if macros else None, extra_flags)
+    fn = _fns.get(key)
+    if fn is None:
+        lib = load_library(lib_name, macros, extra_flags)
+        fn = getattr(lib, fn_name)
+        if (id(lib), fn_name) not in _sigs_done:
+            fn.argtypes = argtypes
+            fn.restype = c_int
+            _sigs_done.add((id(lib), fn_name))
+        _fns[key] = fn
     if _timings is None:
         return fn
 
@@ -473,15 +481,21 @@ GEMM_PLANES_MAX_TOKENS = 256       # up to here gemm_tc_planes leaves them as pl
 SWIGLU_BLOCK = 16  # gate/up rows of a fused SwiGLU weight alternate in blocks of this many
 
 
-def _gemm_macros():
-    """Build options of the tensor-core product from the environment, for measurements:
-    BW_GEMM_NARROW="<stages>,<CTAs per SM>" of the kernel for up to 16 tokens (default: the source's)."""
-    import os
+def _read_gemm_macros():
     v = os.environ.get("BW_GEMM_NARROW")
     if not v:
         return None
     st, ctas = v.split(",")
     return {"GEMM_NARROW_STAGES": int(st), "GEMM_NARROW_CTAS": int(ctas)}
+
+
+_GEMM_MACROS = _read_gemm_macros()
+
+
+def _gemm_macros():
+    """Build options of the tensor-core product from the environment (read when this module is loaded), for
+    measurements: BW_GEMM_NARROW="<stages>,<CTAs per SM>" of the kernel for up to 16 tokens (default: the source's)."""
+    return _GEMM_MACROS
 
 
 def _workspace(device: torch.device):
@@ -833,10 +847,16 @@ def attention_tc_supports(hd: int, G: int, page_size: int) -> bool:
 def attention_mma_macros(hd: int) -> dict:
     """The build of the mma.sync attention for this head size.  BW_ATTN_MERGE_FEW=n in the environment sets up
     to how many slices the slice merge without barriers takes (for measurements; default: the source's)."""
-    macros = {"HEAD_DIM": hd}
-    if os.environ.get("BW_ATTN_MERGE_FEW"):
-        macros["ATTN_MERGE_FEW"] = int(os.environ["BW_ATTN_MERGE_FEW"])
+    macros = _ATTN_MMA_MACROS.get(hd)
+    if macros is None:
+        macros = {"HEAD_DIM": hd}
+        if os.environ.get("BW_ATTN_MERGE_FEW"):
+            macros["ATTN_MERGE_FEW"] = int(os.environ["BW_ATTN_MERGE_FEW"])
+        _ATTN_MMA_MACROS[hd] = macros
     return macros
+
+
+_ATTN_MMA_MACROS = {}
 
 
 def attention_tc_macros(hd: int) -> dict:
