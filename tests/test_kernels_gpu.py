@@ -28,7 +28,8 @@ def rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
                                    (100, 6144, 1024), (256, 384, 96), (257, 512, 256), (300, 260, 200),
                                    (1000, 1111, 520), (2048, 1024, 4096),
                                    (2048, 4096, 64), (2048, 6144 + 48, 64),     # tiles 240 wide, the last one of a row cut
-                                   (3, 19000, 200), (16, 25000, 136), (1, 128 * 149, 64 * 149)])   # few tokens, more tiles than SMs: k-blocks dealt out in ranges
+                                   (3, 19000, 200), (16, 25000, 136), (1, 128 * 149, 64 * 149),    # few tokens, more tiles than SMs: k-blocks dealt out in ranges
+                                   (17, 19000, 200), (40, 25000, 136), (64, 128 * 149, 64 * 3)])   # the same up to 64 tokens
 @pytest.mark.parametrize("mode", ["plain", "bias_f32out", "accumulate"])
 def test_gemm_tc(ops, M, N, K, mode):
     x = rand(M, K, dtype=torch.bfloat16, seed=1).to(DEV)
@@ -252,7 +253,7 @@ def test_gemm_tc_split_k_on_a_tile_width_that_is_no_power_of_two(ops):
     assert float((out.double() - ref).abs().max()) / float(ref.abs().max()) <= 1e-5
 
 
-@pytest.mark.parametrize("M,I,K,splits", [(1, 176, 64, 0), (8, 14336, 4096, 0), (40, 1008, 512, 3), (300, 176, 256, 0),
+@pytest.mark.parametrize("M,I,K,splits", [(1, 176, 64, 0), (8, 14336, 4096, 0), (33, 14336, 1024, 0), (64, 14336, 512, 0), (40, 1008, 512, 3), (300, 176, 256, 0),
                                           (700, 528, 2048, 2), (2048, 1024, 1024, 0),
                                           (2048, 14336, 64, 0)])   # tiles 224 wide
 def test_gemm_tc_swiglu_epilogue(ops, M, I, K, splits):
